@@ -1,0 +1,130 @@
+/*
+ * xkb200 — C ABI of the B200 (sm_100a) fused-MoE hot path.
+ *
+ * Every pointer is a raw DEVICE pointer unless the parameter name ends in
+ * `_host`.  `stream` is a `cudaStream_t` passed as `void*` (NULL = the legacy
+ * default stream).  Every entry point returns 0 on success and a negative
+ * `XKB_ERR_*` code on failure; `xkb_last_error()` then holds a readable
+ * message for the calling thread.  Nothing here allocates device memory: the
+ * caller owns inputs, outputs and the workspace whose size the matching
+ * `*_workspace_bytes` query reports.
+ *
+ * The citations name the reference interface each entry point stands in for
+ * (paths inside the ResearchComputer/xkernels tree).
+ */
+#ifndef XKB200_H_
+#define XKB200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define XKB_OK 0
+#define XKB_ERR_ARG (-1)       /* bad argument / unsupported shape            */
+#define XKB_ERR_CUDA (-2)      /* a CUDA runtime or driver call failed        */
+#define XKB_ERR_WORKSPACE (-3) /* workspace missing or too small              */
+#define XKB_ERR_DEVICE (-4)    /* a kernel reported a bounded-wait time-out   */
+
+/* dtype codes used by the `*_dtype` parameters */
+#define XKB_BF16 0
+#define XKB_F32 1
+
+/* kernel-path selectors for the `path` parameters */
+#define XKB_PATH_AUTO 0  /* tensor-core kernel when the shape allows, else SIMT */
+#define XKB_PATH_SIMT 1  /* force the generic SIMT kernels                      */
+#define XKB_PATH_TC 2    /* force the tcgen05 kernels (error if shape unfit)    */
+
+/* Library / build identification. */
+const char* xkb_version(void);
+/* Message of the last failure on the calling thread ("" if none). */
+const char* xkb_last_error(void);
+/* Number of kernel launches issued by this library since load (all threads). */
+int64_t xkb_launch_count(void);
+
+/* ------------------------------------------------------------------------
+ * moe_align_block_size
+ * Replaces: src/xkernels/ops/moe/w4a16.py:53-101 (moe_align_block_size_ref),
+ *           src/xkernels/ops/moe/triton/align_kernel.py:156-248 (Triton launcher)
+ *           and, with `expert_map`, w4a16.py:104-155 / align_kernel.py:251-312.
+ *
+ * topk_ids      [numel] int32 expert id per token-slot (flattened [M, top_k]).
+ * expert_map    NULL, or [num_map] int32 global->local map (-1 = not local);
+ *               slots whose expert is not local are dropped.  `num_experts`
+ *               is then the LOCAL expert count.
+ * sorted_ids    [numel + (num_experts+1)*(block_size-1)] int32, every entry
+ *               written (unused entries = numel).
+ * expert_ids    [ceil(len(sorted_ids)/block_size)] int32, every entry written
+ *               (entries past the used blocks = 0).
+ * num_post_pad  [1] int32.
+ * expert_offsets NULL or [num_experts+1] int32: start of each expert's padded
+ *               run in sorted_ids (entry num_experts = num_post_pad).
+ * workspace     xkb_moe_align_workspace_bytes(numel, num_experts) bytes.
+ * ---------------------------------------------------------------------- */
+int64_t xkb_moe_align_workspace_bytes(int64_t numel, int num_experts);
+int xkb_moe_align_block_size(const int32_t* topk_ids, int64_t numel,
+                             int num_experts, int block_size,
+                             const int32_t* expert_map, int num_map,
+                             int32_t* sorted_ids, int32_t* expert_ids,
+                             int32_t* num_post_pad, int32_t* expert_offsets,
+                             void* workspace, int64_t workspace_bytes,
+                             void* stream);
+
+/* ------------------------------------------------------------------------
+ * moe_sum_reduce: out[m,:] = rsf * sum_k (w[m,k] or 1) * y[m,k,:]
+ * Replaces: src/xkernels/ops/moe/sum_reduce.py:20-39 (reference),
+ *           src/xkernels/ops/moe/triton/sum_reduce_kernel.py:66-100,
+ *           src/xkernels/ops/moe/cute/entry.py:19-40.
+ * y [M, top_k, H] (y_dtype), w NULL or [M, top_k] (w_dtype), out [M, H]
+ * (out_dtype).  The sum runs in fp32 in ascending k, so it is deterministic.
+ * ---------------------------------------------------------------------- */
+int xkb_moe_sum_reduce(const void* y, int y_dtype, const void* w, int w_dtype,
+                       void* out, int out_dtype, int64_t M, int top_k,
+                       int64_t H, float routed_scaling_factor, void* stream);
+
+/* ------------------------------------------------------------------------
+ * fused_moe_int4_w4a16: out[m] = sum_j w[m,j] * (A[m] @ dequant(W[e_mj])^T)
+ * Replaces: src/xkernels/ops/moe/reference.py:22-70 (moe_w4a16_ref) and
+ *           src/xkernels/ops/moe/triton/moe_int4_kernel.py:438-577 (Triton
+ *           entry: align + grouped GEMM + top-k combine).
+ * A [M,K] (a_dtype), packed [E,N,K/8] int32 (low nibble = lowest k, zero
+ * point 8), scale [E,N,K/group] bf16, topk_ids [M,top_k] int32, topk_w
+ * [M,top_k] fp32, expert_map NULL or [num_map] int32, out [M,N] (a_dtype).
+ * ---------------------------------------------------------------------- */
+int64_t xkb_fused_moe_int4_w4a16_workspace_bytes(int64_t M, int64_t N,
+                                                 int64_t K, int E, int top_k,
+                                                 int a_dtype);
+int xkb_fused_moe_int4_w4a16(const void* A, int a_dtype, const int32_t* packed,
+                             const void* scale, const int32_t* topk_ids,
+                             const float* topk_w, const int32_t* expert_map,
+                             int num_map, void* out, int64_t M, int64_t N,
+                             int64_t K, int E, int top_k, int group_size,
+                             int mul_routed_weight, int path, void* workspace,
+                             int64_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------
+ * fused_moe_mxfp4: gate_up GEMM -> clamped SwiGLU -> down GEMM -> combine
+ * Replaces: src/xkernels/ops/moe/mxfp4_reference.py:28-112 (moe_mxfp4_ref)
+ *           and src/xkernels/ops/moe/triton/moe_mxfp4_kernel.py:487-568.
+ * A [M,hidden] (a_dtype), w13 [E,2*ispp,hidden/2] u8, w13_scale
+ * [E,2*ispp,hidden/32] u8 (e8m0), w2 [E,hidden,ispp/2] u8, w2_scale
+ * [E,hidden,ispp/32] u8, b13 NULL or [E,2*ispp] bf16, b2 NULL or [E,hidden]
+ * bf16, out [M,hidden] (a_dtype).  swiglu_limit <= 0 disables the clamp.
+ * ---------------------------------------------------------------------- */
+int64_t xkb_fused_moe_mxfp4_workspace_bytes(int64_t M, int64_t hidden,
+                                            int64_t ispp, int E, int top_k);
+int xkb_fused_moe_mxfp4(const void* A, int a_dtype, const uint8_t* w13,
+                        const uint8_t* w13_scale, const uint8_t* w2,
+                        const uint8_t* w2_scale, const int32_t* topk_ids,
+                        const float* topk_w, const void* b13, const void* b2,
+                        const int32_t* expert_map, int num_map, void* out,
+                        int64_t M, int64_t hidden, int64_t ispp, int E,
+                        int top_k, float swiglu_limit, int mul_routed_weight,
+                        int path, void* workspace, int64_t workspace_bytes,
+                        void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* XKB200_H_ */

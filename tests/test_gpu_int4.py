@@ -1,0 +1,109 @@
+"""fused_moe_int4_w4a16 on the GPU, through the C-ABI, vs the oracle and the fixtures made by
+the reference.  Tolerance (written here, from the task statement and the op spec
+registry/ops/moe_int4_w4a16.spec.json:30-41): bf16 outputs |a-e| <= 1e-2 + 2e-2|e| against the
+fp32-accumulated reference; fp32 activations rtol = atol = 1e-3."""
+
+import pytest
+import torch
+
+import xkernels_b200 as xkb
+from oracle import moe_oracle as oracle
+from tests.golden.golden_io import load_case
+from tests.gpu_util import assert_within, to_dev
+from xkernels_b200 import synth
+
+pytestmark = pytest.mark.gpu
+TOL = {torch.bfloat16: (2e-2, 1e-2), torch.float32: (1e-3, 1e-3)}
+KEYS = ("A", "packed", "scale", "topk_ids", "topk_w")
+
+
+def call(c, dev, **kw):
+    d = to_dev({k: c[k] for k in KEYS}, dev)
+    return xkb.fused_moe_int4_w4a16(d["A"], d["packed"], d["scale"], d["topk_ids"], d["topk_w"],
+                                    group_size=int(c.get("group_size", 32)), **kw)
+
+
+@pytest.mark.parametrize("name", ["int4_sweep0", "int4_sweep1", "int4_sweep2", "int4_sweep3", "int4_tiny"])
+@pytest.mark.parametrize("path", ["auto", "simt"])
+def test_golden(name, path, cuda_device):
+    c = load_case(name)
+    out = call(c, cuda_device, path=path)
+    assert_within(out, c["out"], *TOL[c["A"].dtype], what=f"{name}/{path}")
+
+
+def test_golden_no_routed_weight(cuda_device):
+    c = load_case("int4_tiny")
+    out = call(c, cuda_device, mul_routed_weight=False)
+    assert_within(out, load_case("int4_tiny_noweight")["out"], *TOL[torch.bfloat16], what="noweight")
+
+
+def test_golden_replicated_expert_parallel(cuda_device):
+    c = load_case("int4_tiny")
+    total = torch.zeros(c["out"].shape, dtype=torch.float32)
+    for rank in range(2):
+        g = load_case(f"int4_tiny_ep_rank{rank}")
+        sl = slice(rank * 4, (rank + 1) * 4)
+        d = to_dev({k: c[k] for k in KEYS}, cuda_device)
+        part = xkb.fused_moe_int4_w4a16(d["A"], d["packed"][sl].contiguous(), d["scale"][sl].contiguous(),
+                                        d["topk_ids"], d["topk_w"], expert_map=g["expert_map"].to(cuda_device))
+        assert_within(part, g["out"], *TOL[torch.bfloat16], what=f"partial rank {rank}")
+        total += part.float().cpu()
+    assert_within(total, c["out"].float(), 2e-2, 2e-2, what="sum of partials")
+
+
+@pytest.mark.parametrize("M,K,N,E,top_k,group,dtype", [
+    (16, 64, 32, 4, 2, 32, torch.bfloat16), (1, 64, 32, 4, 2, 32, torch.bfloat16),
+    (37, 96, 48, 8, 3, 32, torch.bfloat16), (16, 64, 32, 4, 2, 32, torch.float32),
+    (5, 128, 130, 3, 2, 64, torch.bfloat16), (9, 256, 17, 2, 1, 128, torch.float32),
+    (33, 512, 256, 6, 4, 32, torch.bfloat16), (3, 40, 8, 2, 2, 8, torch.bfloat16),
+])
+def test_against_oracle_with_repeated_ids(M, K, N, E, top_k, group, dtype, cuda_device):
+    """Harness-style inputs (registry/input_gen.py:138-159): ids drawn with replacement, weights
+    uniform and not normalised."""
+    g = torch.Generator().manual_seed(M * 7 + K)
+    A = torch.randn(M, K, generator=g).to(dtype)
+    codes = torch.randint(0, 16, (E, N, K), generator=g)
+    packed = synth.pack_int4_codes(codes)
+    scale = (torch.rand(E, N, K // group, generator=g) * 0.02 + 0.005).to(torch.bfloat16)
+    ids = torch.randint(0, E, (M, top_k), generator=g, dtype=torch.int32)
+    w = torch.rand(M, top_k, generator=g)
+    want = oracle.moe_w4a16_loop(A, packed, scale, ids, w, group)
+    c = {"A": A, "packed": packed, "scale": scale, "topk_ids": ids, "topk_w": w, "group_size": group}
+    got = call(c, cuda_device)
+    assert_within(got, want, *TOL[dtype], what="auto")
+    assert torch.equal(got, call(c, cuda_device)), "second run differs: the combine must be deterministic"
+
+
+def test_padding_never_leaks(cuda_device):
+    """Poisoned activations for tokens that no slot of a hot expert uses must not reach other
+    rows: NaN in one token's row only shows up in that token's output row."""
+    c = load_case("int4_tiny")
+    A = c["A"].clone()
+    A[3] = float("nan")
+    c2 = dict(c, A=A)
+    out = call(c2, cuda_device).cpu()
+    assert torch.isnan(out[3]).all()
+    keep = [i for i in range(out.shape[0]) if i != 3]
+    assert_within(out[keep], c["out"][keep], *TOL[torch.bfloat16], what="other rows")
+
+
+def test_decode_config_slice_and_properties(cuda_device):
+    """M=64, K=7168, N=4096, E=48, top_k=8 at full size: a 256-row slice of N is checked against
+    the oracle; the whole output through determinism and linearity in the routing weights."""
+    cfg = synth.CONFIGS["int4_decode"]
+    d = synth.make_int4(cfg, seed=1729, device=cuda_device)
+    out = xkb.fused_moe_int4_w4a16(d["A"], d["packed"], d["scale"], d["topk_ids"], d["topk_w"])
+    assert out.shape == (cfg.M, cfg.N) and out.dtype == torch.bfloat16
+    n0, n1 = 1024, 1280
+    want = oracle.moe_w4a16(d["A"].cpu(), d["packed"][:, n0:n1].cpu(), d["scale"][:, n0:n1].cpu(),
+                            d["topk_ids"].cpu(), d["topk_w"].cpu(), 32)
+    assert_within(out[:, n0:n1], want, *TOL[torch.bfloat16], what="decode slice")
+    assert torch.equal(out, xkb.fused_moe_int4_w4a16(d["A"], d["packed"], d["scale"], d["topk_ids"], d["topk_w"]))
+    out2 = xkb.fused_moe_int4_w4a16(d["A"], d["packed"], d["scale"], d["topk_ids"], 2 * d["topk_w"])
+    assert_within(out2.float(), 2 * out.float(), 1.6e-2, 1e-2, what="linearity in topk_w")
+
+
+def test_cpu_tensor_is_refused():
+    c = load_case("int4_sweep0")
+    with pytest.raises(RuntimeError, match="CUDA"):
+        xkb.fused_moe_int4_w4a16(c["A"], c["packed"], c["scale"], c["topk_ids"], c["topk_w"])

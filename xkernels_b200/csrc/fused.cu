@@ -1,0 +1,217 @@
+// Host side of the fused ops: workspace carving, kernel-path choice and the
+// launch sequence  align -> grouped GEMM(s) -> fixed-order fp32 combine.
+// Everything is enqueued on the caller's stream; no host synchronisation and no
+// allocation happens here.
+#include "common.cuh"
+#include "moe_kernels.h"
+
+namespace xkb {
+
+std::atomic<int64_t> g_launches{0};
+
+char* last_error_buf() {
+  static thread_local char buf[512] = {0};
+  return buf;
+}
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(last_error_buf(), 512, fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+namespace {
+
+struct RoutingBuffers {
+  int32_t* sorted_ids;
+  int32_t* expert_ids;
+  int32_t* num_post;
+  int32_t* expert_off;
+  void* align_ws;
+  int64_t align_ws_bytes;
+};
+
+// Routing buffers are sized for the worst case over the block sizes any path
+// may pick: the longest sorted_ids (largest block) and the most blocks
+// (smallest block).
+constexpr int kMaxBlock = 256;
+constexpr int kMinBlock = 16;
+
+int64_t routing_max_pad(int64_t numel, int E, int block) {
+  return numel + (int64_t)(E + 1) * (block - 1);
+}
+
+RoutingBuffers carve_routing(Carver& c, int64_t numel, int E) {
+  RoutingBuffers r;
+  r.sorted_ids = c.take<int32_t>(routing_max_pad(numel, E, kMaxBlock));
+  r.expert_ids = c.take<int32_t>(ceil_div(routing_max_pad(numel, E, kMinBlock), kMinBlock) + 1);
+  r.num_post = c.take<int32_t>(1);
+  r.expert_off = c.take<int32_t>(E + 1);
+  r.align_ws_bytes = align_workspace_bytes(numel, E);
+  r.align_ws = c.take<char>(r.align_ws_bytes);
+  return r;
+}
+
+int64_t routing_bytes(int64_t numel, int E) {
+  Carver c(nullptr);
+  carve_routing(c, numel, E);
+  return c.off;
+}
+
+Routing make_routing(const RoutingBuffers& b, int64_t numel, int E, int block) {
+  Routing r;
+  r.sorted_ids = b.sorted_ids;
+  r.expert_ids = b.expert_ids;
+  r.num_post = b.num_post;
+  r.expert_off = b.expert_off;
+  r.numel = numel;
+  r.block = block;
+  r.max_pad = routing_max_pad(numel, E, block);
+  r.max_blocks = ceil_div(r.max_pad, block);
+  return r;
+}
+
+}  // namespace
+}  // namespace xkb
+
+using namespace xkb;
+
+extern "C" const char* xkb_version(void) { return "xkb200 0.1 (sm_100a)"; }
+extern "C" const char* xkb_last_error(void) { return last_error_buf(); }
+extern "C" int64_t xkb_launch_count(void) { return g_launches.load(); }
+
+// ---------------------------------------------------------------------------
+// INT4 W4A16
+// ---------------------------------------------------------------------------
+extern "C" int64_t xkb_fused_moe_int4_w4a16_workspace_bytes(int64_t M, int64_t N, int64_t K, int E,
+                                                            int top_k, int a_dtype) {
+  (void)a_dtype;
+  if (M < 0 || N < 0 || K < 0 || E < 0 || top_k < 0) return -1;
+  const int64_t numel = M * top_k;
+  int64_t total = routing_bytes(numel, E);
+  total += align_up(numel * N * 4, 256);           // fp32 slot-indexed partial rows
+  total += int4_tc_workspace_bytes(numel, N, K, E);  // gathered activations etc.
+  return total + 256;
+}
+
+extern "C" int xkb_fused_moe_int4_w4a16(const void* A, int a_dtype, const int32_t* packed,
+                                        const void* scale, const int32_t* topk_ids,
+                                        const float* topk_w, const int32_t* expert_map, int num_map,
+                                        void* out, int64_t M, int64_t N, int64_t K, int E, int top_k,
+                                        int group_size, int mul_routed_weight, int path,
+                                        void* workspace, int64_t workspace_bytes, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  XKB_REQUIRE(a_dtype == XKB_BF16 || a_dtype == XKB_F32, "fused_moe_int4_w4a16: bad a_dtype %d", a_dtype);
+  XKB_REQUIRE(M >= 0 && N >= 0 && K >= 0 && E >= 0 && top_k >= 0, "fused_moe_int4_w4a16: negative dim");
+  XKB_REQUIRE(group_size > 0 && group_size % 8 == 0 && K % group_size == 0 && K % 8 == 0,
+              "fused_moe_int4_w4a16: need K %% 8 == 0, group_size %% 8 == 0, K %% group_size == 0 "
+              "(K=%lld group_size=%d)", (long long)K, group_size);
+  XKB_REQUIRE(path == XKB_PATH_AUTO || path == XKB_PATH_SIMT || path == XKB_PATH_TC,
+              "fused_moe_int4_w4a16: bad path %d", path);
+  if (M == 0 || N == 0) return XKB_OK;
+  XKB_REQUIRE(A && packed && scale && topk_ids && out, "fused_moe_int4_w4a16: null pointer argument");
+  XKB_REQUIRE(topk_w || !mul_routed_weight, "fused_moe_int4_w4a16: topk_w is null");
+  const int64_t need = xkb_fused_moe_int4_w4a16_workspace_bytes(M, N, K, E, top_k, a_dtype);
+  if (workspace == nullptr || workspace_bytes < need)
+    return fail(XKB_ERR_WORKSPACE, "fused_moe_int4_w4a16: workspace of %lld bytes needed, %lld given",
+                (long long)need, (long long)workspace_bytes);
+  XKB_REQUIRE(reinterpret_cast<uintptr_t>(workspace) % 256 == 0, "workspace must be 256-byte aligned");
+
+  const int64_t numel = M * top_k;
+  Carver carve(workspace);
+  RoutingBuffers rb = carve_routing(carve, numel, E);
+  float* scratch = carve.take<float>(numel * N);
+  void* tc_ws = carve.take<char>(int4_tc_workspace_bytes(numel, N, K, E));
+
+  const bool tc_fit = int4_tc_supported(a_dtype, M, N, K, E, top_k, group_size);
+  if (path == XKB_PATH_TC && !tc_fit)
+    return fail(XKB_ERR_ARG,
+                "fused_moe_int4_w4a16: shape not supported by the tcgen05 path (needs bf16 A, "
+                "N %% 128 == 0, K %% 256 == 0, group_size 32)");
+  const bool use_tc = (path == XKB_PATH_TC) || (path == XKB_PATH_AUTO && tc_fit);
+  const int block = use_tc ? int4_tc_block(numel, E) : kSimtBlock;
+
+  Routing r = make_routing(rb, numel, E, block);
+  int rc = launch_align(topk_ids, numel, E, block, expert_map, num_map, rb.sorted_ids, rb.expert_ids,
+                        rb.num_post, rb.expert_off, rb.align_ws, rb.align_ws_bytes, stream);
+  if (rc != XKB_OK) return rc;
+  if (use_tc)
+    rc = launch_int4_tc(A, packed, scale, r, topk_w, scratch, N, K, E, top_k, mul_routed_weight, tc_ws,
+                        stream);
+  else
+    rc = launch_int4_simt(A, a_dtype, packed, scale, r, topk_w, scratch, N, K, top_k, group_size,
+                          mul_routed_weight, stream);
+  if (rc != XKB_OK) return rc;
+  return launch_combine(scratch, topk_ids, expert_map, num_map, out, a_dtype, M, top_k, N, stream);
+}
+
+// ---------------------------------------------------------------------------
+// MXFP4
+// ---------------------------------------------------------------------------
+extern "C" int64_t xkb_fused_moe_mxfp4_workspace_bytes(int64_t M, int64_t hidden, int64_t ispp, int E,
+                                                       int top_k) {
+  if (M < 0 || hidden < 0 || ispp < 0 || E < 0 || top_k < 0) return -1;
+  const int64_t numel = M * top_k;
+  int64_t total = routing_bytes(numel, E);
+  total += align_up(numel * hidden * 4, 256);                                 // fp32 partial rows
+  total += align_up(routing_max_pad(numel, E, kMaxBlock) * ispp * 2, 256);    // bf16 activations
+  total += mxfp4_tc_workspace_bytes(numel, hidden, ispp, E);
+  return total + 256;
+}
+
+extern "C" int xkb_fused_moe_mxfp4(const void* A, int a_dtype, const uint8_t* w13,
+                                   const uint8_t* w13_scale, const uint8_t* w2,
+                                   const uint8_t* w2_scale, const int32_t* topk_ids,
+                                   const float* topk_w, const void* b13, const void* b2,
+                                   const int32_t* expert_map, int num_map, void* out, int64_t M,
+                                   int64_t hidden, int64_t ispp, int E, int top_k, float swiglu_limit,
+                                   int mul_routed_weight, int path, void* workspace,
+                                   int64_t workspace_bytes, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  XKB_REQUIRE(a_dtype == XKB_BF16 || a_dtype == XKB_F32, "fused_moe_mxfp4: bad a_dtype %d", a_dtype);
+  XKB_REQUIRE(M >= 0 && hidden >= 0 && ispp >= 0 && E >= 0 && top_k >= 0, "fused_moe_mxfp4: negative dim");
+  XKB_REQUIRE(hidden % 32 == 0 && ispp % 32 == 0,
+              "fused_moe_mxfp4: hidden and ispp must be multiples of the MX block 32 (got %lld, %lld)",
+              (long long)hidden, (long long)ispp);
+  XKB_REQUIRE(path == XKB_PATH_AUTO || path == XKB_PATH_SIMT || path == XKB_PATH_TC,
+              "fused_moe_mxfp4: bad path %d", path);
+  if (M == 0 || hidden == 0) return XKB_OK;
+  XKB_REQUIRE(A && w13 && w13_scale && w2 && w2_scale && topk_ids && out,
+              "fused_moe_mxfp4: null pointer argument");
+  XKB_REQUIRE(topk_w || !mul_routed_weight, "fused_moe_mxfp4: topk_w is null");
+  const int64_t need = xkb_fused_moe_mxfp4_workspace_bytes(M, hidden, ispp, E, top_k);
+  if (workspace == nullptr || workspace_bytes < need)
+    return fail(XKB_ERR_WORKSPACE, "fused_moe_mxfp4: workspace of %lld bytes needed, %lld given",
+                (long long)need, (long long)workspace_bytes);
+  XKB_REQUIRE(reinterpret_cast<uintptr_t>(workspace) % 256 == 0, "workspace must be 256-byte aligned");
+
+  const int64_t numel = M * top_k;
+  Carver carve(workspace);
+  RoutingBuffers rb = carve_routing(carve, numel, E);
+  float* scratch = carve.take<float>(numel * hidden);
+  __nv_bfloat16* act = carve.take<__nv_bfloat16>(routing_max_pad(numel, E, kMaxBlock) * ispp);
+  void* tc_ws = carve.take<char>(mxfp4_tc_workspace_bytes(numel, hidden, ispp, E));
+
+  const bool tc_fit = mxfp4_tc_supported(a_dtype, M, hidden, ispp, E, top_k);
+  if (path == XKB_PATH_TC && !tc_fit)
+    return fail(XKB_ERR_ARG,
+                "fused_moe_mxfp4: shape not supported by the tcgen05 path (needs bf16 A, "
+                "hidden %% 256 == 0, ispp %% 256 == 0)");
+  const bool use_tc = (path == XKB_PATH_TC) || (path == XKB_PATH_AUTO && tc_fit);
+  const int block = use_tc ? mxfp4_tc_block(numel, E) : kSimtBlock;
+
+  Routing r = make_routing(rb, numel, E, block);
+  int rc = launch_align(topk_ids, numel, E, block, expert_map, num_map, rb.sorted_ids, rb.expert_ids,
+                        rb.num_post, rb.expert_off, rb.align_ws, rb.align_ws_bytes, stream);
+  if (rc != XKB_OK) return rc;
+  if (use_tc)
+    rc = launch_mxfp4_tc(A, w13, w13_scale, w2, w2_scale, b13, b2, r, topk_w, act, scratch, hidden,
+                         ispp, E, top_k, swiglu_limit, mul_routed_weight, tc_ws, stream);
+  else
+    rc = launch_mxfp4_simt(A, a_dtype, w13, w13_scale, w2, w2_scale, b13, b2, r, topk_w, act, scratch,
+                           hidden, ispp, top_k, swiglu_limit, mul_routed_weight, stream);
+  if (rc != XKB_OK) return rc;
+  return launch_combine(scratch, topk_ids, expert_map, num_map, out, a_dtype, M, top_k, hidden, stream);
+}

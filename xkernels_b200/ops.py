@@ -1,0 +1,262 @@
+"""Host side of the four ops: argument checks, output allocation, one C-ABI call.
+
+The callables keep the parameter names of the reference backends because the
+reference's ``verify`` harness calls a card as ``fn(**inputs)``
+(src/xkernels/verify.py:213-222 with names from
+src/xkernels/registry/input_gen.py:68-72,84-103,138-159).  PyTorch is used for
+device memory and the current stream only; all arithmetic happens in
+``libxkb200.so``.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+_DT = {torch.bfloat16: _lib.XKB_BF16, torch.float32: _lib.XKB_F32}
+_workspaces: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def _require_cuda(name: str, *tensors) -> torch.device:
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not isinstance(t, torch.Tensor):
+            raise TypeError(f"{name}: expected torch.Tensor, got {type(t).__name__}")
+        if not t.is_cuda:
+            raise RuntimeError(
+                f"{name}: the sm_100a backend needs CUDA tensors (got device {t.device}); "
+                "there is no CPU path"
+            )
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise RuntimeError(f"{name}: tensors live on different devices ({dev} vs {t.device})")
+    return dev
+
+
+def _ptr(t) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def _stream(dev: torch.device) -> int:
+    return torch.cuda.current_stream(dev).cuda_stream
+
+
+def get_workspace(dev: torch.device, nbytes: int, tag: int = 0) -> torch.Tensor:
+    """Grow-only per-device scratch buffer shared by calls on one stream.
+
+    Calls that overlap on different streams of one device must pass distinct
+    ``tag`` values (or serialise): the buffer holds the routing and the fp32
+    partial rows of the call in flight.
+    """
+    key = (dev.index if dev.index is not None else torch.cuda.current_device(), tag)
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(int(nbytes), 1 << 20), dtype=torch.uint8, device=dev)
+        _workspaces[key] = buf
+    return buf
+
+
+def release_workspaces() -> None:
+    _workspaces.clear()
+
+
+# ---------------------------------------------------------------------------
+def moe_align_block_size(topk_ids, block_size, num_experts, truncate=True, workspace=None,
+                         expert_map=None):
+    """Sort/pad routed token-slots into per-expert blocks on the GPU.
+
+    Same contract as ``moe_align_block_size_ref``
+    (src/xkernels/ops/moe/w4a16.py:53-101): returns ``(sorted_token_ids
+    [M*top_k + (E+1)*(block-1)], expert_ids, num_tokens_post_padded [1])``, all
+    int32, bit-exact with the reference including the unused tails.
+    ``truncate=True`` trims ``expert_ids`` to the used blocks and therefore
+    reads ``num_tokens_post_padded`` back (one host sync); ``truncate=False`` is
+    sync-free.  ``expert_map`` gives the expert-parallel form of
+    ``moe_align_block_size_ep`` (w4a16.py:104-155): ``num_experts`` is then the
+    local expert count and non-local slots are dropped.
+    """
+    lib = _lib.load()
+    dev = _require_cuda("moe_align_block_size", topk_ids, expert_map)
+    block_size, num_experts = int(block_size), int(num_experts)
+    if block_size <= 0:
+        raise ValueError("block_size must be > 0")
+    ids = topk_ids.reshape(-1)
+    if ids.dtype != torch.int32:
+        ids = ids.to(torch.int32)
+    ids = ids.contiguous()
+    numel = ids.numel()
+    emap = None
+    if expert_map is not None:
+        emap = expert_map.to(device=dev, dtype=torch.int32).contiguous()
+    max_pad = numel + (num_experts + 1) * (block_size - 1)
+    max_blocks = -(-max_pad // block_size)
+    with torch.cuda.device(dev):
+        sorted_ids = torch.empty(max_pad, dtype=torch.int32, device=dev)
+        expert_ids = torch.empty(max(max_blocks, 1), dtype=torch.int32, device=dev)
+        num_post = torch.empty(1, dtype=torch.int32, device=dev)
+        if max_blocks == 0:
+            expert_ids.zero_()
+        ws_bytes = int(lib.xkb_moe_align_workspace_bytes(numel, num_experts))
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+        _lib.check(
+            lib.xkb_moe_align_block_size(
+                _ptr(ids), numel, num_experts, block_size, _ptr(emap),
+                0 if emap is None else emap.numel(), _ptr(sorted_ids), _ptr(expert_ids),
+                _ptr(num_post), 0, _ptr(ws), ws_bytes, _stream(dev)),
+            "xkb_moe_align_block_size")
+    if truncate:
+        used = int(num_post.item()) // block_size
+        expert_ids = expert_ids[: max(used, 1)]
+    else:
+        expert_ids = expert_ids[: max(max_blocks, 1)] if max_blocks == 0 else expert_ids[:max_blocks]
+    return sorted_ids, expert_ids, num_post
+
+
+# ---------------------------------------------------------------------------
+def moe_sum_reduce(y, w=None, routed_scaling_factor=1.0):
+    """``out[m] = routed_scaling_factor * sum_k w[m,k] * y[m,k,:]`` in fp32, ascending k.
+
+    Reference: ``moe_sum_reduce_ref`` (src/xkernels/ops/moe/sum_reduce.py:20-39).
+    ``y`` is ``[M, top_k, H]`` bf16/fp32, ``w`` ``[M, top_k]`` fp32/bf16 or None;
+    the result has ``y.dtype``.
+    """
+    lib = _lib.load()
+    dev = _require_cuda("moe_sum_reduce", y, w)
+    if y.dim() != 3:
+        raise ValueError("y must be [M, top_k, H]")
+    if y.dtype not in _DT:
+        raise TypeError(f"moe_sum_reduce: unsupported y dtype {y.dtype}")
+    y = y.contiguous()
+    M, top_k, H = y.shape
+    if w is not None:
+        if w.dtype not in _DT:
+            w = w.to(torch.float32)
+        if tuple(w.shape) != (M, top_k):
+            raise ValueError(f"w must be [M, top_k] = [{M}, {top_k}], got {tuple(w.shape)}")
+        w = w.contiguous()
+    with torch.cuda.device(dev):
+        out = torch.empty((M, H), dtype=y.dtype, device=dev)
+        _lib.check(
+            lib.xkb_moe_sum_reduce(_ptr(y), _DT[y.dtype], _ptr(w),
+                                   _lib.XKB_F32 if w is None else _DT[w.dtype], _ptr(out),
+                                   _DT[y.dtype], M, top_k, H, float(routed_scaling_factor),
+                                   _stream(dev)),
+            "xkb_moe_sum_reduce")
+    return out
+
+
+# ---------------------------------------------------------------------------
+def _routing_args(name, topk_ids, topk_w, expert_map, dev, M):
+    if topk_ids.dim() != 2 or topk_ids.shape[0] != M:
+        raise ValueError(f"{name}: topk_ids must be [M, top_k]")
+    ids = topk_ids if topk_ids.dtype == torch.int32 else topk_ids.to(torch.int32)
+    ids = ids.contiguous()
+    tw = topk_w if topk_w.dtype == torch.float32 else topk_w.to(torch.float32)
+    tw = tw.contiguous()
+    if tuple(tw.shape) != tuple(ids.shape):
+        raise ValueError(f"{name}: topk_w shape {tuple(tw.shape)} != topk_ids shape {tuple(ids.shape)}")
+    emap = None
+    if expert_map is not None:
+        emap = expert_map.to(device=dev, dtype=torch.int32).contiguous()
+    return ids, tw, emap
+
+
+def fused_moe_int4_w4a16(A, packed, scale, topk_ids, topk_w, group_size=32, mul_routed_weight=True,
+                         fused_combine=None, expert_map=None, workspace=None, *, path="auto"):
+    """INT4 W4A16 grouped fused-MoE GEMM ``out[m] = sum_j w[m,j] * (A[m] @ W[e_mj]^T)``.
+
+    Signature of the reference backends (src/xkernels/ops/moe/reference.py:22-33,
+    triton/moe_int4_kernel.py:438-449).  ``fused_combine`` and ``workspace`` are
+    accepted for API parity: the combine is always the fixed-order fp32 reduce
+    and scratch memory comes from this package's per-device buffer.
+    ``expert_map`` selects the replicated expert-parallel mode (partial output).
+    ``path``: ``"auto"`` | ``"simt"`` | ``"tc"``.
+    """
+    lib = _lib.load()
+    dev = _require_cuda("fused_moe_int4_w4a16", A, packed, scale, topk_ids, topk_w, expert_map)
+    if A.dtype not in _DT:
+        raise TypeError(f"fused_moe_int4_w4a16: A must be bf16 or fp32, got {A.dtype}")
+    if packed.dtype != torch.int32 or packed.dim() != 3:
+        raise TypeError("fused_moe_int4_w4a16: packed must be int32 [E, N, K//8]")
+    A = A.contiguous()
+    packed = packed.contiguous()
+    M, K = A.shape
+    E, N, kp = packed.shape
+    group_size = int(group_size)
+    if kp * 8 != K:
+        raise ValueError(f"packed last dim {kp} != K//8 = {K // 8}")
+    if scale.dtype != torch.bfloat16:
+        scale = scale.to(torch.bfloat16)
+    scale = scale.contiguous()
+    if tuple(scale.shape) != (E, N, K // group_size):
+        raise ValueError(f"scale must be [E, N, K//group_size] = [{E}, {N}, {K // group_size}]")
+    ids, tw, emap = _routing_args("fused_moe_int4_w4a16", topk_ids, topk_w, expert_map, dev, M)
+    top_k = ids.shape[1]
+    pcode = {"auto": _lib.PATH_AUTO, "simt": _lib.PATH_SIMT, "tc": _lib.PATH_TC}[path]
+    with torch.cuda.device(dev):
+        out = torch.empty((M, N), dtype=A.dtype, device=dev)
+        ws_bytes = int(lib.xkb_fused_moe_int4_w4a16_workspace_bytes(M, N, K, E, top_k, _DT[A.dtype]))
+        ws = get_workspace(dev, ws_bytes)
+        _lib.check(
+            lib.xkb_fused_moe_int4_w4a16(
+                _ptr(A), _DT[A.dtype], _ptr(packed), _ptr(scale), _ptr(ids), _ptr(tw), _ptr(emap),
+                0 if emap is None else emap.numel(), _ptr(out), M, N, K, E, top_k, group_size,
+                1 if mul_routed_weight else 0, pcode, _ptr(ws), ws.numel(), _stream(dev)),
+            "xkb_fused_moe_int4_w4a16")
+    return out
+
+
+def fused_moe_mxfp4(A, w13, w13_scale, w2, w2_scale, topk_ids, topk_w, b13=None, b2=None,
+                    swiglu_limit=10.0, group_size=32, mul_routed_weight=True, expert_map=None,
+                    workspace=None, *, path="auto"):
+    """MXFP4 fused MoE: gate_up GEMM -> clamped SwiGLU -> down GEMM -> weighted combine.
+
+    Signature of the reference backends
+    (src/xkernels/ops/moe/mxfp4_reference.py:28-43, triton/moe_mxfp4_kernel.py:487-502).
+    ``w13`` ``[E, 2*ispp, hidden//2]`` and ``w2`` ``[E, hidden, ispp//2]`` are uint8
+    E2M1 pairs, the scales uint8 e8m0 per 32 elements.  The three bf16 rounding
+    points of the reference (gate_up, activation, down) are reproduced.
+    """
+    lib = _lib.load()
+    dev = _require_cuda("fused_moe_mxfp4", A, w13, w13_scale, w2, w2_scale, topk_ids, topk_w, b13, b2,
+                        expert_map)
+    if int(group_size) != 32:
+        raise ValueError("fused_moe_mxfp4: the MX block size is 32")
+    if A.dtype not in _DT:
+        raise TypeError(f"fused_moe_mxfp4: A must be bf16 or fp32, got {A.dtype}")
+    for name, t in (("w13", w13), ("w13_scale", w13_scale), ("w2", w2), ("w2_scale", w2_scale)):
+        if t.dtype != torch.uint8:
+            raise TypeError(f"fused_moe_mxfp4: {name} must be uint8")
+    A = A.contiguous()
+    w13, w13_scale, w2, w2_scale = (t.contiguous() for t in (w13, w13_scale, w2, w2_scale))
+    M, hidden = A.shape
+    E, two_ispp, half_hidden = w13.shape
+    ispp = two_ispp // 2
+    if half_hidden * 2 != hidden or tuple(w2.shape) != (E, hidden, ispp // 2):
+        raise ValueError("fused_moe_mxfp4: w13 must be [E, 2*ispp, hidden//2] and w2 [E, hidden, ispp//2]")
+    if tuple(w13_scale.shape) != (E, 2 * ispp, hidden // 32) or tuple(w2_scale.shape) != (E, hidden, ispp // 32):
+        raise ValueError("fused_moe_mxfp4: scale shapes must be [E,2*ispp,hidden//32] and [E,hidden,ispp//32]")
+    if b13 is not None:
+        b13 = b13.to(torch.bfloat16).contiguous()
+    if b2 is not None:
+        b2 = b2.to(torch.bfloat16).contiguous()
+    ids, tw, emap = _routing_args("fused_moe_mxfp4", topk_ids, topk_w, expert_map, dev, M)
+    top_k = ids.shape[1]
+    limit = 0.0 if swiglu_limit is None else float(swiglu_limit)
+    pcode = {"auto": _lib.PATH_AUTO, "simt": _lib.PATH_SIMT, "tc": _lib.PATH_TC}[path]
+    with torch.cuda.device(dev):
+        out = torch.empty((M, hidden), dtype=A.dtype, device=dev)
+        ws_bytes = int(lib.xkb_fused_moe_mxfp4_workspace_bytes(M, hidden, ispp, E, top_k))
+        ws = get_workspace(dev, ws_bytes)
+        _lib.check(
+            lib.xkb_fused_moe_mxfp4(
+                _ptr(A), _DT[A.dtype], _ptr(w13), _ptr(w13_scale), _ptr(w2), _ptr(w2_scale), _ptr(ids),
+                _ptr(tw), _ptr(b13), _ptr(b2), _ptr(emap), 0 if emap is None else emap.numel(),
+                _ptr(out), M, hidden, ispp, E, top_k, limit, 1 if mul_routed_weight else 0, pcode,
+                _ptr(ws), ws.numel(), _stream(dev)),
+            "xkb_fused_moe_mxfp4")
+    return out
