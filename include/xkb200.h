@@ -124,6 +124,15 @@ int xkb_fused_moe_mxfp4(const void* A, int a_dtype, const uint8_t* w13,
                         int path, void* workspace, int64_t workspace_bytes,
                         void* stream);
 
+/* ------------------------------------------------------------------------
+ * Device status of the last fused call that used `workspace`: synchronises
+ * `stream`, reads the status word in the workspace header and returns
+ * XKB_ERR_DEVICE if a tcgen05 kernel gave up one of its bounded waits.
+ * The reference reports kernel failures as Python exceptions raised by the
+ * launch (src/xkernels/_dispatch.py:204-240); this is the explicit query.
+ * ---------------------------------------------------------------------- */
+int xkb_workspace_status(const void* workspace, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -31,6 +31,38 @@ def test_golden(name, path, cuda_device):
     assert_within(out, c["out"], *TOL[c["A"].dtype], what=f"{name}/{path}")
 
 
+@pytest.mark.parametrize("M,K,N,E,top_k,tile", [
+    (16, 512, 256, 8, 2, 16),      # the tiny configuration: 4 tokens per expert
+    (64, 256, 128, 4, 2, 32),      # 32 slots per expert on average -> 64-token tile
+    (40, 768, 384, 8, 4, 32),      # 20 per expert -> 32-token tile
+    (96, 1024, 256, 6, 4, 64),     # 64 per expert -> 128-token tile
+    (300, 512, 128, 3, 2, 256),    # 200 per expert -> 256-token tile
+    (7, 7168, 256, 48, 8, 16),     # decode-like K, mostly empty experts
+])
+def test_tensor_core_path_against_oracle(M, K, N, E, top_k, tile, cuda_device):
+    """The tcgen05 kernel at every token-tile size it is instantiated for."""
+    from xkernels_b200 import ops
+
+    g = torch.Generator().manual_seed(M + K + N)
+    A = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    packed, scale = synth.int4_weights(E, N, K, 32, seed=M, device="cpu")
+    ids, w = synth.routing(M, E, top_k, seed=K, device="cpu")
+    want = oracle.moe_w4a16(A, packed, scale, ids, w, 32)
+    c = {"A": A, "packed": packed, "scale": scale, "topk_ids": ids, "topk_w": w}
+    got = call(c, cuda_device, path="tc")
+    ops.check_status(cuda_device)
+    assert_within(got, want, *TOL[torch.bfloat16], what=f"tc tile~{tile}")
+    simt = call(c, cuda_device, path="simt")
+    assert_within(got, simt, 1e-2, 1e-2, what="tc vs simt")
+    assert torch.equal(got, call(c, cuda_device, path="tc"))
+
+
+def test_tensor_core_path_refuses_unfit_shapes(cuda_device):
+    c = load_case("int4_sweep2")  # K=96, N=48
+    with pytest.raises(RuntimeError, match="tcgen05"):
+        call(c, cuda_device, path="tc")
+
+
 def test_golden_no_routed_weight(cuda_device):
     c = load_case("int4_tiny")
     out = call(c, cuda_device, mul_routed_weight=False)

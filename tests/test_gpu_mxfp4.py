@@ -59,6 +59,7 @@ def test_expert_parallel_partials_sum_to_dense(cuda_device):
     dense = call(c, cuda_device, swiglu_limit=10.0).float().cpu()
     E = c["w13"].shape[0]
     total = torch.zeros_like(dense)
+    mags = torch.zeros_like(dense)
     for rank in range(2):
         emap = torch.full((E,), -1, dtype=torch.int32)
         lo, hi = rank * E // 2, (rank + 1) * E // 2
@@ -73,7 +74,11 @@ def test_expert_parallel_partials_sum_to_dense(cuda_device):
                                 b2=c["b2"][lo:hi], expert_map=emap)
         assert_within(part, want, RTOL, ATOL, what=f"partial {rank}", allowed=max(1, want.numel() // 2000))
         total += part.float().cpu()
-    assert_within(total, dense, 3e-2, 3e-2, what="sum of partials")
+        mags += part.float().cpu().abs()
+    # each partial is rounded to bf16 on its own, so the sum carries up to half a bf16 ulp of
+    # every partial: allow 2^-8 of the partials' magnitudes on top of the op tolerance
+    slack = 3e-2 + 3e-2 * dense.abs() + 2.0 ** -8 * mags
+    assert bool(((total - dense).abs() <= slack).all()), "sum of partials differs from the dense result"
 
 
 def test_decode_config_full(cuda_device):

@@ -45,6 +45,7 @@ SIGNATURES = {
          c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_float,
          c_int, c_int, c_void_p, c_int64, c_void_p],
     ),
+    "xkb_workspace_status": (c_int, [c_void_p, c_void_p]),
 }
 
 _lib = None

@@ -25,6 +25,7 @@ int fail(int code, const char* fmt, ...) {
 namespace {
 
 struct RoutingBuffers {
+  int* status;
   int32_t* sorted_ids;
   int32_t* expert_ids;
   int32_t* num_post;
@@ -45,6 +46,7 @@ int64_t routing_max_pad(int64_t numel, int E, int block) {
 
 RoutingBuffers carve_routing(Carver& c, int64_t numel, int E) {
   RoutingBuffers r;
+  r.status = c.take<int>(64);  // workspace header: word 0 = device status of the last call
   r.sorted_ids = c.take<int32_t>(routing_max_pad(numel, E, kMaxBlock));
   r.expert_ids = c.take<int32_t>(ceil_div(routing_max_pad(numel, E, kMinBlock), kMinBlock) + 1);
   r.num_post = c.take<int32_t>(1);
@@ -134,12 +136,13 @@ extern "C" int xkb_fused_moe_int4_w4a16(const void* A, int a_dtype, const int32_
   const int block = use_tc ? int4_tc_block(numel, E) : kSimtBlock;
 
   Routing r = make_routing(rb, numel, E, block);
+  XKB_CHECK_CUDA(cudaMemsetAsync(rb.status, 0, sizeof(int), stream));
   int rc = launch_align(topk_ids, numel, E, block, expert_map, num_map, rb.sorted_ids, rb.expert_ids,
                         rb.num_post, rb.expert_off, rb.align_ws, rb.align_ws_bytes, stream);
   if (rc != XKB_OK) return rc;
   if (use_tc)
     rc = launch_int4_tc(A, packed, scale, r, topk_w, scratch, N, K, E, top_k, mul_routed_weight, tc_ws,
-                        stream);
+                        rb.status, stream);
   else
     rc = launch_int4_simt(A, a_dtype, packed, scale, r, topk_w, scratch, N, K, top_k, group_size,
                           mul_routed_weight, stream);
@@ -203,15 +206,28 @@ extern "C" int xkb_fused_moe_mxfp4(const void* A, int a_dtype, const uint8_t* w1
   const int block = use_tc ? mxfp4_tc_block(numel, E) : kSimtBlock;
 
   Routing r = make_routing(rb, numel, E, block);
+  XKB_CHECK_CUDA(cudaMemsetAsync(rb.status, 0, sizeof(int), stream));
   int rc = launch_align(topk_ids, numel, E, block, expert_map, num_map, rb.sorted_ids, rb.expert_ids,
                         rb.num_post, rb.expert_off, rb.align_ws, rb.align_ws_bytes, stream);
   if (rc != XKB_OK) return rc;
   if (use_tc)
     rc = launch_mxfp4_tc(A, w13, w13_scale, w2, w2_scale, b13, b2, r, topk_w, act, scratch, hidden,
-                         ispp, E, top_k, swiglu_limit, mul_routed_weight, tc_ws, stream);
+                         ispp, E, top_k, swiglu_limit, mul_routed_weight, tc_ws, rb.status, stream);
   else
     rc = launch_mxfp4_simt(A, a_dtype, w13, w13_scale, w2, w2_scale, b13, b2, r, topk_w, act, scratch,
                            hidden, ispp, top_k, swiglu_limit, mul_routed_weight, stream);
   if (rc != XKB_OK) return rc;
   return launch_combine(scratch, topk_ids, expert_map, num_map, out, a_dtype, M, top_k, hidden, stream);
+}
+
+// ---------------------------------------------------------------------------
+extern "C" int xkb_workspace_status(const void* workspace, void* stream_) {
+  XKB_REQUIRE(workspace != nullptr, "xkb_workspace_status: null workspace");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  int host = 0;
+  XKB_CHECK_CUDA(cudaMemcpyAsync(&host, workspace, sizeof(int), cudaMemcpyDeviceToHost, stream));
+  XKB_CHECK_CUDA(cudaStreamSynchronize(stream));
+  if (host != 0)
+    return fail(XKB_ERR_DEVICE, "a kernel gave up a bounded wait: status 0x%x (wait site %d)", host, host >> 8);
+  return XKB_OK;
 }

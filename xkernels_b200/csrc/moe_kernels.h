@@ -22,7 +22,7 @@ int int4_tc_block(int64_t numel, int E);
 int64_t int4_tc_workspace_bytes(int64_t numel, int64_t N, int64_t K, int E);
 int launch_int4_tc(const void* A, const int32_t* packed, const void* scale, const Routing& r,
                    const float* topk_w, float* scratch, int64_t N, int64_t K, int E, int top_k,
-                   int mul_w, void* tc_ws, cudaStream_t stream);
+                   int mul_w, void* tc_ws, int* status, cudaStream_t stream);
 
 bool mxfp4_tc_supported(int a_dtype, int64_t M, int64_t hidden, int64_t ispp, int E, int top_k);
 int mxfp4_tc_block(int64_t numel, int E);
@@ -30,7 +30,7 @@ int64_t mxfp4_tc_workspace_bytes(int64_t numel, int64_t hidden, int64_t ispp, in
 int launch_mxfp4_tc(const void* A, const uint8_t* w13, const uint8_t* w13_scale, const uint8_t* w2,
                     const uint8_t* w2_scale, const void* b13, const void* b2, const Routing& r,
                     const float* topk_w, __nv_bfloat16* act, float* scratch, int64_t hidden,
-                    int64_t ispp, int E, int top_k, float limit, int mul_w, void* tc_ws,
+                    int64_t ispp, int E, int top_k, float limit, int mul_w, void* tc_ws, int* status,
                     cudaStream_t stream);
 
 }  // namespace xkb

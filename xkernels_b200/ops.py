@@ -60,6 +60,18 @@ def get_workspace(dev: torch.device, nbytes: int, tag: int = 0) -> torch.Tensor:
     return buf
 
 
+def check_status(dev=None, tag: int = 0) -> None:
+    """Synchronise and raise if a kernel of the last fused call on ``dev`` gave up a bounded
+    wait (the tcgen05 kernels never spin without a limit; they record a status word instead)."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if dev is None else torch.device(dev)
+    key = (dev.index if dev.index is not None else torch.cuda.current_device(), tag)
+    buf = _workspaces.get(key)
+    if buf is None:
+        return
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().xkb_workspace_status(buf.data_ptr(), _stream(dev)), "xkb_workspace_status")
+
+
 def release_workspaces() -> None:
     _workspaces.clear()
 
