@@ -133,6 +133,19 @@ int xkb_fused_moe_mxfp4(const void* A, int a_dtype, const uint8_t* w13,
  * ---------------------------------------------------------------------- */
 int xkb_workspace_status(const void* workspace, void* stream);
 
+/* ------------------------------------------------------------------------
+ * Measurement support: time the expert-GEMM kernel(s) of each fused call with
+ * CUDA events recorded on the caller's stream around their launch.
+ * `xkb_gemm_timer_enable(n)` arms n event pairs (0 disarms); each fused call
+ * then uses the next pair; `xkb_gemm_timer_read` waits for the recorded
+ * pairs, writes their durations in milliseconds to the HOST array and re-arms.
+ * The reference times whole ops from Python
+ * (src/xkernels/utils/benchmarking.py:68-141); per-kernel timing is new here.
+ * Not thread-safe: arm, run and read from one thread.
+ * ---------------------------------------------------------------------- */
+int xkb_gemm_timer_enable(int max_calls);
+int xkb_gemm_timer_read(float* ms_host, int capacity, int* count_host);
+
 #ifdef __cplusplus
 }
 #endif

@@ -46,6 +46,8 @@ SIGNATURES = {
          c_int, c_int, c_void_p, c_int64, c_void_p],
     ),
     "xkb_workspace_status": (c_int, [c_void_p, c_void_p]),
+    "xkb_gemm_timer_enable": (c_int, [c_int]),
+    "xkb_gemm_timer_read": (c_int, [c_void_p, c_int, c_void_p]),
 }
 
 _lib = None
@@ -82,3 +84,15 @@ def check(status: int, what: str) -> None:
 
 def launch_count() -> int:
     return int(load().xkb_launch_count())
+
+
+def gemm_timer_enable(max_calls: int) -> None:
+    check(load().xkb_gemm_timer_enable(int(max_calls)), "xkb_gemm_timer_enable")
+
+
+def gemm_timer_read(capacity: int = 1 << 16) -> list[float]:
+    """Durations (ms) of the expert-GEMM launches of the fused calls made since arming."""
+    buf = (ctypes.c_float * capacity)()
+    n = ctypes.c_int(0)
+    check(load().xkb_gemm_timer_read(buf, capacity, ctypes.byref(n)), "xkb_gemm_timer_read")
+    return [float(buf[i]) for i in range(n.value)]

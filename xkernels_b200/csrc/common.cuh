@@ -86,6 +86,15 @@ int launch_combine(const float* scratch, const int32_t* topk_ids, const int32_t*
                    int num_map, void* out, int out_dtype, int64_t M, int top_k, int64_t N,
                    cudaStream_t stream);
 
+// Records one event pair of the optional GEMM timer (xkb_gemm_timer_enable) around
+// the launches made while it is alive; does nothing when the timer is not armed.
+struct GemmTimerScope {
+  cudaStream_t stream;
+  int slot;
+  explicit GemmTimerScope(cudaStream_t s);
+  ~GemmTimerScope();
+};
+
 // ---- device helpers --------------------------------------------------------
 #ifdef __CUDACC__
 __device__ __forceinline__ float bf16_bits_to_float(uint32_t bits16) {

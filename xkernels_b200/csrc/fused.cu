@@ -5,6 +5,8 @@
 #include "common.cuh"
 #include "moe_kernels.h"
 
+#include <vector>
+
 namespace xkb {
 
 std::atomic<int64_t> g_launches{0};
@@ -20,6 +22,26 @@ int fail(int code, const char* fmt, ...) {
   vsnprintf(last_error_buf(), 512, fmt, ap);
   va_end(ap);
   return code;
+}
+
+// ---- optional per-call timing of the grouped-GEMM kernel(s) -----------------
+// A ring of event pairs; when enabled, every fused call records one pair around
+// its expert GEMM launch(es) on the caller's stream.
+struct GemmTimer {
+  std::vector<cudaEvent_t> start, stop;
+  int used = 0;
+  bool enabled = false;
+};
+static GemmTimer g_timer;
+
+GemmTimerScope::GemmTimerScope(cudaStream_t s) : stream(s), slot(-1) {
+  if (g_timer.enabled && g_timer.used < (int)g_timer.start.size()) {
+    slot = g_timer.used++;
+    cudaEventRecord(g_timer.start[slot], stream);
+  }
+}
+GemmTimerScope::~GemmTimerScope() {
+  if (slot >= 0) cudaEventRecord(g_timer.stop[slot], stream);
 }
 
 namespace {
@@ -229,5 +251,36 @@ extern "C" int xkb_workspace_status(const void* workspace, void* stream_) {
   XKB_CHECK_CUDA(cudaStreamSynchronize(stream));
   if (host != 0)
     return fail(XKB_ERR_DEVICE, "a kernel gave up a bounded wait: status 0x%x (wait site %d)", host, host >> 8);
+  return XKB_OK;
+}
+
+// ---------------------------------------------------------------------------
+extern "C" int xkb_gemm_timer_enable(int max_calls) {
+  XKB_REQUIRE(max_calls >= 0 && max_calls <= (1 << 16), "xkb_gemm_timer_enable: max_calls out of range");
+  for (auto e : g_timer.start) cudaEventDestroy(e);
+  for (auto e : g_timer.stop) cudaEventDestroy(e);
+  g_timer.start.clear();
+  g_timer.stop.clear();
+  g_timer.used = 0;
+  g_timer.enabled = max_calls > 0;
+  for (int i = 0; i < max_calls; ++i) {
+    cudaEvent_t a, b;
+    XKB_CHECK_CUDA(cudaEventCreate(&a));
+    XKB_CHECK_CUDA(cudaEventCreate(&b));
+    g_timer.start.push_back(a);
+    g_timer.stop.push_back(b);
+  }
+  return XKB_OK;
+}
+
+extern "C" int xkb_gemm_timer_read(float* ms_host, int capacity, int* count_host) {
+  XKB_REQUIRE(ms_host != nullptr && count_host != nullptr, "xkb_gemm_timer_read: null output");
+  const int n = g_timer.used < capacity ? g_timer.used : capacity;
+  for (int i = 0; i < n; ++i) {
+    XKB_CHECK_CUDA(cudaEventSynchronize(g_timer.stop[i]));
+    XKB_CHECK_CUDA(cudaEventElapsedTime(&ms_host[i], g_timer.start[i], g_timer.stop[i]));
+  }
+  *count_host = n;
+  g_timer.used = 0;
   return XKB_OK;
 }

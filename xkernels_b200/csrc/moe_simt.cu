@@ -281,6 +281,7 @@ int launch_int4_simt(const void* A, int a_dtype, const int32_t* packed, const vo
   XKB_REQUIRE(r.max_blocks <= 65535 * 32, "too many routing blocks for one launch");
   dim3 grid((unsigned)ceil_div(N, kSimtBN), (unsigned)r.max_blocks);
   XKB_REQUIRE(grid.y <= 65535u, "routing has %u blocks; the SIMT path supports at most 65535", grid.y);
+  GemmTimerScope timed(stream);
   if (a_dtype == XKB_BF16)
     int4_simt_kernel<__nv_bfloat16><<<grid, kSimtBN, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(A), packed, static_cast<const __nv_bfloat16*>(scale),
@@ -303,6 +304,7 @@ int launch_mxfp4_simt(const void* A, int a_dtype, const uint8_t* w13, const uint
   XKB_REQUIRE(r.max_blocks <= 65535, "routing has %lld blocks; the SIMT path supports at most 65535",
               (long long)r.max_blocks);
   dim3 g0((unsigned)ceil_div(ispp, kSimtBN), (unsigned)r.max_blocks);
+  GemmTimerScope timed(stream);
   if (a_dtype == XKB_BF16)
     mxfp4_stage0_simt_kernel<__nv_bfloat16><<<g0, kSimtBN, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(A), w13, w13_scale, static_cast<const __nv_bfloat16*>(b13),

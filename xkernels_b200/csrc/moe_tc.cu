@@ -348,7 +348,10 @@ int launch_bt(const CUtensorMap& tmp, const CUtensorMap& tms, const CUtensorMap&
   int64_t grid = (int64_t)sms * per_sm;
   if (grid > max_tiles) grid = max_tiles;
   if (grid < 1) grid = 1;
-  int4_tc_kernel<BT><<<(unsigned)grid, kThreads, Cfg::kSmemBytes, stream>>>(tmp, tms, tmt, prm);
+  {
+    GemmTimerScope timed(stream);
+    int4_tc_kernel<BT><<<(unsigned)grid, kThreads, Cfg::kSmemBytes, stream>>>(tmp, tms, tmt, prm);
+  }
   XKB_CHECK_LAUNCH("int4_tc_kernel");
   return XKB_OK;
 }
