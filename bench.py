@@ -461,6 +461,36 @@ def run_multi_gpu(args, world: int, rank: int, local_rank: int):
     dist.destroy_process_group()
 
 
+PROFILE_CASES = {
+    # small relatives of the benchmark configurations (weights still exceed the 126 MB L2) for
+    # ncu captures: few launches, a few hundred MB on the device
+    "int4_decode_small": ("int4", dict(M=22, K=7168, N=4096, E=16, top_k=8)),
+    "int4_prefill_small": ("int4", dict(M=2048, K=7168, N=4096, E=16, top_k=8, expert_bias_std=0.5)),
+    "mxfp4_decode_small": ("mxfp4", dict(M=12, hidden=4096, ispp=512, E=64, top_k=6)),
+}
+
+
+def run_profile_case(args):
+    """One small case, a handful of calls, no extras: the command ncu wraps."""
+    import xkernels_b200 as xkb
+    from xkernels_b200 import ops, synth
+
+    dev = torch.device("cuda", 0)
+    kind, kw = PROFILE_CASES[args.case]
+    if kind == "int4":
+        cfg = synth.Int4Config(args.case, **kw)
+        d = synth.make_int4(cfg, seed=1729, device=dev)
+        fn = lambda: xkb.fused_moe_int4_w4a16(d["A"], d["packed"], d["scale"], d["topk_ids"], d["topk_w"])  # noqa: E731
+    else:
+        cfg = synth.Mxfp4Config(args.case, **kw)
+        d = synth.make_mxfp4(cfg, seed=1729, device=dev)
+        fn = lambda: xkb.fused_moe_mxfp4(d["A"], d["w13"], d["w13_scale"], d["w2"], d["w2_scale"],  # noqa: E731
+                                         d["topk_ids"], d["topk_w"])
+    ms = time_call(fn, args.warmup, args.steps)
+    ops.check_status(dev)
+    print(json.dumps({"case": args.case, "config": kw, "us_per_call": ms * 1e3, "steps": args.steps}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -469,10 +499,17 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the other single-GPU configurations")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    ap.add_argument("--case", default=None, choices=sorted(PROFILE_CASES),
+                    help="run one small profiling case instead of the benchmark")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.case is not None:
+        if args.steps == 200:
+            args.steps = 3
+        run_profile_case(args)
+        return
     if args.impl == "reference":
         if args.steps == 200:
             args.steps = 3

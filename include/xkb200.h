@@ -104,6 +104,31 @@ int xkb_fused_moe_int4_w4a16(const void* A, int a_dtype, const int32_t* packed,
                              int64_t workspace_bytes, void* stream);
 
 /* ------------------------------------------------------------------------
+ * Expert-parallel building blocks (all-to-all mode).  The reference has no
+ * all-to-all; its expert-parallel contract is "per-rank partials sum to the
+ * dense result" (tests/test_moe_int4_ep.py:152-177).  These two calls are the
+ * local halves around the NCCL exchanges:
+ *
+ * xkb_moe_int4_w4a16_rows: as xkb_fused_moe_int4_w4a16 but WITHOUT the top-k
+ *   combine: rows_out [M*top_k, N] fp32, row = token*top_k + j (the grouped
+ *   GEMM stage of triton/moe_int4_kernel.py:550-577 before its `.sum(1)`).
+ *   Same workspace size as the fused call.
+ * xkb_moe_gather_sum_reduce: out[m,:] = sum_k w[m,k] * rows[row_index[m,k],:]
+ *   in fp32, ascending k (row_index < 0 skips); the combine of
+ *   ops/moe/reference.py:59-69 over rows that came back in exchange order.
+ * ---------------------------------------------------------------------- */
+int xkb_moe_int4_w4a16_rows(const void* A, int a_dtype, const int32_t* packed,
+                            const void* scale, const int32_t* topk_ids,
+                            const float* topk_w, float* rows_out, int64_t M,
+                            int64_t N, int64_t K, int E, int top_k,
+                            int group_size, int mul_routed_weight, int path,
+                            void* workspace, int64_t workspace_bytes,
+                            void* stream);
+int xkb_moe_gather_sum_reduce(const float* rows, const int32_t* row_index,
+                              const float* w, void* out, int out_dtype,
+                              int64_t M, int top_k, int64_t H, void* stream);
+
+/* ------------------------------------------------------------------------
  * fused_moe_mxfp4: gate_up GEMM -> clamped SwiGLU -> down GEMM -> combine
  * Replaces: src/xkernels/ops/moe/mxfp4_reference.py:28-112 (moe_mxfp4_ref)
  *           and src/xkernels/ops/moe/triton/moe_mxfp4_kernel.py:487-568.

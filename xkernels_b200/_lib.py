@@ -11,7 +11,10 @@ import ctypes
 from ctypes import c_char_p, c_float, c_int, c_int64, c_void_p
 from pathlib import Path
 
-LIB_PATH = Path(__file__).resolve().parent / "libxkb200.so"
+import os
+
+# XKB200_LIB points at an alternative build of the library (e.g. an instrumented one).
+LIB_PATH = Path(os.environ.get("XKB200_LIB") or Path(__file__).resolve().parent / "libxkb200.so")
 
 XKB_BF16 = 0
 XKB_F32 = 1
@@ -38,6 +41,13 @@ SIGNATURES = {
         [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
          c_int64, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int64, c_void_p],
     ),
+    "xkb_moe_int4_w4a16_rows": (
+        c_int,
+        [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
+         c_int, c_int, c_int, c_int, c_int, c_void_p, c_int64, c_void_p],
+    ),
+    "xkb_moe_gather_sum_reduce": (
+        c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_int64, c_void_p]),
     "xkb_fused_moe_mxfp4_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64, c_int, c_int]),
     "xkb_fused_moe_mxfp4": (
         c_int,

@@ -120,13 +120,13 @@ extern "C" int64_t xkb_fused_moe_int4_w4a16_workspace_bytes(int64_t M, int64_t N
   return total + 256;
 }
 
-extern "C" int xkb_fused_moe_int4_w4a16(const void* A, int a_dtype, const int32_t* packed,
-                                        const void* scale, const int32_t* topk_ids,
-                                        const float* topk_w, const int32_t* expert_map, int num_map,
-                                        void* out, int64_t M, int64_t N, int64_t K, int E, int top_k,
-                                        int group_size, int mul_routed_weight, int path,
-                                        void* workspace, int64_t workspace_bytes, void* stream_) {
-  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+// rows_out == nullptr: combine into `out` ([M,N], a_dtype).  rows_out != nullptr: leave the fp32
+// per-slot rows ([M*top_k, N], row = token*top_k + j) there and skip the combine.
+static int int4_impl(const void* A, int a_dtype, const int32_t* packed, const void* scale,
+                     const int32_t* topk_ids, const float* topk_w, const int32_t* expert_map,
+                     int num_map, void* out, float* rows_out, int64_t M, int64_t N, int64_t K, int E,
+                     int top_k, int group_size, int mul_routed_weight, int path, void* workspace,
+                     int64_t workspace_bytes, cudaStream_t stream) {
   XKB_REQUIRE(a_dtype == XKB_BF16 || a_dtype == XKB_F32, "fused_moe_int4_w4a16: bad a_dtype %d", a_dtype);
   XKB_REQUIRE(M >= 0 && N >= 0 && K >= 0 && E >= 0 && top_k >= 0, "fused_moe_int4_w4a16: negative dim");
   XKB_REQUIRE(group_size > 0 && group_size % 8 == 0 && K % group_size == 0 && K % 8 == 0,
@@ -135,7 +135,8 @@ extern "C" int xkb_fused_moe_int4_w4a16(const void* A, int a_dtype, const int32_
   XKB_REQUIRE(path == XKB_PATH_AUTO || path == XKB_PATH_SIMT || path == XKB_PATH_TC,
               "fused_moe_int4_w4a16: bad path %d", path);
   if (M == 0 || N == 0) return XKB_OK;
-  XKB_REQUIRE(A && packed && scale && topk_ids && out, "fused_moe_int4_w4a16: null pointer argument");
+  XKB_REQUIRE(A && packed && scale && topk_ids && (out || rows_out),
+              "fused_moe_int4_w4a16: null pointer argument");
   XKB_REQUIRE(topk_w || !mul_routed_weight, "fused_moe_int4_w4a16: topk_w is null");
   const int64_t need = xkb_fused_moe_int4_w4a16_workspace_bytes(M, N, K, E, top_k, a_dtype);
   if (workspace == nullptr || workspace_bytes < need)
@@ -147,6 +148,7 @@ extern "C" int xkb_fused_moe_int4_w4a16(const void* A, int a_dtype, const int32_
   Carver carve(workspace);
   RoutingBuffers rb = carve_routing(carve, numel, E);
   float* scratch = carve.take<float>(numel * N);
+  if (rows_out != nullptr) scratch = rows_out;
   void* tc_ws = carve.take<char>(int4_tc_workspace_bytes(numel, N, K, E));
 
   const bool tc_fit = int4_tc_supported(a_dtype, M, N, K, E, top_k, group_size);
@@ -169,7 +171,31 @@ extern "C" int xkb_fused_moe_int4_w4a16(const void* A, int a_dtype, const int32_
     rc = launch_int4_simt(A, a_dtype, packed, scale, r, topk_w, scratch, N, K, top_k, group_size,
                           mul_routed_weight, stream);
   if (rc != XKB_OK) return rc;
+  if (rows_out != nullptr) return XKB_OK;
   return launch_combine(scratch, topk_ids, expert_map, num_map, out, a_dtype, M, top_k, N, stream);
+}
+
+extern "C" int xkb_fused_moe_int4_w4a16(const void* A, int a_dtype, const int32_t* packed,
+                                        const void* scale, const int32_t* topk_ids,
+                                        const float* topk_w, const int32_t* expert_map, int num_map,
+                                        void* out, int64_t M, int64_t N, int64_t K, int E, int top_k,
+                                        int group_size, int mul_routed_weight, int path,
+                                        void* workspace, int64_t workspace_bytes, void* stream) {
+  XKB_REQUIRE(out != nullptr || M == 0 || N == 0, "fused_moe_int4_w4a16: null out");
+  return int4_impl(A, a_dtype, packed, scale, topk_ids, topk_w, expert_map, num_map, out, nullptr, M, N,
+                   K, E, top_k, group_size, mul_routed_weight, path, workspace, workspace_bytes,
+                   static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int xkb_moe_int4_w4a16_rows(const void* A, int a_dtype, const int32_t* packed,
+                                       const void* scale, const int32_t* topk_ids, const float* topk_w,
+                                       float* rows_out, int64_t M, int64_t N, int64_t K, int E,
+                                       int top_k, int group_size, int mul_routed_weight, int path,
+                                       void* workspace, int64_t workspace_bytes, void* stream) {
+  XKB_REQUIRE(rows_out != nullptr || M == 0 || N == 0, "moe_int4_w4a16_rows: null rows_out");
+  return int4_impl(A, a_dtype, packed, scale, topk_ids, topk_w, nullptr, 0, nullptr, rows_out, M, N, K,
+                   E, top_k, group_size, mul_routed_weight, path, workspace, workspace_bytes,
+                   static_cast<cudaStream_t>(stream));
 }
 
 // ---------------------------------------------------------------------------

@@ -4,17 +4,18 @@
 // weight rows per CTA tile) and the routed tokens the "B" operand (N = BT
 // tokens of one expert block), so a decode batch with a handful of tokens per
 // expert still fills the 128-row datapath and the kernel's cost is the weight
-// stream.  Per CTA, eight warps:
+// stream.  Per CTA, twelve warps:
 //
 //   warp 0   TMA producer, weights: packed int32 tile [128 rows x 128 B] (128B
 //            swizzle, so that one row per thread reads conflict-free) + bf16
 //            scale tile [128 x 8] per 256-wide K stage.
 //   warp 1   TMA producer, tokens: [BT x 64] bf16 tiles (128B swizzle = the UMMA
 //            K-major canonical layout) from the gathered activation buffer.
-//   warp 2   MMA issuer: tcgen05.mma kind::f16, A from tensor memory, B from
-//            shared memory, fp32 accumulators in tensor memory.
-//   warp 3   tensor-memory allocation / release.
-//   warps 4-7 dequantisers: thread = weight row; nibbles -> exact bf16 integers
+//            It also allocates and releases tensor memory.
+//   warps 2-3 MMA issuers: tcgen05.mma kind::f16, A from tensor memory, B from
+//            shared memory, fp32 accumulators in tensor memory (two issuers with
+//            one accumulator each for token tiles <= 64, one issuer above).
+//   warps 4-11 dequantisers: thread = weight row; nibbles -> exact bf16 integers
 //            by the 0x4300|nib trick, minus 136, times the group scale in one
 //            bf16 multiply (= the reference's single rounding,
 //            src/xkernels/ops/moe/w4a16.py:44-50), written to tensor memory with
@@ -40,22 +41,58 @@ constexpr int kTileRows = 128;   // weight rows per tile (UMMA M)
 constexpr int kStageK = 256;     // K per weight pipeline stage
 constexpr int kSubK = 64;        // K per token stage / tensor-memory A slot
 constexpr int kSubs = kStageK / kSubK;
-constexpr int kASlots = 4;       // tensor-memory A ring
-constexpr int kAColsPerSlot = kSubK / 2;               // 32 columns of bf16 pairs
-constexpr int kDCol0 = kASlots * kAColsPerSlot;        // accumulators start at column 128
+constexpr int kAColsPerSlot = kSubK / 2;               // 32 columns of bf16 pairs per A slot
 constexpr int kWStages = 4;
-constexpr int kThreads = 256;
+constexpr int kCtrlWarps = 6;      // weight producer, token producer, up to four MMA issuers
 constexpr int kPackedStageBytes = kTileRows * (kStageK / 2);  // 16 KiB
 constexpr int kScaleStageBytes = kTileRows * (kStageK / 32) * 2;  // 2 KiB
 
 template <int BT> struct TcCfg {
-  static constexpr int kBStages = (BT <= 32) ? 8 : 4;
-  static constexpr int kBStageBytes = BT * kSubK * 2;
-  static constexpr int kTmemCols = (BT <= 128) ? 256 : 512;
+  // Token (B operand) ring: a stage holds kBSub sub-tiles of [BT x 64]; small token tiles
+  // are loaded several at a time so that one barrier round trip covers up to 256 K.  With two
+  // MMA issuers kBSub must be a multiple of 2 (each issuer waits/releases once per stage).
+  static constexpr int kBSub = (BT <= 32) ? 4 : (BT == 64) ? 2 : 1;
+  static constexpr int kBStages = (BT <= 32) ? 3 : 4;
+  static constexpr int kBSubBytes = BT * kSubK * 2;
+  static constexpr int kBStageBytes = kBSub * kBSubBytes;
+  // MMA issuers: narrow token tiles make the MMAs short (about 45 cycles each whatever N <= 64),
+  // so the issuing thread's own instruction stream becomes the limit; two issuer warps then
+  // take alternate K slices, each into its own accumulator (summed in the epilogue).
+  static constexpr int kIssuers = (BT <= 64) ? 2 : 1;
+  // Dequantiser warpgroups (4 warps each).  Two CTAs share an SM for narrow tiles (2 x 2
+  // warpgroups); wider tiles run one CTA per SM with four.  Warpgroup w owns the K slices
+  // sub = w, w + kWGs, ... of every 256-wide stage.
+  static constexpr int kWGs = (BT <= 32) ? 2 : 4;
+  static constexpr int kDequantWarps = 4 * kWGs;
+  static constexpr int kThreads = 32 * (kCtrlWarps + kDequantWarps);
+  static constexpr int kAcc = kIssuers;
+  static constexpr int kDCols = kAcc * BT;
+  static constexpr int kTmemCols = (BT <= 32) ? 256 : 512;
+  static constexpr int kASlots = (BT <= 32) ? 4 : 8;     // multiple of kIssuers and of kWGs
+  static constexpr int kACol0 = kDCols;                  // A ring starts after the accumulators
+  static_assert(kDCols + kASlots * kAColsPerSlot <= kTmemCols, "tensor memory overcommitted");
   static constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + (size_t)kWStages * kPackedStageBytes +
                                        (size_t)kBStages * kBStageBytes + (size_t)kWStages * kScaleStageBytes +
                                        1024 /*barriers*/;
 };
+
+#ifdef XKB_TC_TRACE
+// Debug builds only: CTA 0 logs (clock, tag) pairs per role into a global buffer.
+constexpr int kTraceCap = 4096;
+}  // namespace
+__device__ long long g_trace[8][kTraceCap];
+__device__ int g_trace_n[8];
+namespace {
+#define TRACE(role, tag)                                                         \
+  do {                                                                           \
+    if (blockIdx.x == 0 && trace_i < kTraceCap) {                                \
+      g_trace[role][trace_i++] = (clock64() << 8) | (tag);                       \
+      g_trace_n[role] = trace_i;                                                 \
+    }                                                                            \
+  } while (0)
+#else
+#define TRACE(role, tag) do {} while (0)
+#endif
 
 struct TcParams {
   const int32_t* sorted_ids;
@@ -84,7 +121,7 @@ __device__ __forceinline__ uint32_t dequant_pair(uint32_t biased, uint32_t scale
 }
 
 template <int BT>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(TcCfg<BT>::kThreads, (BT <= 32) ? 2 : 1)
 int4_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_constant__ CUtensorMap tm_scale,
                const __grid_constant__ CUtensorMap tm_tokens, const TcParams p) {
   using Cfg = TcCfg<BT>;
@@ -100,23 +137,28 @@ int4_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_const
   uint64_t* b_full = w_empty + kWStages;         // [kBStages]
   uint64_t* b_empty = b_full + Cfg::kBStages;    // [kBStages]
   uint64_t* a_full = b_empty + Cfg::kBStages;    // [kASlots]
-  uint64_t* a_empty = a_full + kASlots;          // [kASlots]
-  uint64_t* d_full = a_empty + kASlots;          // [1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(d_full + 1);
+  uint64_t* a_empty = a_full + Cfg::kASlots;     // [kASlots]
+  uint64_t* d_full = a_empty + Cfg::kASlots;     // [1]
+  uint64_t* d_empty = d_full + 1;                // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(d_empty + 1);
   int* abort_word = reinterpret_cast<int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   Guard guard{abort_word, p.status};
+#ifdef XKB_TC_TRACE
+  int trace_i = 0;
+#endif
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < kWStages; ++i) { mbar_init(&w_full[i], 1); mbar_init(&w_empty[i], 128); }
-    for (int i = 0; i < Cfg::kBStages; ++i) { mbar_init(&b_full[i], 1); mbar_init(&b_empty[i], 1); }
-    for (int i = 0; i < kASlots; ++i) { mbar_init(&a_full[i], 128); mbar_init(&a_empty[i], 1); }
-    mbar_init(d_full, 1);
+    for (int i = 0; i < kWStages; ++i) { mbar_init(&w_full[i], 1); mbar_init(&w_empty[i], Cfg::kDequantWarps); }
+    for (int i = 0; i < Cfg::kBStages; ++i) { mbar_init(&b_full[i], 1); mbar_init(&b_empty[i], Cfg::kIssuers); }
+    for (int i = 0; i < Cfg::kASlots; ++i) { mbar_init(&a_full[i], 4); mbar_init(&a_empty[i], 1); }
+    mbar_init(d_full, Cfg::kIssuers);
+    mbar_init(d_empty, Cfg::kDequantWarps);
     *abort_word = 0;
     mbar_fence_init();
   }
-  if (warp == 3) tmem_alloc(tmem_slot, Cfg::kTmemCols);
+  if (warp == 1) tmem_alloc(tmem_slot, Cfg::kTmemCols);
   if (warp == 0 && lane == 0) { prefetch_tensormap(&tm_packed); prefetch_tensormap(&tm_scale); }
   if (warp == 1 && lane == 0) prefetch_tensormap(&tm_tokens);
   tc_fence_before();
@@ -137,7 +179,9 @@ int4_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_const
         const int nt = (int)(t % n_tiles), b = (int)(t / n_tiles);
         const int row0 = p.expert_ids[b] * p.N + nt * kTileRows;
         for (int ks = 0; ks < k_stages; ++ks) {
-          if (!mbar_wait(&w_empty[st], ph ^ 1, guard, 1)) break;
+          TRACE(0, 1);
+          if (!mbar_wait(&w_empty[st], ph ^ 1, guard, 1, 400)) break;
+          TRACE(0, 2);
           mbar_expect_tx(&w_full[st], kPackedStageBytes + kScaleStageBytes);
           tma_load_2d(s_packed + st * kPackedStageBytes, &tm_packed, &w_full[st], ks * (kStageK / 2), row0);
           tma_load_2d(s_scale + st * kScaleStageBytes, &tm_scale, &w_full[st], ks * (kStageK / 32), row0);
@@ -152,96 +196,150 @@ int4_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_const
       for (int64_t t = blockIdx.x; t < total_tiles && !guard.aborted(); t += gridDim.x) {
         const int b = (int)(t / n_tiles);
         const int pos0 = b * BT;
-        for (int s = 0; s < k_stages * kSubs; ++s) {
-          if (!mbar_wait(&b_empty[st], ph ^ 1, guard, 2)) break;
+        for (int s = 0; s < k_stages * kSubs; s += Cfg::kBSub) {
+          TRACE(1, 1);
+          if (!mbar_wait(&b_empty[st], ph ^ 1, guard, 2, 400)) break;
+          TRACE(1, 2);
           mbar_expect_tx(&b_full[st], Cfg::kBStageBytes);
-          tma_load_2d(s_tokens + st * Cfg::kBStageBytes, &tm_tokens, &b_full[st], s * kSubK, pos0);
+#pragma unroll
+          for (int j = 0; j < Cfg::kBSub; ++j)
+            tma_load_2d(s_tokens + st * Cfg::kBStageBytes + j * Cfg::kBSubBytes, &tm_tokens, &b_full[st],
+                        (s + j) * kSubK, pos0);
           if (++st == Cfg::kBStages) { st = 0; ph ^= 1; }
         }
       }
     }
-  } else if (warp == 2) {
-    // ---------------- MMA issuer ----------------
-    if (lane == 0) {
+  } else if (warp < kCtrlWarps) {
+    // ---------------- MMA issuer(s) ----------------
+    // Issuer i takes the K slices g with g % kIssuers == i and accumulates into accumulator i.
+    const int me = warp - 2;
+    if (lane == 0 && me < Cfg::kIssuers) {
       constexpr uint32_t idesc = umma_idesc_bf16(kTileRows, BT);
-      uint32_t bst = 0, bph = 0, aq = 0, aph = 0;
-      const uint32_t d_tmem = tmem_base + kDCol0;
+      constexpr int kStep = Cfg::kIssuers;
+      uint32_t bst = 0, bph = 0, aq = me, aph = 0, eph = 0;
+      const uint32_t d_tmem = tmem_base + me * BT;
       for (int64_t t = blockIdx.x; t < total_tiles && !guard.aborted(); t += gridDim.x) {
-        bool ok = true;
-        for (int s = 0; s < k_stages * kSubs && ok; ++s) {
-          ok = mbar_wait(&a_full[aq], aph, guard, 3) && mbar_wait(&b_full[bst], bph, guard, 4);
+        // the previous tile's accumulators must have been read out by every epilogue thread
+        bool ok = mbar_wait(d_empty, eph ^ 1, guard, 8, 100);
+        eph ^= 1;
+        if (ok) tc_fence_after();
+        for (int s = me; s < k_stages * kSubs && ok; s += kStep) {
+          const int bsub = s % Cfg::kBSub;
+          TRACE(2, 1);
+          ok = mbar_wait(&a_full[aq], aph, guard, 3, 100);
+          TRACE(2, 2);
+          // first slice of this issuer inside a token stage: the stage must have landed
+          if (ok && bsub < kStep) ok = mbar_wait(&b_full[bst], bph, guard, 4);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t a_tmem = tmem_base + aq * kAColsPerSlot;
-          const uint64_t b_desc = umma_desc_k_sw128(smem_u32(s_tokens + bst * Cfg::kBStageBytes));
+          TRACE(2, 3);
+          const uint32_t a_tmem = tmem_base + Cfg::kACol0 + aq * kAColsPerSlot;
+          const uint64_t b_desc =
+              umma_desc_k_sw128(smem_u32(s_tokens + bst * Cfg::kBStageBytes + bsub * Cfg::kBSubBytes));
 #pragma unroll
-          for (int kk = 0; kk < kSubK / 16; ++kk)
-            umma_ts_bf16(d_tmem, a_tmem + kk * 8, b_desc + (uint64_t)(kk * 2), idesc, (s | kk) != 0 ? 1u : 0u);
+          for (int kk = 0; kk < kSubK / 16; ++kk)  // the first MMA of a tile overwrites the accumulator
+            umma_ts_bf16(d_tmem, a_tmem + kk * 8, b_desc + (uint64_t)(kk * 2), idesc, (s != me || kk != 0) ? 1u : 0u);
+          TRACE(2, 4);
           tc_commit(&a_empty[aq]);
-          tc_commit(&b_empty[bst]);
-          if (++aq == kASlots) { aq = 0; aph ^= 1; }
-          if (++bst == Cfg::kBStages) { bst = 0; bph ^= 1; }
+          TRACE(2, 5);
+          aq += kStep;
+          if (aq >= (uint32_t)Cfg::kASlots) { aq -= Cfg::kASlots; aph ^= 1; }
+          // last slice of this issuer inside the token stage: release it
+          if (bsub + kStep >= Cfg::kBSub) {
+            tc_commit(&b_empty[bst]);
+            if (++bst == Cfg::kBStages) { bst = 0; bph ^= 1; }
+          }
         }
         if (!ok) break;
         tc_commit(d_full);
       }
     }
-  } else if (warp >= 4) {
+  } else {
     // ---------------- dequantisers + epilogue ----------------
+    // K slices of 64 are numbered g = 0,1,2,... across stages and tiles; slice g goes to
+    // tensor-memory slot g % kASlots and is produced by warpgroup g % kWGs.
+    // A slice is stored eight columns at a time as its words are dequantised and published
+    // as soon as the stores have completed.
+    const int wg = (warp - kCtrlWarps) >> 2;
     const int quarter = warp & 3;              // tensor-memory lane quarter this warp may access
     const int row = quarter * 32 + lane;       // weight row inside the tile
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-    uint32_t wst = 0, wph = 0, aq = 0, aph = 0, dph = 0;
+    uint32_t wst = 0, wph = 0, dph = 0;
+    uint32_t aq = wg, aph = 0;                 // next slot of this warpgroup and its phase
     for (int64_t t = blockIdx.x; t < total_tiles; t += gridDim.x) {
       const int nt = (int)(t % n_tiles), b = (int)(t / n_tiles);
       bool ok = true;
       for (int ks = 0; ks < k_stages && ok; ++ks) {
+        if (lane == 0 && quarter == 0) TRACE(3 + wg, 1);
         if (!mbar_wait(&w_full[wst], wph, guard, 5)) { ok = false; break; }
+        if (lane == 0 && quarter == 0) TRACE(3 + wg, 2);
         const unsigned char* pk = s_packed + wst * kPackedStageBytes + row * 128;
         const uint4 sc = *reinterpret_cast<const uint4*>(s_scale + wst * kScaleStageBytes + row * 16);
         const uint32_t sc_w[4] = {sc.x, sc.y, sc.z, sc.w};
 #pragma unroll
-        for (int sub = 0; sub < kSubs; ++sub) {
-          uint32_t out[32];
+        for (int i = 0; i < kSubs / Cfg::kWGs; ++i) {
+          const int sub = wg + Cfg::kWGs * i;
+          if (lane == 0 && quarter == 0) TRACE(3 + wg, 3);
+          if (!mbar_wait(&a_empty[aq], aph ^ 1, guard, 6)) { ok = false; break; }
+          tc_fence_after();
+          if (lane == 0 && quarter == 0) TRACE(3 + wg, 4);
+          const uint32_t dst = tmem_base + lane_base + Cfg::kACol0 + aq * kAColsPerSlot;
+          uint32_t sw = sc_w[0];  // the two group scales of slice `sub` (static indices only)
+#pragma unroll
+          for (int q = 1; q < kSubs; ++q)
+            if (q == sub) sw = sc_w[q];
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             const int chunk = sub * 2 + h;  // 16-byte chunk = 32 weights = one scale group
             const uint4 w4 = *reinterpret_cast<const uint4*>(pk + ((chunk ^ (row & 7)) << 4));
-            const uint32_t s16 = (chunk & 1) ? (sc_w[chunk >> 1] >> 16) : (sc_w[chunk >> 1] & 0xFFFFu);
-            const uint32_t s2 = s16 | (s16 << 16);
+            const uint32_t s2 = h ? __byte_perm(sw, sw, 0x3232) : __byte_perm(sw, sw, 0x1010);
             const uint32_t words[4] = {w4.x, w4.y, w4.z, w4.w};
 #pragma unroll
-            for (int wi = 0; wi < 4; ++wi) {
-              const uint32_t x = words[wi];
-              out[h * 16 + wi * 4 + 0] = dequant_pair(nib_pair(x), s2);        // nibbles 0,4
-              out[h * 16 + wi * 4 + 1] = dequant_pair(nib_pair(x >> 4), s2);   // nibbles 1,5
-              out[h * 16 + wi * 4 + 2] = dequant_pair(nib_pair(x >> 8), s2);   // nibbles 2,6
-              out[h * 16 + wi * 4 + 3] = dequant_pair(nib_pair(x >> 12), s2);  // nibbles 3,7
+            for (int wp = 0; wp < 2; ++wp) {  // two words = 16 weights = 8 columns
+              const uint32_t x0 = words[2 * wp], x1 = words[2 * wp + 1];
+              tmem_st_32x8(dst + h * 16 + wp * 8,
+                           dequant_pair(nib_pair(x0), s2), dequant_pair(nib_pair(x0 >> 4), s2),
+                           dequant_pair(nib_pair(x0 >> 8), s2), dequant_pair(nib_pair(x0 >> 12), s2),
+                           dequant_pair(nib_pair(x1), s2), dequant_pair(nib_pair(x1 >> 4), s2),
+                           dequant_pair(nib_pair(x1 >> 8), s2), dequant_pair(nib_pair(x1 >> 12), s2));
             }
           }
-          if (!mbar_wait(&a_empty[aq], aph ^ 1, guard, 6)) { ok = false; break; }
-          tc_fence_after();
-          tmem_st_32x32(tmem_base + lane_base + aq * kAColsPerSlot, out);
+          if (i == kSubs / Cfg::kWGs - 1) {  // last read of this stage is done: one arrival per warp
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&w_empty[wst]);
+          }
+          if (lane == 0 && quarter == 0) TRACE(3 + wg, 5);
           tmem_wait_st();
           tc_fence_before();
-          mbar_arrive(&a_full[aq]);
-          if (++aq == kASlots) { aq = 0; aph ^= 1; }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&a_full[aq]);
+          if (lane == 0 && quarter == 0) TRACE(3 + wg, 6);
+          aq += Cfg::kWGs;
+          if (aq >= (uint32_t)Cfg::kASlots) { aq -= Cfg::kASlots; aph ^= 1; }
         }
-        mbar_arrive(&w_empty[wst]);
         if (++wst == kWStages) { wst = 0; wph ^= 1; }
       }
       if (!ok) break;
-      // epilogue: accumulators -> x topk_w -> fp32 slot rows
+      // epilogue (the warpgroups take the 16-column groups round robin):
+      // sum of the kAcc accumulators -> x topk_w -> fp32 slot rows
       if (!mbar_wait(d_full, dph, guard, 7)) break;
       dph ^= 1;
       tc_fence_after();
       const int64_t n_glob = (int64_t)nt * kTileRows + row;
       const int32_t* slots = p.sorted_ids + (int64_t)b * BT;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BT; c0 += 16) {
+      for (int c0 = wg * 16; c0 < BT; c0 += 16 * Cfg::kWGs) {
         uint32_t acc[16];
-        tmem_ld_32x16(tmem_base + lane_base + kDCol0 + c0, acc);
+        tmem_ld_32x16(tmem_base + lane_base + c0, acc);
         tmem_wait_ld();
+#pragma unroll
+        for (int a = 1; a < Cfg::kAcc; ++a) {
+          uint32_t more[16];
+          tmem_ld_32x16(tmem_base + lane_base + a * BT + c0, more);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) acc[j] = __float_as_uint(__uint_as_float(acc[j]) + __uint_as_float(more[j]));
+        }
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           const int32_t slot = __ldg(slots + c0 + j);  // same address for the whole warp
@@ -253,12 +351,14 @@ int4_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_const
         }
       }
       tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(d_empty);
     }
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 3) {
+  if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }
@@ -350,7 +450,7 @@ int launch_bt(const CUtensorMap& tmp, const CUtensorMap& tms, const CUtensorMap&
   if (grid < 1) grid = 1;
   {
     GemmTimerScope timed(stream);
-    int4_tc_kernel<BT><<<(unsigned)grid, kThreads, Cfg::kSmemBytes, stream>>>(tmp, tms, tmt, prm);
+    int4_tc_kernel<BT><<<(unsigned)grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tmp, tms, tmt, prm);
   }
   XKB_CHECK_LAUNCH("int4_tc_kernel");
   return XKB_OK;
@@ -435,3 +535,14 @@ int launch_mxfp4_tc(const void*, const uint8_t*, const uint8_t*, const uint8_t*,
 }
 
 }  // namespace xkb
+
+#ifdef XKB_TC_TRACE
+extern "C" int xkb_debug_trace(long long* host, int* counts_host) {
+  int zero[8] = {0};
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(counts_host, xkb::g_trace_n, sizeof(int) * 8);
+  cudaMemcpyFromSymbol(host, xkb::g_trace, sizeof(long long) * 8 * xkb::kTraceCap);
+  cudaMemcpyToSymbol(xkb::g_trace_n, zero, sizeof(zero));
+  return 0;
+}
+#endif

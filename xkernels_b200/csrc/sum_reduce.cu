@@ -148,6 +148,31 @@ int dispatch_out(int out_dtype, const void* y, const void* w, void* out, int64_t
   return launch_typed<TY, TW, float>(y, w, out, M, top_k, H, rsf, ids, emap, num_map, s);
 }
 
+// out[m, :] = sum_k w[m,k] * rows[row_index[m,k], :]   (fp32 rows, ascending k, fp32 sum).
+// row_index < 0 skips the term.  One thread = 4 consecutive columns.
+template <typename TO>
+__global__ void __launch_bounds__(256)
+gather_reduce_kernel(const float* __restrict__ rows, const int32_t* __restrict__ row_index,
+                     const float* __restrict__ w, TO* __restrict__ out, int64_t M, int top_k, int64_t H) {
+  const int64_t hv = H >> 2;
+  const int64_t total = M * hv;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t m = idx / hv;
+    const int64_t h = (idx - m * hv) << 2;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k = 0; k < top_k; ++k) {
+      const int32_t r = row_index[m * top_k + k];
+      if (r < 0) continue;
+      const float4 v = __ldg(reinterpret_cast<const float4*>(rows + (int64_t)r * H + h));
+      const float wk = (w != nullptr) ? w[m * top_k + k] : 1.f;
+      acc.x += wk * v.x; acc.y += wk * v.y; acc.z += wk * v.z; acc.w += wk * v.w;
+    }
+    TO* o = out + m * H + h;
+    from_f(o[0], acc.x); from_f(o[1], acc.y); from_f(o[2], acc.z); from_f(o[3], acc.w);
+  }
+}
+
 }  // namespace
 
 int launch_combine(const float* scratch, const int32_t* topk_ids, const int32_t* expert_map,
@@ -180,4 +205,27 @@ extern "C" int xkb_moe_sum_reduce(const void* y, int y_dtype, const void* w, int
   if (w != nullptr && w_dtype == XKB_BF16)
     return dispatch_out<float, __nv_bfloat16>(out_dtype, y, w, out, M, top_k, H, rsf, nullptr, nullptr, 0, s);
   return dispatch_out<float, float>(out_dtype, y, w, out, M, top_k, H, rsf, nullptr, nullptr, 0, s);
+}
+
+extern "C" int xkb_moe_gather_sum_reduce(const float* rows, const int32_t* row_index, const float* w,
+                                         void* out, int out_dtype, int64_t M, int top_k, int64_t H,
+                                         void* stream) {
+  using namespace xkb;
+  XKB_REQUIRE(M >= 0 && H >= 0 && top_k >= 0, "moe_gather_sum_reduce: negative dimension");
+  XKB_REQUIRE(H % 4 == 0, "moe_gather_sum_reduce: H must be a multiple of 4 (got %lld)", (long long)H);
+  XKB_REQUIRE(out_dtype == XKB_BF16 || out_dtype == XKB_F32, "moe_gather_sum_reduce: bad out_dtype");
+  if (M == 0 || H == 0) return XKB_OK;
+  XKB_REQUIRE(rows && row_index && out, "moe_gather_sum_reduce: null pointer");
+  XKB_REQUIRE(reinterpret_cast<uintptr_t>(rows) % 16 == 0, "moe_gather_sum_reduce: rows must be 16-byte aligned");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int64_t blocks = ceil_div(M * (H / 4), 256);
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  if (out_dtype == XKB_BF16)
+    gather_reduce_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, s>>>(
+        rows, row_index, w, static_cast<__nv_bfloat16*>(out), M, top_k, H);
+  else
+    gather_reduce_kernel<float><<<(unsigned)blocks, 256, 0, s>>>(rows, row_index, w,
+                                                                 static_cast<float*>(out), M, top_k, H);
+  XKB_CHECK_LAUNCH("gather_reduce_kernel");
+  return XKB_OK;
 }

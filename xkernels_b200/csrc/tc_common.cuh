@@ -14,9 +14,9 @@ namespace tc {
 // Error codes a kernel writes to its status word when a bounded wait runs out.
 constexpr int kErrWaitTimeout = 1;
 
-// Poll budget of one wait.  A poll costs tens of nanoseconds, so this bounds a
-// wait to roughly a second; a healthy pipeline needs a few hundred polls.
-constexpr uint32_t kMaxPolls = 1u << 25;
+// Poll budget of one wait.  A probe parks the thread for up to its time hint (2 us by default),
+// so this bounds a wait to about a second; a healthy pipeline needs a handful of probes.
+constexpr uint32_t kMaxPolls = 1u << 19;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -36,14 +36,17 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                : "memory");
 }
-__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
+// One probe of the barrier phase.  `hint_ns` lets the hardware park the thread for up to that
+// long while the phase is incomplete (it is woken when the phase completes), so that waiting
+// roles do not burn the issue slots the dequantiser warps need.
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
       : "memory");
   return ok != 0;
 }
@@ -61,10 +64,15 @@ struct Guard {
 
 // Bounded wait: returns false (after recording the failure) if the barrier has
 // not completed the phase within the poll budget or another role aborted.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Guard& g, int where) {
+// `sleep_ns` > 0 backs off between probes: roles that run ahead of the pipeline
+// (the TMA producers) and roles that wait on the slower side (the MMA issuers)
+// would otherwise spend issue slots on probes that the dequantiser warps need.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Guard& g, int where,
+                                          uint32_t sleep_ns = 0) {
   for (uint32_t i = 0; i < kMaxPolls; ++i) {
-    if (mbar_try(bar, parity)) return true;
-    if ((i & 1023u) == 1023u && g.aborted()) return false;
+    if (mbar_try(bar, parity, 1000)) return true;
+    if (sleep_ns) __nanosleep(sleep_ns);
+    if ((i & 63u) == 63u && g.aborted()) return false;
   }
   g.raise(kErrWaitTimeout + (where << 8));
   return false;
@@ -117,6 +125,13 @@ __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r
       "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]),
       "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
+}
+// 32 lanes x 8 columns store (registers r[0..7] of each thread).
+__device__ __forceinline__ void tmem_st_32x8(uint32_t taddr, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3,
+                                             uint32_t r4, uint32_t r5, uint32_t r6, uint32_t r7) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               ::"r"(taddr), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "r"(r4), "r"(r5), "r"(r6), "r"(r7)
+               : "memory");
 }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 

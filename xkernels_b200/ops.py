@@ -272,3 +272,55 @@ def fused_moe_mxfp4(A, w13, w13_scale, w2, w2_scale, topk_ids, topk_w, b13=None,
                 _ptr(ws), ws.numel(), _stream(dev)),
             "xkb_fused_moe_mxfp4")
     return out
+
+
+# ---------------------------------------------------------------------------
+# expert-parallel building blocks
+# ---------------------------------------------------------------------------
+def moe_int4_w4a16_rows(A, packed, scale, topk_ids, topk_w=None, group_size=32, *, path="auto"):
+    """Grouped INT4 expert GEMM without the top-k combine: ``[M*top_k, N]`` fp32 rows, row
+    ``m*top_k + j`` = ``A[m] @ W[topk_ids[m,j]]^T`` (times ``topk_w[m,j]`` if given)."""
+    lib = _lib.load()
+    dev = _require_cuda("moe_int4_w4a16_rows", A, packed, scale, topk_ids, topk_w)
+    if A.dtype not in _DT:
+        raise TypeError(f"moe_int4_w4a16_rows: A must be bf16 or fp32, got {A.dtype}")
+    A, packed = A.contiguous(), packed.contiguous()
+    scale = scale.to(torch.bfloat16).contiguous()
+    M, K = A.shape
+    E, N, _ = packed.shape
+    ids = topk_ids.to(torch.int32).contiguous()
+    top_k = ids.shape[1]
+    tw = None if topk_w is None else topk_w.to(torch.float32).contiguous()
+    pcode = {"auto": _lib.PATH_AUTO, "simt": _lib.PATH_SIMT, "tc": _lib.PATH_TC}[path]
+    with torch.cuda.device(dev):
+        rows = torch.empty((M * top_k, N), dtype=torch.float32, device=dev)
+        if M == 0:
+            return rows
+        ws_bytes = int(lib.xkb_fused_moe_int4_w4a16_workspace_bytes(M, N, K, E, top_k, _DT[A.dtype]))
+        ws = get_workspace(dev, ws_bytes)
+        _lib.check(
+            lib.xkb_moe_int4_w4a16_rows(_ptr(A), _DT[A.dtype], _ptr(packed), _ptr(scale), _ptr(ids),
+                                        _ptr(tw), _ptr(rows), M, N, K, E, top_k, int(group_size),
+                                        0 if tw is None else 1, pcode, _ptr(ws), ws.numel(), _stream(dev)),
+            "xkb_moe_int4_w4a16_rows")
+    return rows
+
+
+def moe_gather_sum_reduce(rows, row_index, w, out_dtype=torch.bfloat16):
+    """``out[m] = sum_k w[m,k] * rows[row_index[m,k]]`` in fp32, ascending k (index < 0 skips)."""
+    lib = _lib.load()
+    dev = _require_cuda("moe_gather_sum_reduce", rows, row_index, w)
+    if rows.dtype != torch.float32:
+        raise TypeError("moe_gather_sum_reduce: rows must be fp32")
+    rows = rows.contiguous()
+    idx = row_index.to(torch.int32).contiguous()
+    M, top_k = idx.shape
+    H = rows.shape[1]
+    w = None if w is None else w.to(torch.float32).contiguous()
+    with torch.cuda.device(dev):
+        out = torch.empty((M, H), dtype=out_dtype, device=dev)
+        _lib.check(
+            lib.xkb_moe_gather_sum_reduce(_ptr(rows), _ptr(idx), _ptr(w), _ptr(out), _DT[out_dtype], M, top_k,
+                                          H, _stream(dev)),
+            "xkb_moe_gather_sum_reduce")
+    return out
