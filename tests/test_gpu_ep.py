@@ -1,0 +1,86 @@
+"""Expert-parallel mode on GPUs: the two local C-ABI building blocks on one GPU, and the full
+NCCL all-to-all path as one child process per GPU when at least two GPUs are visible."""
+
+import os
+import socket
+
+import pytest
+import torch
+
+import xkernels_b200 as xkb
+from oracle import moe_oracle as oracle
+from tests.gpu_util import assert_within
+from xkernels_b200 import ops, synth
+
+pytestmark = pytest.mark.gpu
+
+
+def test_rows_and_gather_reduce_equal_the_fused_op(cuda_device):
+    cfg = synth.Int4Config("t", M=40, K=512, N=256, E=8, top_k=4)
+    d = synth.make_int4(cfg, seed=11, device=cuda_device)
+    fused = xkb.fused_moe_int4_w4a16(d["A"], d["packed"], d["scale"], d["topk_ids"], d["topk_w"])
+    rows = ops.moe_int4_w4a16_rows(d["A"], d["packed"], d["scale"], d["topk_ids"])
+    assert rows.shape == (cfg.M * cfg.top_k, cfg.N) and rows.dtype == torch.float32
+    idx = torch.arange(cfg.M * cfg.top_k, device=cuda_device, dtype=torch.int32).view(cfg.M, cfg.top_k)
+    out = ops.moe_gather_sum_reduce(rows, idx, d["topk_w"], torch.bfloat16)
+    assert_within(out, fused, 1e-2, 1e-2, what="rows + gather_reduce vs fused")
+    # a permuted row buffer with the matching index gives the same bits
+    perm = torch.randperm(rows.shape[0], device=cuda_device)
+    inv = torch.empty_like(perm)
+    inv[perm] = torch.arange(perm.numel(), device=cuda_device)
+    out2 = ops.moe_gather_sum_reduce(rows[perm].contiguous(), inv.view(cfg.M, cfg.top_k).int(), d["topk_w"],
+                                     torch.bfloat16)
+    assert torch.equal(out, out2)
+    # one row per slot with top_k = 1 (the form the expert side of the exchange uses)
+    cpu = {k: (v.cpu() if isinstance(v, torch.Tensor) else v) for k, v in d.items()}
+    flat_ids = d["topk_ids"].reshape(-1, 1)
+    A_rows = d["A"].repeat_interleave(cfg.top_k, dim=0)
+    rows1 = ops.moe_int4_w4a16_rows(A_rows, d["packed"], d["scale"], flat_ids)
+    want = oracle.moe_w4a16(cpu["A"].repeat_interleave(cfg.top_k, dim=0), cpu["packed"], cpu["scale"],
+                            cpu["topk_ids"].reshape(-1, 1), torch.ones(cfg.M * cfg.top_k, 1), 32)
+    assert_within(rows1.bfloat16(), want, 2e-2, 1e-2, what="top_k=1 rows")
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _ep_worker(rank: int, world: int, port: int):
+    import torch.distributed as dist
+
+    from xkernels_b200 import ep
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        cfg = synth.Int4Config("ep", M=96, K=512, N=256, E=16, top_k=4, zipf_scale=2.0)
+        packed, scale = synth.int4_weights(cfg.E, cfg.N, cfg.K, 32, seed=5)      # global, CPU, same on all ranks
+        e_local = cfg.E // world
+        sl = slice(rank * e_local, (rank + 1) * e_local)
+        A = synth.activations(cfg.M, cfg.K, seed=100 + rank)
+        ids, w = synth.routing(cfg.M, cfg.E, cfg.top_k, seed=200 + rank, zipf_scale=cfg.zipf_scale)
+        layer = ep.ExpertParallelInt4(packed[sl].to(dev), scale[sl].to(dev), num_global_experts=cfg.E)
+        out = layer(A.to(dev), ids.to(dev), w.to(dev))
+        ops.check_status(dev)
+        want = oracle.moe_w4a16(A, packed, scale, ids, w, 32)
+        bad = oracle.count_violations(out.cpu(), want, 2e-2, 1e-2)
+        assert bad == 0, f"rank {rank}: {bad} elements differ from the dense oracle"
+        again = layer(A.to(dev), ids.to(dev), w.to(dev))
+        assert torch.equal(out, again)
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_all_to_all_on_gpus():
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    import torch.multiprocessing as mp
+
+    world = 4 if n >= 4 else 2
+    mp.spawn(_ep_worker, args=(world, _free_port()), nprocs=world, join=True)
