@@ -72,6 +72,37 @@ int xkb_moe_align_block_size(const int32_t* topk_ids, int64_t numel,
                              void* stream);
 
 /* ------------------------------------------------------------------------
+ * xkb_moe_align_block_size_static: the same operation and outputs as
+ * xkb_moe_align_block_size, for callers that cannot provide scratch memory.
+ * It has no counterpart in the reference.
+ *
+ * Who needs it: code that is not allowed to create device memory at the point
+ * of the call - a plug-in living inside another runtime's memory pool, a
+ * serving loop that has frozen its allocator, a plain C caller without one.
+ * The scratch of the multi-launch path (the chunk x expert count matrix) is a
+ * fixed array compiled into the library, about 258 KiB on every GPU that loads
+ * the library, kept until the process ends.  The call makes no cudaMalloc /
+ * cudaFree and uses no allocating library routine; inputs and outputs are
+ * still the caller's.
+ *
+ * Limits: numel <= 262144 token-slots and num_experts <= 256; larger
+ * arguments are refused with XKB_ERR_ARG and a message that names the limit.
+ * The first call on a device looks up the array's device address
+ * (cudaGetSymbolAddress, with that device current) and remembers it; make
+ * that first call before starting any stream capture.  All calls on a device
+ * share the one array, which keeps whatever the previous call left in it (no
+ * part of it needs clearing: every entry that is read is first rewritten by
+ * the same call).  Two calls that overlap on the GPU - different streams, or
+ * different host threads - race on it and must be serialised by the caller.
+ * ---------------------------------------------------------------------- */
+int xkb_moe_align_block_size_static(const int32_t* topk_ids, int64_t numel,
+                                    int num_experts, int block_size,
+                                    const int32_t* expert_map, int num_map,
+                                    int32_t* sorted_ids, int32_t* expert_ids,
+                                    int32_t* num_post_pad,
+                                    int32_t* expert_offsets, void* stream);
+
+/* ------------------------------------------------------------------------
  * moe_sum_reduce: out[m,:] = rsf * sum_k (w[m,k] or 1) * y[m,k,:]
  * Replaces: src/xkernels/ops/moe/sum_reduce.py:20-39 (reference),
  *           src/xkernels/ops/moe/triton/sum_reduce_kernel.py:66-100,

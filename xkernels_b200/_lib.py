@@ -31,6 +31,10 @@ SIGNATURES = {
         [c_void_p, c_int64, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
          c_void_p, c_int64, c_void_p],
     ),
+    "xkb_moe_align_block_size_static": (
+        c_int,
+        [c_void_p, c_int64, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+    ),
     "xkb_moe_sum_reduce": (
         c_int,
         [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int64, c_int, c_int64, c_float, c_void_p],

@@ -324,3 +324,70 @@ extern "C" int xkb_moe_align_block_size(const int32_t* topk_ids, int64_t numel, 
                            expert_ids, num_post_pad, expert_offsets, workspace, workspace_bytes,
                            static_cast<cudaStream_t>(stream));
 }
+
+// ---------------------------------------------------------------------------
+// Allocation-free variant.
+//
+// Some hosts of this library may not create device memory at all: a plug-in that runs inside
+// another runtime's memory pool, code that executes while that runtime forbids allocation (for
+// example between the points where its allocator may be entered), or a C caller that simply has
+// no allocator for scratch buffers.  For them the chunk x expert count matrix of the multi-launch
+// align path lives in a fixed array inside the library image instead of a caller workspace.
+// The price is a size limit and the loss of re-entrancy (see the header comment).
+// ---------------------------------------------------------------------------
+namespace xkb {
+namespace {
+
+constexpr int64_t kStaticMaxSlots = 262144;   // numel limit: 256 chunks of 1024 slots
+constexpr int kStaticMaxExperts = 256;        // num_experts limit
+constexpr int64_t kStaticChunks = kStaticMaxSlots / kChunk;
+constexpr int64_t kStaticInts = kStaticChunks * (kStaticMaxExperts + 1) + (kStaticMaxExperts + 1) + 256;
+
+// ~258 KiB per GPU that loads the library, held until the process exits.
+static __device__ __align__(256) int32_t g_align_static_scratch[kStaticInts];
+
+constexpr int kMaxDevices = 64;
+void* g_static_ptr[kMaxDevices] = {nullptr};   // device address of the array, per device
+
+// The array's name is only a host-side handle; the device address has to be asked for, once per
+// device, with that device current.
+int static_scratch_address(void** out) {
+  int dev = -1;
+  XKB_CHECK_CUDA(cudaGetDevice(&dev));
+  XKB_REQUIRE(dev >= 0 && dev < kMaxDevices, "moe_align (static): device index %d not supported", dev);
+  if (g_static_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    XKB_CHECK_CUDA(cudaGetSymbolAddress(&p, g_align_static_scratch));
+    XKB_REQUIRE(p != nullptr, "moe_align (static): cudaGetSymbolAddress returned a null address");
+    g_static_ptr[dev] = p;
+  }
+  *out = g_static_ptr[dev];
+  return XKB_OK;
+}
+
+}  // namespace
+}  // namespace xkb
+
+extern "C" int xkb_moe_align_block_size_static(const int32_t* topk_ids, int64_t numel, int num_experts,
+                                               int block_size, const int32_t* expert_map, int num_map,
+                                               int32_t* sorted_ids, int32_t* expert_ids,
+                                               int32_t* num_post_pad, int32_t* expert_offsets,
+                                               void* stream) {
+  using namespace xkb;
+  XKB_REQUIRE(numel >= 0 && numel <= kStaticMaxSlots,
+              "moe_align (static): numel=%lld exceeds the built-in scratch limit of %lld token-slots; "
+              "use xkb_moe_align_block_size with a caller workspace",
+              (long long)numel, (long long)kStaticMaxSlots);
+  XKB_REQUIRE(num_experts >= 0 && num_experts <= kStaticMaxExperts,
+              "moe_align (static): num_experts=%d exceeds the built-in scratch limit of %d; "
+              "use xkb_moe_align_block_size with a caller workspace",
+              num_experts, kStaticMaxExperts);
+  void* scratch = nullptr;
+  const int rc = static_scratch_address(&scratch);
+  if (rc != XKB_OK) return rc;
+  // Nothing in the scratch has to start at zero: the count kernel writes every entry of the
+  // chunk x expert matrix that the later kernels read, and the offsets slice is fully rewritten.
+  return launch_align(topk_ids, numel, num_experts, block_size, expert_map, num_map, sorted_ids,
+                      expert_ids, num_post_pad, expert_offsets, scratch,
+                      kStaticInts * (int64_t)sizeof(int32_t), static_cast<cudaStream_t>(stream));
+}
