@@ -246,9 +246,13 @@ def run_single_gpu(args):
     value = cfg.M / (ms_per_step * 1e-3)
     gemm_avg_ms = sum(gemm_ms) / max(len(gemm_ms), 1)
     achieved = alg_bytes / (gemm_avg_ms * 1e-3) / 1e9
+    # DRAM traffic per launch from the ncu capture of the 16-expert relative of this workload
+    # (profiles/int4_tc_kernel_decode_small.md: 276.6 MB read+write for 264.2 MB of weights and
+    # scales); traffic grows with the experts touched, so it is scaled by n_active / 16.
+    traffic = 276.6e6 * n_active / 16.0
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                "frac": achieved / peaks["hbm_gbs"], "traffic": None,
-                "kernel": "int4_tc_kernel<16>", "kernel_us": gemm_avg_ms * 1e3,
+                "frac": achieved / peaks["hbm_gbs"], "traffic": traffic,
+                "kernel": "moe_tc_kernel<16, int4>", "kernel_us": gemm_avg_ms * 1e3,
                 "algorithmic_bytes": alg_bytes, "peak_source": peaks["source"],
                 "whole_call_frac": (alg_bytes / (ms_per_step * 1e-3) / 1e9) / peaks["hbm_gbs"]}
 
@@ -339,12 +343,15 @@ def extras(dev, peaks):
         n_active = int(torch.unique(d["topk_ids"]).numel())
         fn = lambda: xkb.fused_moe_mxfp4(d["A"], d["w13"], d["w13_scale"], d["w2"], d["w2_scale"],  # noqa: E731
                                          d["topk_ids"], d["topk_w"])
-        _lib.gemm_timer_enable(20)
-        ms = time_call(fn, 3, 20)
-        g = _lib.gemm_timer_read()[-20:]
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        _lib.gemm_timer_enable(64)          # two GEMM kernels (gate_up, down) per call
+        ms = time_call(fn, 0, 20)
+        g = _lib.gemm_timer_read()
         _lib.gemm_timer_enable(0)
         ops.check_status(dev)
-        gm = sum(g) / len(g)
+        gm = sum(g) / 20
         b = synth.mxfp4_algorithmic_bytes(cfg, n_active)
         out["mxfp4_decode"] = {"us_per_call": ms * 1e3, "gemm_kernels_us": gm * 1e3, "active_experts": n_active,
                                "algorithmic_bytes": b, "gemm_gbs": b / (gm * 1e-3) / 1e9,

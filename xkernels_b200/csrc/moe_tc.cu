@@ -47,7 +47,8 @@ constexpr int kCtrlWarps = 6;      // weight producer, token producer, up to fou
 constexpr int kPackedStageBytes = kTileRows * (kStageK / 2);  // 16 KiB
 constexpr int kScaleStageBytes = kTileRows * (kStageK / 32) * 2;  // 2 KiB
 
-template <int BT> struct TcCfg {
+// MATS = weight matrices that alternate 256-K stages inside one tile (2 in the MXFP4 gate_up mode)
+template <int BT, int MATS = 1> struct TcCfg {
   // Token (B operand) ring: a stage holds kBSub sub-tiles of [BT x 64]; small token tiles
   // are loaded several at a time so that one barrier round trip covers up to 256 K.  With two
   // MMA issuers kBSub must be a multiple of 2 (each issuer waits/releases once per stage).
@@ -65,7 +66,7 @@ template <int BT> struct TcCfg {
   static constexpr int kWGs = (BT <= 32) ? 2 : 4;
   static constexpr int kDequantWarps = 4 * kWGs;
   static constexpr int kThreads = 32 * (kCtrlWarps + kDequantWarps);
-  static constexpr int kAcc = kIssuers;
+  static constexpr int kAcc = kIssuers * MATS;   // accumulator a = issuer * MATS + matrix
   static constexpr int kDCols = kAcc * BT;
   static constexpr int kTmemCols = (BT <= 32) ? 256 : 512;
   static constexpr int kASlots = (BT <= 32) ? 4 : 8;     // multiple of kIssuers and of kWGs
@@ -94,16 +95,28 @@ namespace {
 #define TRACE(role, tag) do {} while (0)
 #endif
 
+// Kernel modes: which weights are streamed and what the epilogue does.
+constexpr int kModeInt4 = 0;      // INT4 W4A16: rows = N, bf16 group scales by TMA, fp32 slot rows out
+constexpr int kModeMxGateUp = 1;  // MXFP4 w13: a tile is 128 gate rows + the 128 matching up rows, the
+                                  // two matrices alternate 256-K stages and accumulators; SwiGLU epilogue
+constexpr int kModeMxDown = 2;    // MXFP4 w2: rows = hidden, bf16-rounded result x routing weight out
+
 struct TcParams {
   const int32_t* sorted_ids;
   const int32_t* expert_ids;
   const int32_t* num_post;
   const float* topk_w;
-  float* scratch;
+  float* scratch;               // [M*top_k, N] fp32 slot rows (INT4, MX down)
   int* status;
   int64_t numel;
-  int N, K;
+  int N, K;                     // tile rows are taken from N rows per expert; K = contraction length
   int mul_w;
+  // MXFP4 only
+  const uint8_t* mx_scale;      // e8m0 scales of the streamed matrix, [E, rows_per_expert, K/32]
+  const __nv_bfloat16* bias;    // b13 [E, 2*ispp] or b2 [E, hidden] or nullptr
+  __nv_bfloat16* act;           // gate_up mode output: [positions, N] bf16 in the K-permuted order
+  int rows_per_expert;          // 2*ispp (gate_up) or hidden (down)
+  float limit;                  // SwiGLU clamp, <= 0 disables
 };
 
 // (x & 0x000F000F) | 0x43004300  ->  two bf16 values 128 + nibble
@@ -120,11 +133,43 @@ __device__ __forceinline__ uint32_t dequant_pair(uint32_t biased, uint32_t scale
   return *reinterpret_cast<const uint32_t*>(&w);
 }
 
-template <int BT>
-__global__ void __launch_bounds__(TcCfg<BT>::kThreads, (BT <= 32) ? 2 : 1)
-int4_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_constant__ CUtensorMap tm_scale,
+// ---- MXFP4: E2M1 code -> bf16 -------------------------------------------------------------
+// The three magnitude bits (e1 e0 m) placed at bf16 bits 8..6 read as  e2m1 * 2^-126  (the code
+// 0b001 = 0.5 lands on the bf16 subnormal 2^-127), the sign bit goes to bit 15.  Multiplying by
+// 2^(s-1) = 2^126 * 2^(s-127) then gives e2m1 * 2^(s-127) exactly; the power of two is split in
+// two bf16 factors so that every e8m0 byte, 0 and 254 included, stays in range (0xFF -> 0).
+__device__ __forceinline__ void mx_scale_factors(uint32_t s, uint32_t& c1, uint32_t& c2) {
+  const int e = (int)s - 1;
+  const int e1 = e >> 1, e2 = e - e1;
+  uint32_t b1 = (uint32_t)(e1 + 127) << 7;
+  const uint32_t b2 = (uint32_t)(e2 + 127) << 7;
+  if (s == 0xFFu) b1 = 0;
+  c1 = b1 | (b1 << 16);
+  c2 = b2 | (b2 << 16);
+}
+__device__ __forceinline__ uint32_t mx_pair(uint32_t mag_shifted, uint32_t sign_shifted, uint32_t c1, uint32_t c2) {
+  uint32_t t;
+  asm("lop3.b32 %0, %1, 0x01C001C0, 0, 0xC0;" : "=r"(t) : "r"(mag_shifted));            // a & b
+  asm("lop3.b32 %0, %0, %1, 0x80008000, 0xF8;" : "+r"(t) : "r"(sign_shifted));           // a | (b & c)
+  const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(&t);
+  const __nv_bfloat162 w = __hmul2(__hmul2(v, *reinterpret_cast<const __nv_bfloat162*>(&c1)),
+                                   *reinterpret_cast<const __nv_bfloat162*>(&c2));
+  return *reinterpret_cast<const uint32_t*>(&w);
+}
+// One packed word (8 codes) -> 4 registers in the nibble order (0,4),(1,5),(2,6),(3,7).
+__device__ __forceinline__ void mx_word(uint32_t x, uint32_t c1, uint32_t c2, uint32_t& r0, uint32_t& r1,
+                                        uint32_t& r2, uint32_t& r3) {
+  r0 = mx_pair(x << 6, x << 12, c1, c2);
+  r1 = mx_pair(x << 2, x << 8, c1, c2);
+  r2 = mx_pair(x >> 2, x << 4, c1, c2);
+  r3 = mx_pair(x >> 6, x, c1, c2);
+}
+
+template <int BT, int MODE>
+__global__ void __launch_bounds__(TcCfg<BT, (MODE == 1 ? 2 : 1)>::kThreads, (BT <= 32) ? 2 : 1)
+moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_constant__ CUtensorMap tm_scale,
                const __grid_constant__ CUtensorMap tm_tokens, const TcParams p) {
-  using Cfg = TcCfg<BT>;
+  using Cfg = TcCfg<BT, (MODE == kModeMxGateUp ? 2 : 1)>;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                                          ~uintptr_t(1023));
@@ -159,7 +204,7 @@ int4_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_const
     mbar_fence_init();
   }
   if (warp == 1) tmem_alloc(tmem_slot, Cfg::kTmemCols);
-  if (warp == 0 && lane == 0) { prefetch_tensormap(&tm_packed); prefetch_tensormap(&tm_scale); }
+  if (warp == 0 && lane == 0) { prefetch_tensormap(&tm_packed); if (MODE == kModeInt4) prefetch_tensormap(&tm_scale); }
   if (warp == 1 && lane == 0) prefetch_tensormap(&tm_tokens);
   tc_fence_before();
   __syncthreads();
@@ -170,6 +215,17 @@ int4_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_const
   const int n_blocks = p.num_post[0] / BT;
   const int64_t total_tiles = (int64_t)n_blocks * n_tiles;
   const int k_stages = p.K / kStageK;
+  // "virtual" weight stages of a tile: gate_up mode alternates the gate and the up matrix
+  constexpr int kMats = (MODE == kModeMxGateUp) ? 2 : 1;
+  const int v_stages = kMats * k_stages;
+  static_assert(MODE != kModeMxGateUp || Cfg::kBSub == kSubs, "gate_up mode needs 256-K token stages");
+  // first weight row (in the [E * rows_per_expert] row space) of virtual stage vs of tile (b, nt)
+  auto tile_row = [&](int b, int nt, int vs) -> int {
+    const int e = p.expert_ids[b];
+    if (MODE == kModeInt4) return e * p.N + nt * kTileRows;
+    if (MODE == kModeMxDown) return e * p.rows_per_expert + nt * kTileRows;
+    return e * p.rows_per_expert + (vs & 1) * p.N + nt * kTileRows;  // gate rows, then up rows
+  };
 
   if (warp == 0) {
     // ---------------- weight producer ----------------
@@ -177,14 +233,20 @@ int4_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_const
       uint32_t st = 0, ph = 0;
       for (int64_t t = blockIdx.x; t < total_tiles && !guard.aborted(); t += gridDim.x) {
         const int nt = (int)(t % n_tiles), b = (int)(t / n_tiles);
-        const int row0 = p.expert_ids[b] * p.N + nt * kTileRows;
-        for (int ks = 0; ks < k_stages; ++ks) {
+        for (int vs = 0; vs < v_stages; ++vs) {
+          const int ks = vs / kMats;
+          const int row0 = tile_row(b, nt, vs);
           TRACE(0, 1);
           if (!mbar_wait(&w_empty[st], ph ^ 1, guard, 1, 400)) break;
           TRACE(0, 2);
-          mbar_expect_tx(&w_full[st], kPackedStageBytes + kScaleStageBytes);
-          tma_load_2d(s_packed + st * kPackedStageBytes, &tm_packed, &w_full[st], ks * (kStageK / 2), row0);
-          tma_load_2d(s_scale + st * kScaleStageBytes, &tm_scale, &w_full[st], ks * (kStageK / 32), row0);
+          if (MODE == kModeInt4) {
+            mbar_expect_tx(&w_full[st], kPackedStageBytes + kScaleStageBytes);
+            tma_load_2d(s_packed + st * kPackedStageBytes, &tm_packed, &w_full[st], ks * (kStageK / 2), row0);
+            tma_load_2d(s_scale + st * kScaleStageBytes, &tm_scale, &w_full[st], ks * (kStageK / 32), row0);
+          } else {  // MXFP4 scales are read straight from global memory by the dequantisers
+            mbar_expect_tx(&w_full[st], kPackedStageBytes);
+            tma_load_2d(s_packed + st * kPackedStageBytes, &tm_packed, &w_full[st], ks * (kStageK / 2), row0);
+          }
           if (++st == kWStages) { st = 0; ph ^= 1; }
         }
       }
@@ -217,35 +279,41 @@ int4_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_const
       constexpr uint32_t idesc = umma_idesc_bf16(kTileRows, BT);
       constexpr int kStep = Cfg::kIssuers;
       uint32_t bst = 0, bph = 0, aq = me, aph = 0, eph = 0;
-      const uint32_t d_tmem = tmem_base + me * BT;
       for (int64_t t = blockIdx.x; t < total_tiles && !guard.aborted(); t += gridDim.x) {
         // the previous tile's accumulators must have been read out by every epilogue thread
         bool ok = mbar_wait(d_empty, eph ^ 1, guard, 8, 100);
         eph ^= 1;
         if (ok) tc_fence_after();
-        for (int s = me; s < k_stages * kSubs && ok; s += kStep) {
-          const int bsub = s % Cfg::kBSub;
+        // slices of the tile in order: virtual stage vs = v / 4 (gate_up: even = gate, odd = up),
+        // slice sub = v % 4; this issuer takes every kStep-th one
+        for (int v = me; v < v_stages * kSubs && ok; v += kStep) {
+          const int vs = v / kSubs, sub = v % kSubs;
+          const int mat = vs % kMats;                       // which matrix this stage belongs to
+          const int bsub = sub % Cfg::kBSub;                // sub-tile inside the token stage
           TRACE(2, 1);
           ok = mbar_wait(&a_full[aq], aph, guard, 3, 100);
           TRACE(2, 2);
           // first slice of this issuer inside a token stage: the stage must have landed
-          if (ok && bsub < kStep) ok = mbar_wait(&b_full[bst], bph, guard, 4);
+          // (in gate_up mode the up stage re-uses the token stage of the gate stage before it)
+          if (ok && mat == 0 && bsub < kStep) ok = mbar_wait(&b_full[bst], bph, guard, 4);
           if (!ok) break;
           tc_fence_after();
           TRACE(2, 3);
+          const uint32_t d_tmem = tmem_base + (uint32_t)((me * kMats + mat) * BT);
           const uint32_t a_tmem = tmem_base + Cfg::kACol0 + aq * kAColsPerSlot;
           const uint64_t b_desc =
               umma_desc_k_sw128(smem_u32(s_tokens + bst * Cfg::kBStageBytes + bsub * Cfg::kBSubBytes));
+          const bool first = (vs < kMats) && (sub == me);   // first MMA into this accumulator
 #pragma unroll
-          for (int kk = 0; kk < kSubK / 16; ++kk)  // the first MMA of a tile overwrites the accumulator
-            umma_ts_bf16(d_tmem, a_tmem + kk * 8, b_desc + (uint64_t)(kk * 2), idesc, (s != me || kk != 0) ? 1u : 0u);
+          for (int kk = 0; kk < kSubK / 16; ++kk)
+            umma_ts_bf16(d_tmem, a_tmem + kk * 8, b_desc + (uint64_t)(kk * 2), idesc, (first && kk == 0) ? 0u : 1u);
           TRACE(2, 4);
           tc_commit(&a_empty[aq]);
           TRACE(2, 5);
           aq += kStep;
           if (aq >= (uint32_t)Cfg::kASlots) { aq -= Cfg::kASlots; aph ^= 1; }
-          // last slice of this issuer inside the token stage: release it
-          if (bsub + kStep >= Cfg::kBSub) {
+          // last slice of this issuer inside the token stage (of the last matrix): release it
+          if (mat == kMats - 1 && bsub + kStep >= Cfg::kBSub) {
             tc_commit(&b_empty[bst]);
             if (++bst == Cfg::kBStages) { bst = 0; bph ^= 1; }
           }
@@ -266,16 +334,32 @@ int4_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_const
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     uint32_t wst = 0, wph = 0, dph = 0;
     uint32_t aq = wg, aph = 0;                 // next slot of this warpgroup and its phase
+    // MXFP4: the 8 e8m0 bytes of this row for one 256-K stage, fetched one stage ahead
+    auto mx_scale_load = [&](int64_t t, int vs) -> uint2 {
+      const int nt = (int)(t % n_tiles), b = (int)(t / n_tiles);
+      const int64_t grow = (int64_t)tile_row(b, nt, vs) + row;
+      return __ldg(reinterpret_cast<const uint2*>(p.mx_scale + grow * (p.K / 32) + (vs / kMats) * (kStageK / 32)));
+    };
+    uint2 mx_next = make_uint2(0, 0);
+    if (MODE != kModeInt4 && (int64_t)blockIdx.x < total_tiles) mx_next = mx_scale_load(blockIdx.x, 0);
     for (int64_t t = blockIdx.x; t < total_tiles; t += gridDim.x) {
       const int nt = (int)(t % n_tiles), b = (int)(t / n_tiles);
       bool ok = true;
-      for (int ks = 0; ks < k_stages && ok; ++ks) {
+      for (int vs = 0; vs < v_stages && ok; ++vs) {
         if (lane == 0 && quarter == 0) TRACE(3 + wg, 1);
         if (!mbar_wait(&w_full[wst], wph, guard, 5)) { ok = false; break; }
         if (lane == 0 && quarter == 0) TRACE(3 + wg, 2);
         const unsigned char* pk = s_packed + wst * kPackedStageBytes + row * 128;
-        const uint4 sc = *reinterpret_cast<const uint4*>(s_scale + wst * kScaleStageBytes + row * 16);
-        const uint32_t sc_w[4] = {sc.x, sc.y, sc.z, sc.w};
+        uint32_t sc_w[4] = {0, 0, 0, 0};
+        uint64_t mx_sc = 0;
+        if (MODE == kModeInt4) {
+          const uint4 sc = *reinterpret_cast<const uint4*>(s_scale + wst * kScaleStageBytes + row * 16);
+          sc_w[0] = sc.x; sc_w[1] = sc.y; sc_w[2] = sc.z; sc_w[3] = sc.w;
+        } else {
+          mx_sc = (uint64_t)mx_next.x | ((uint64_t)mx_next.y << 32);
+          if (vs + 1 < v_stages) mx_next = mx_scale_load(t, vs + 1);
+          else if (t + gridDim.x < total_tiles) mx_next = mx_scale_load(t + gridDim.x, 0);
+        }
 #pragma unroll
         for (int i = 0; i < kSubs / Cfg::kWGs; ++i) {
           const int sub = wg + Cfg::kWGs * i;
@@ -284,7 +368,7 @@ int4_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_const
           tc_fence_after();
           if (lane == 0 && quarter == 0) TRACE(3 + wg, 4);
           const uint32_t dst = tmem_base + lane_base + Cfg::kACol0 + aq * kAColsPerSlot;
-          uint32_t sw = sc_w[0];  // the two group scales of slice `sub` (static indices only)
+          uint32_t sw = sc_w[0];  // INT4: the two group scales of slice `sub` (static indices only)
 #pragma unroll
           for (int q = 1; q < kSubs; ++q)
             if (q == sub) sw = sc_w[q];
@@ -292,16 +376,28 @@ int4_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_const
           for (int h = 0; h < 2; ++h) {
             const int chunk = sub * 2 + h;  // 16-byte chunk = 32 weights = one scale group
             const uint4 w4 = *reinterpret_cast<const uint4*>(pk + ((chunk ^ (row & 7)) << 4));
-            const uint32_t s2 = h ? __byte_perm(sw, sw, 0x3232) : __byte_perm(sw, sw, 0x1010);
             const uint32_t words[4] = {w4.x, w4.y, w4.z, w4.w};
+            if (MODE == kModeInt4) {
+              const uint32_t s2 = h ? __byte_perm(sw, sw, 0x3232) : __byte_perm(sw, sw, 0x1010);
 #pragma unroll
-            for (int wp = 0; wp < 2; ++wp) {  // two words = 16 weights = 8 columns
-              const uint32_t x0 = words[2 * wp], x1 = words[2 * wp + 1];
-              tmem_st_32x8(dst + h * 16 + wp * 8,
-                           dequant_pair(nib_pair(x0), s2), dequant_pair(nib_pair(x0 >> 4), s2),
-                           dequant_pair(nib_pair(x0 >> 8), s2), dequant_pair(nib_pair(x0 >> 12), s2),
-                           dequant_pair(nib_pair(x1), s2), dequant_pair(nib_pair(x1 >> 4), s2),
-                           dequant_pair(nib_pair(x1 >> 8), s2), dequant_pair(nib_pair(x1 >> 12), s2));
+              for (int wp = 0; wp < 2; ++wp) {  // two words = 16 weights = 8 columns
+                const uint32_t x0 = words[2 * wp], x1 = words[2 * wp + 1];
+                tmem_st_32x8(dst + h * 16 + wp * 8,
+                             dequant_pair(nib_pair(x0), s2), dequant_pair(nib_pair(x0 >> 4), s2),
+                             dequant_pair(nib_pair(x0 >> 8), s2), dequant_pair(nib_pair(x0 >> 12), s2),
+                             dequant_pair(nib_pair(x1), s2), dequant_pair(nib_pair(x1 >> 4), s2),
+                             dequant_pair(nib_pair(x1 >> 8), s2), dequant_pair(nib_pair(x1 >> 12), s2));
+              }
+            } else {
+              uint32_t c1, c2;
+              mx_scale_factors((uint32_t)(mx_sc >> (8 * chunk)) & 0xFFu, c1, c2);
+#pragma unroll
+              for (int wp = 0; wp < 2; ++wp) {
+                uint32_t r[8];
+                mx_word(words[2 * wp], c1, c2, r[0], r[1], r[2], r[3]);
+                mx_word(words[2 * wp + 1], c1, c2, r[4], r[5], r[6], r[7]);
+                tmem_st_32x8(dst + h * 16 + wp * 8, r[0], r[1], r[2], r[3], r[4], r[5], r[6], r[7]);
+              }
             }
           }
           if (i == kSubs / Cfg::kWGs - 1) {  // last read of this stage is done: one arrival per warp
@@ -320,32 +416,73 @@ int4_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_const
         if (++wst == kWStages) { wst = 0; wph ^= 1; }
       }
       if (!ok) break;
-      // epilogue (the warpgroups take the 16-column groups round robin):
-      // sum of the kAcc accumulators -> x topk_w -> fp32 slot rows
+      // ---- epilogue (the warpgroups take the 16-column groups round robin) ----
       if (!mbar_wait(d_full, dph, guard, 7)) break;
       dph ^= 1;
       tc_fence_after();
       const int64_t n_glob = (int64_t)nt * kTileRows + row;
       const int32_t* slots = p.sorted_ids + (int64_t)b * BT;
+      float bias0 = 0.f, bias1 = 0.f;
+      if (MODE != kModeInt4 && p.bias != nullptr) {
+        const int64_t e_row = (int64_t)p.expert_ids[b] * p.rows_per_expert;
+        bias0 = __bfloat162float(p.bias[e_row + n_glob]);
+        if (MODE == kModeMxGateUp) bias1 = __bfloat162float(p.bias[e_row + p.N + n_glob]);
+      }
 #pragma unroll 1
       for (int c0 = wg * 16; c0 < BT; c0 += 16 * Cfg::kWGs) {
-        uint32_t acc[16];
+        // acc = matrix 0 (INT4 / down: the only one; gate_up: gate), more = matrix 1 (up); each is
+        // the sum over the issuers' accumulators
+        uint32_t acc[16], more[16];
         tmem_ld_32x16(tmem_base + lane_base + c0, acc);
         tmem_wait_ld();
-#pragma unroll
-        for (int a = 1; a < Cfg::kAcc; ++a) {
-          uint32_t more[16];
-          tmem_ld_32x16(tmem_base + lane_base + a * BT + c0, more);
+        if (kMats > 1) {
+          tmem_ld_32x16(tmem_base + lane_base + BT + c0, more);
           tmem_wait_ld();
-#pragma unroll
-          for (int j = 0; j < 16; ++j) acc[j] = __float_as_uint(__uint_as_float(acc[j]) + __uint_as_float(more[j]));
         }
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int32_t slot = __ldg(slots + c0 + j);  // same address for the whole warp
-          if (slot >= 0 && slot < p.numel) {
+        for (int is = 1; is < Cfg::kIssuers; ++is) {
+          uint32_t part[16];
+          tmem_ld_32x16(tmem_base + lane_base + (is * kMats) * BT + c0, part);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) acc[j] = __float_as_uint(__uint_as_float(acc[j]) + __uint_as_float(part[j]));
+          if (kMats > 1) {
+            tmem_ld_32x16(tmem_base + lane_base + (is * kMats + 1) * BT + c0, part);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) more[j] = __float_as_uint(__uint_as_float(more[j]) + __uint_as_float(part[j]));
+          }
+        }
+        if (MODE == kModeMxGateUp) {
+          // acc = gate, more = up.  Rounding points of the reference
+          // (src/xkernels/ops/moe/mxfp4_reference.py:92-100): gate_up to bf16, (+ bf16 bias, rounded),
+          // fp32 clamp and silu(gate) * up, then bf16.  The activation goes out in the K order the
+          // down GEMM's dequantiser produces: element j of a group of 8 at ((j & 3) << 1) | (j >> 2).
+          const int64_t col = (n_glob & ~int64_t(7)) | (((n_glob & 3) << 1) | ((n_glob >> 2) & 1));
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int32_t slot = __ldg(slots + c0 + j);
+            if (slot < 0 || slot >= p.numel) continue;
+            float g = round_to_bf16(__uint_as_float(acc[j]));
+            float u = round_to_bf16(__uint_as_float(more[j]));
+            if (p.bias != nullptr) { g = round_to_bf16(g + bias0); u = round_to_bf16(u + bias1); }
+            if (p.limit > 0.f) { g = fminf(g, p.limit); u = fminf(fmaxf(u, -p.limit), p.limit); }
+            const float silu = g / (1.f + expf(-g));
+            p.act[((int64_t)b * BT + c0 + j) * p.N + col] = __float2bfloat16_rn(silu * u);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int32_t slot = __ldg(slots + c0 + j);  // same address for the whole warp
+            if (slot < 0 || slot >= p.numel) continue;
             float v = __uint_as_float(acc[j]);
-            if (p.mul_w) v = p.topk_w[slot] * v;
+            if (MODE == kModeMxDown) {  // reference rounds `down` to bf16, adds the bf16 bias, then x w
+              v = round_to_bf16(v);
+              if (p.bias != nullptr) v = round_to_bf16(v + bias0);
+              if (p.mul_w) v = v * p.topk_w[slot];
+            } else if (p.mul_w) {
+              v = p.topk_w[slot] * v;
+            }
             p.scratch[(int64_t)slot * p.N + n_glob] = v;
           }
         }
@@ -431,11 +568,11 @@ int make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const 
   return XKB_OK;
 }
 
-template <int BT>
+template <int BT, int MODE>
 int launch_bt(const CUtensorMap& tmp, const CUtensorMap& tms, const CUtensorMap& tmt, const TcParams& prm,
               int64_t max_tiles, cudaStream_t stream) {
-  using Cfg = TcCfg<BT>;
-  XKB_CHECK_CUDA(cudaFuncSetAttribute(int4_tc_kernel<BT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  using Cfg = TcCfg<BT, (MODE == kModeMxGateUp ? 2 : 1)>;
+  XKB_CHECK_CUDA(cudaFuncSetAttribute(moe_tc_kernel<BT, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)Cfg::kSmemBytes));
   int dev = 0, sms = 148;
   XKB_CHECK_CUDA(cudaGetDevice(&dev));
@@ -450,9 +587,9 @@ int launch_bt(const CUtensorMap& tmp, const CUtensorMap& tms, const CUtensorMap&
   if (grid < 1) grid = 1;
   {
     GemmTimerScope timed(stream);
-    int4_tc_kernel<BT><<<(unsigned)grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tmp, tms, tmt, prm);
+    moe_tc_kernel<BT, MODE><<<(unsigned)grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tmp, tms, tmt, prm);
   }
-  XKB_CHECK_LAUNCH("int4_tc_kernel");
+  XKB_CHECK_LAUNCH("moe_tc_kernel");
   return XKB_OK;
 }
 
@@ -513,25 +650,104 @@ int launch_int4_tc(const void* A, const int32_t* packed, const void* scale, cons
   prm.N = (int)N;
   prm.K = (int)K;
   prm.mul_w = mul_w;
+  prm.mx_scale = nullptr;
+  prm.bias = nullptr;
+  prm.act = nullptr;
+  prm.rows_per_expert = (int)N;
+  prm.limit = 0.f;
   const int64_t max_tiles = r.max_blocks * (N / kTileRows);
   switch (r.block) {
-    case 16: return launch_bt<16>(tm_packed, tm_scale, tm_tokens, prm, max_tiles, stream);
-    case 32: return launch_bt<32>(tm_packed, tm_scale, tm_tokens, prm, max_tiles, stream);
-    case 64: return launch_bt<64>(tm_packed, tm_scale, tm_tokens, prm, max_tiles, stream);
-    case 128: return launch_bt<128>(tm_packed, tm_scale, tm_tokens, prm, max_tiles, stream);
-    case 256: return launch_bt<256>(tm_packed, tm_scale, tm_tokens, prm, max_tiles, stream);
+    case 16: return launch_bt<16, kModeInt4>(tm_packed, tm_scale, tm_tokens, prm, max_tiles, stream);
+    case 32: return launch_bt<32, kModeInt4>(tm_packed, tm_scale, tm_tokens, prm, max_tiles, stream);
+    case 64: return launch_bt<64, kModeInt4>(tm_packed, tm_scale, tm_tokens, prm, max_tiles, stream);
+    case 128: return launch_bt<128, kModeInt4>(tm_packed, tm_scale, tm_tokens, prm, max_tiles, stream);
+    case 256: return launch_bt<256, kModeInt4>(tm_packed, tm_scale, tm_tokens, prm, max_tiles, stream);
     default: return fail(XKB_ERR_ARG, "int4 tcgen05 path: unsupported token tile %d", r.block);
   }
 }
 
-// ---- MXFP4 tcgen05 path: not built yet, the SIMT kernels serve every shape ----
-bool mxfp4_tc_supported(int, int64_t, int64_t, int64_t, int, int) { return false; }
-int mxfp4_tc_block(int64_t, int) { return kSimtBlock; }
-int64_t mxfp4_tc_workspace_bytes(int64_t, int64_t, int64_t, int) { return 256; }
-int launch_mxfp4_tc(const void*, const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, const void*,
-                    const void*, const Routing&, const float*, __nv_bfloat16*, float*, int64_t, int64_t, int, int,
-                    float, int, void*, int*, cudaStream_t) {
-  return fail(XKB_ERR_ARG, "the MXFP4 tcgen05 path is not available");
+// ---------------------------------------------------------------------------
+// MXFP4: gate_up GEMM with fused SwiGLU, then down GEMM, both on the same pipeline
+// ---------------------------------------------------------------------------
+bool mxfp4_tc_supported(int a_dtype, int64_t M, int64_t hidden, int64_t ispp, int E, int top_k) {
+  return a_dtype == XKB_BF16 && M > 0 && E > 0 && top_k > 0 && hidden > 0 && ispp > 0 &&
+         hidden % kStageK == 0 && ispp % kStageK == 0 &&   // both are contraction lengths and tile-row counts
+         (int64_t)E * 2 * ispp < (1ll << 31) && (int64_t)E * hidden < (1ll << 31);
+}
+
+int mxfp4_tc_block(int64_t numel, int E) {
+  // the gate_up mode needs two issuers and 256-K token stages: token tiles up to 32
+  const double avg = (double)numel / (E > 0 ? E : 1);
+  return avg <= 12 ? 16 : 32;
+}
+
+int64_t mxfp4_tc_workspace_bytes(int64_t numel, int64_t hidden, int64_t ispp, int E) {
+  (void)ispp;
+  return align_up((numel + (int64_t)(E + 1) * 255) * hidden * 2, 256);  // gathered activations
+}
+
+int launch_mxfp4_tc(const void* A, const uint8_t* w13, const uint8_t* w13_scale, const uint8_t* w2,
+                    const uint8_t* w2_scale, const void* b13, const void* b2, const Routing& r,
+                    const float* topk_w, __nv_bfloat16* act, float* scratch, int64_t hidden, int64_t ispp,
+                    int E, int top_k, float limit, int mul_w, void* tc_ws, int* status, cudaStream_t stream) {
+  XKB_REQUIRE(r.block == 16 || r.block == 32, "mxfp4 tcgen05 path: unsupported token tile %d", r.block);
+  XKB_REQUIRE(reinterpret_cast<uintptr_t>(w13_scale) % 8 == 0 && reinterpret_cast<uintptr_t>(w2_scale) % 8 == 0,
+              "mxfp4 tcgen05 path: scale tensors must be 8-byte aligned");
+  Carver carve(tc_ws);
+  __nv_bfloat16* Ag = carve.take<__nv_bfloat16>(r.max_pad * hidden);
+  int64_t gblocks = r.max_pad < 148 * 16 ? r.max_pad : 148 * 16;
+  if (gblocks < 1) gblocks = 1;
+  gather_permute_kernel<<<(unsigned)gblocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(A),
+                                                               r.sorted_ids, r.num_post, Ag, r.numel,
+                                                               (int)hidden, top_k);
+  XKB_CHECK_LAUNCH("gather_permute_kernel");
+
+  CUtensorMap tm_w13, tm_w2, tm_tok0, tm_tok1;
+  int rc = make_map_2d(&tm_w13, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w13, (uint64_t)E * 2 * ispp, (uint64_t)hidden / 2,
+                       kTileRows, kStageK / 2, CU_TENSOR_MAP_SWIZZLE_128B, "w13");
+  if (rc != XKB_OK) return rc;
+  rc = make_map_2d(&tm_w2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w2, (uint64_t)E * hidden, (uint64_t)ispp / 2,
+                   kTileRows, kStageK / 2, CU_TENSOR_MAP_SWIZZLE_128B, "w2");
+  if (rc != XKB_OK) return rc;
+  rc = make_map_2d(&tm_tok0, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, Ag, (uint64_t)r.max_pad, (uint64_t)hidden,
+                   (uint32_t)r.block, kSubK, CU_TENSOR_MAP_SWIZZLE_128B, "gathered activations");
+  if (rc != XKB_OK) return rc;
+  rc = make_map_2d(&tm_tok1, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, act, (uint64_t)r.max_pad, (uint64_t)ispp,
+                   (uint32_t)r.block, kSubK, CU_TENSOR_MAP_SWIZZLE_128B, "SwiGLU activations");
+  if (rc != XKB_OK) return rc;
+
+  TcParams prm;
+  prm.sorted_ids = r.sorted_ids;
+  prm.expert_ids = r.expert_ids;
+  prm.num_post = r.num_post;
+  prm.topk_w = topk_w;
+  prm.status = status;
+  prm.numel = r.numel;
+  prm.mul_w = mul_w;
+  prm.limit = limit;
+  // stage 0: gate_up + SwiGLU -> act
+  prm.scratch = nullptr;
+  prm.act = act;
+  prm.N = (int)ispp;
+  prm.K = (int)hidden;
+  prm.rows_per_expert = (int)(2 * ispp);
+  prm.mx_scale = w13_scale;
+  prm.bias = static_cast<const __nv_bfloat16*>(b13);
+  int64_t max_tiles = r.max_blocks * (ispp / kTileRows);
+  rc = (r.block == 16) ? launch_bt<16, kModeMxGateUp>(tm_w13, tm_w13, tm_tok0, prm, max_tiles, stream)
+                       : launch_bt<32, kModeMxGateUp>(tm_w13, tm_w13, tm_tok0, prm, max_tiles, stream);
+  if (rc != XKB_OK) return rc;
+  // stage 1: down -> fp32 slot rows
+  prm.scratch = scratch;
+  prm.act = nullptr;
+  prm.N = (int)hidden;
+  prm.K = (int)ispp;
+  prm.rows_per_expert = (int)hidden;
+  prm.mx_scale = w2_scale;
+  prm.bias = static_cast<const __nv_bfloat16*>(b2);
+  max_tiles = r.max_blocks * (hidden / kTileRows);
+  return (r.block == 16) ? launch_bt<16, kModeMxDown>(tm_w2, tm_w2, tm_tok1, prm, max_tiles, stream)
+                         : launch_bt<32, kModeMxDown>(tm_w2, tm_w2, tm_tok1, prm, max_tiles, stream);
 }
 
 }  // namespace xkb
