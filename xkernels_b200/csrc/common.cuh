@@ -82,9 +82,10 @@ int64_t align_workspace_bytes(int64_t numel, int num_experts);
 
 // out[m,n] = sum_j scratch[m*top_k+j, n] over the slots that are local
 // (expert_map NULL or expert_map[topk_ids[slot]] >= 0), ascending j, fp32.
+// `parts` copies of the slot rows (part p at scratch + p*M*top_k*N) are added up, part-major inside a slot.
 int launch_combine(const float* scratch, const int32_t* topk_ids, const int32_t* expert_map,
                    int num_map, void* out, int out_dtype, int64_t M, int top_k, int64_t N,
-                   cudaStream_t stream);
+                   cudaStream_t stream, int parts = 1);
 
 // Records one event pair of the optional GEMM timer (xkb_gemm_timer_enable) around
 // the launches made while it is alive; does nothing when the timer is not armed.
