@@ -190,8 +190,9 @@ def workload_config(cfg, world: int):
                 "parallelism": "single GPU"}
     return {"workload": (f"int4_w4a16 expert-parallel: E={cfg.E} over {world} GPUs, K={cfg.K} N={cfg.N} "
                          f"top_k={cfg.top_k}, {cfg.M // world} tokens per GPU, zipf(1.1)*2.0 expert bias"),
+            "expert_placement": "see the ep key",
             "l2": "per-rank weights exceed the 126 MB L2, no flush needed",
-            "parallelism": f"ep{world} (experts sharded contiguously, NCCL all-to-all dispatch/combine)"}
+            "parallelism": f"ep{world} (E/W experts per rank, NCCL all-to-all dispatch/combine)"}
 
 
 # --------------------------------------------------------------------------------------
@@ -385,13 +386,25 @@ def run_multi_gpu(args, world: int, rank: int, local_rank: int):
     peaks = load_peaks()
     cfg = synth.CONFIGS["int4_ep"]
     e_local = cfg.E // world
-    lo, hi = rank * e_local, (rank + 1) * e_local
-    # every rank: its own tokens/routing (seeded by rank), its own expert shard
+    # every rank: its own tokens/routing (seeded by rank) and its experts.  Weights are synthetic, so
+    # each rank simply draws E/W experts; which GLOBAL ids they stand for is fixed by the placement.
     A = synth.activations(cfg.M, cfg.K, seed=1729 + 100 * rank, device=dev)
     ids, w = synth.routing(cfg.M, cfg.E, cfg.top_k, seed=1732 + 100 * rank, device=dev, zipf_scale=cfg.zipf_scale)
-    packed, scale = synth.int4_weights(e_local, cfg.N, cfg.K, cfg.group_size, seed=1730 + 7 * lo, device=dev)
+    packed, scale = synth.int4_weights(e_local, cfg.N, cfg.K, cfg.group_size, seed=1730 + 7 * rank, device=dev)
     layer = ep.ExpertParallelInt4(packed, scale, num_global_experts=cfg.E, group=dist.group.WORLD,
-                                  group_size=cfg.group_size)
+                                  group_size=cfg.group_size, placement=args.ep_placement, chunks=args.ep_chunks)
+
+    # reference point for scaling: the SAME configuration on one GPU (all 256 experts local, 4096
+    # tokens, no exchange), timed on rank 0 before the group run
+    single = None
+    if rank == 0:
+        import xkernels_b200 as xkb
+        pk1, sc1 = synth.int4_weights(cfg.E, cfg.N, cfg.K, cfg.group_size, seed=99, device=dev)
+        t1 = time_call(lambda: xkb.fused_moe_int4_w4a16(A, pk1, sc1, ids, w, group_size=cfg.group_size), 3, 10)
+        single = {"tokens_per_s": cfg.M / (t1 * 1e-3), "ms_per_step": t1}
+        del pk1, sc1
+        torch.cuda.empty_cache()
+    dist.barrier()
 
     def step(_i):
         return layer(A, ids, w)
@@ -462,6 +475,8 @@ def run_multi_gpu(args, world: int, rank: int, local_rank: int):
                          "kernel": "int4_tc_kernel (busiest rank)", "kernel_ms": gemm_max,
                          "peak_source": peaks["source"] + " (sustained)"},
             "slots_received_per_rank": slots,
+            "ep": {"placement": args.ep_placement, "chunks": args.ep_chunks,
+                   "same_config_on_one_gpu": single},
         }
         print(json.dumps(line), flush=True)
     dist.barrier()
@@ -506,6 +521,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the other single-GPU configurations")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    ap.add_argument("--ep-placement", default="round_robin", choices=["contiguous", "round_robin"],
+                    help="expert -> rank assignment of the expert-parallel run")
+    ap.add_argument("--ep-chunks", type=int, default=4, help="token chunks pipelined through the exchanges")
     ap.add_argument("--case", default=None, choices=sorted(PROFILE_CASES),
                     help="run one small profiling case instead of the benchmark")
     args = ap.parse_args()

@@ -44,17 +44,18 @@ def _cpu_reduce(rows, row_index, w, M, dtype):
     return out.to(dtype)
 
 
-def _worker(rank: int, world: int, port: int, fail_rank: int):
+def _worker(rank: int, world: int, port: int, fail_rank: int, placement: str = "contiguous", chunks: int = 1):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         packed, scale = synth.int4_weights(CFG.E, CFG.N, CFG.K, 32, seed=5)      # global experts (same on all ranks)
         e_local = CFG.E // world
-        sl = slice(rank * e_local, (rank + 1) * e_local)
+        sl = torch.tensor(ep.local_expert_ids(rank, e_local, world, placement))
         A = synth.activations(CFG.M, CFG.K, seed=100 + rank)
         ids, w = synth.routing(CFG.M, CFG.E, CFG.top_k, seed=200 + rank, zipf_scale=CFG.zipf_scale)
         layer = ep.ExpertParallelInt4(packed[sl], scale[sl], num_global_experts=CFG.E, group_size=32,
                                       rows_fn=_oracle_rows(packed[sl], scale[sl]), reduce_fn=_cpu_reduce,
+                                      placement=placement, chunks=chunks,
                                       max_recv_slots=0 if rank == fail_rank else None)
         if fail_rank >= 0:
             # capacity check: the overloaded rank raises on the host before any payload moves
@@ -77,20 +78,27 @@ def _worker(rank: int, world: int, port: int, fail_rank: int):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2, 4])
-def test_all_to_all_matches_dense_oracle(world):
-    mp.spawn(_worker, args=(world, _free_port(), -1), nprocs=world, join=True)
+@pytest.mark.parametrize("world,placement,chunks", [(2, "contiguous", 1), (4, "contiguous", 1),
+                                                     (2, "round_robin", 3), (4, "round_robin", 2)])
+def test_all_to_all_matches_dense_oracle(world, placement, chunks):
+    mp.spawn(_worker, args=(world, _free_port(), -1, placement, chunks), nprocs=world, join=True)
 
 
 def test_plan_dispatch_groups_slots_by_owner():
     ids = torch.tensor([[5, 0, 3], [1, 7, 2]], dtype=torch.int32)
     plan = ep.plan_dispatch(ids, experts_per_rank=4, world=2)
-    assert plan.send_counts.tolist() == [4, 2]
+    assert plan.send_counts.tolist() == [[4, 2]]
     assert plan.order.tolist() == [1, 2, 3, 5, 0, 4]          # stable inside a destination
     assert plan.local_expert.tolist() == [0, 3, 1, 2, 1, 3]
     assert plan.token.tolist() == [0, 0, 1, 1, 0, 1]
     with pytest.raises(ValueError):
         ep.plan_dispatch(torch.tensor([[8]], dtype=torch.int32), 4, 2)
+    # round robin: expert g on rank g % 2 as local expert g // 2; two token chunks of one token each
+    plan = ep.plan_dispatch(ids, experts_per_rank=4, world=2, placement="round_robin", chunks=2)
+    assert plan.send_counts.tolist() == [[1, 2], [1, 2]]
+    assert plan.order.tolist() == [1, 0, 2, 5, 3, 4]
+    assert plan.local_expert.tolist() == [0, 2, 1, 1, 0, 3]
+    assert ep.local_expert_ids(1, 4, 2, "round_robin") == [1, 3, 5, 7]
 
 
 def test_receive_capacity_is_checked_on_the_host():
@@ -99,4 +107,4 @@ def test_receive_capacity_is_checked_on_the_host():
     # every rank completes the count exchange, then only the overloaded one refuses; the others would
     # block in the payload exchange, so the test stops after the count phase on all ranks
     plan = ep.plan_dispatch(torch.zeros((4, 2), dtype=torch.int32), 4, 2)
-    assert plan.send_counts.tolist() == [8, 0]
+    assert plan.send_counts.tolist() == [[8, 0]]

@@ -47,7 +47,7 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _ep_worker(rank: int, world: int, port: int):
+def _ep_worker(rank: int, world: int, port: int, placement: str, chunks: int):
     import torch.distributed as dist
 
     from xkernels_b200 import ep
@@ -60,10 +60,11 @@ def _ep_worker(rank: int, world: int, port: int):
         cfg = synth.Int4Config("ep", M=96, K=512, N=256, E=16, top_k=4, zipf_scale=2.0)
         packed, scale = synth.int4_weights(cfg.E, cfg.N, cfg.K, 32, seed=5)      # global, CPU, same on all ranks
         e_local = cfg.E // world
-        sl = slice(rank * e_local, (rank + 1) * e_local)
+        sl = torch.tensor(ep.local_expert_ids(rank, e_local, world, placement))
         A = synth.activations(cfg.M, cfg.K, seed=100 + rank)
         ids, w = synth.routing(cfg.M, cfg.E, cfg.top_k, seed=200 + rank, zipf_scale=cfg.zipf_scale)
-        layer = ep.ExpertParallelInt4(packed[sl].to(dev), scale[sl].to(dev), num_global_experts=cfg.E)
+        layer = ep.ExpertParallelInt4(packed[sl].to(dev), scale[sl].to(dev), num_global_experts=cfg.E,
+                                      placement=placement, chunks=chunks)
         out = layer(A.to(dev), ids.to(dev), w.to(dev))
         ops.check_status(dev)
         want = oracle.moe_w4a16(A, packed, scale, ids, w, 32)
@@ -76,11 +77,12 @@ def _ep_worker(rank: int, world: int, port: int):
         dist.destroy_process_group()
 
 
-def test_all_to_all_on_gpus():
+@pytest.mark.parametrize("placement,chunks", [("contiguous", 1), ("round_robin", 3)])
+def test_all_to_all_on_gpus(placement, chunks):
     n = torch.cuda.device_count()
     if n < 2:
         pytest.skip("needs at least 2 GPUs")
     import torch.multiprocessing as mp
 
     world = 4 if n >= 4 else 2
-    mp.spawn(_ep_worker, args=(world, _free_port()), nprocs=world, join=True)
+    mp.spawn(_ep_worker, args=(world, _free_port(), placement, chunks), nprocs=world, join=True)
