@@ -523,7 +523,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--ep-placement", default="round_robin", choices=["contiguous", "round_robin"],
                     help="expert -> rank assignment of the expert-parallel run")
-    ap.add_argument("--ep-chunks", type=int, default=4, help="token chunks pipelined through the exchanges")
+    ap.add_argument("--ep-chunks", type=int, default=1, help="token chunks pipelined through the exchanges")
     ap.add_argument("--case", default=None, choices=sorted(PROFILE_CASES),
                     help="run one small profiling case instead of the benchmark")
     args = ap.parse_args()
