@@ -44,7 +44,7 @@ constexpr int kSubK = 64;        // K per token stage / tensor-memory A slot
 constexpr int kSubs = kStageK / kSubK;
 constexpr int kAColsPerSlot = kSubK / 2;               // 32 columns of bf16 pairs per A slot
 constexpr int kWStages = 4;
-constexpr int kCtrlWarps = 6;      // weight producer, token producer, up to four MMA issuers
+constexpr int kCtrlWarps = 4;      // weight producer, token producer (+ tensor-memory owner), two MMA issuers
 constexpr int kPackedStageBytes = kTileRows * (kStageK / 2);  // 16 KiB
 constexpr int kScaleStageBytes = kTileRows * (kStageK / 32) * 2;  // 2 KiB
 
@@ -62,14 +62,16 @@ template <int BT, int MATS = 1> struct TcCfg {
   // take alternate K slices, each into its own accumulator (summed in the epilogue).
   static constexpr int kIssuers = (BT <= 64) ? 2 : 1;
   // Dequantiser warpgroups (4 warps each).  Two CTAs share an SM for narrow tiles (2 x 2
-  // warpgroups); wider tiles run one CTA per SM with four.  Warpgroup w owns the K slices
-  // sub = w, w + kWGs, ... of every 256-wide stage.
-  static constexpr int kWGs = (BT <= 32) ? 2 : 4;
+  // warpgroups); wider tiles run one CTA per SM with four.  K slice g (numbered across stages and
+  // tiles) belongs to warpgroup g % kWGs; kWGs divides the four slices of a stage.
+  static constexpr int kWGs = (BT <= 32) ? 2 : 4;   // (three per CTA at 64 registers measured slower: 283 vs 245 us)
+  static_assert(kSubs % kWGs == 0, "the warpgroups must divide the slices of a stage");
   static constexpr int kDequantWarps = 4 * kWGs;
   static constexpr int kThreads = 32 * (kCtrlWarps + kDequantWarps);
   static constexpr int kAcc = kIssuers * MATS;   // accumulator a = issuer * MATS + matrix
   static constexpr int kTmemCols = (BT <= 32) ? 256 : 512;
-  static constexpr int kASlots = (BT <= 32) ? 4 : 8;     // multiple of kIssuers and of kWGs
+  // ring of A slots: a multiple of kIssuers and of kWGs; the narrowest tile has room for six
+  static constexpr int kASlots = (BT <= 32) ? 6 : 8;
   // Two accumulator sets when tensor memory has room: the MMAs of the next tile start while the
   // previous tile's accumulators are still being read out.
   static constexpr int kDBuf = (2 * kAcc * BT + kASlots * kAColsPerSlot <= kTmemCols) ? 2 : 1;
@@ -457,7 +459,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
         }
 #pragma unroll
         for (int i = 0; i < kSubs / Cfg::kWGs; ++i) {
-          const int sub = wg + Cfg::kWGs * i;
+          const int sub = wg + Cfg::kWGs * i;  // kWGs divides 4: the same slices in every stage
           if (lane == 0 && quarter == 0) TRACE(3 + wg, 3);
           if (!mbar_wait(&a_empty[aq], aph ^ 1, guard, 6)) { ok = false; break; }
           tc_fence_after();
@@ -495,10 +497,6 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
               }
             }
           }
-          if (i == kSubs / Cfg::kWGs - 1) {  // last read of this stage is done: one arrival per warp
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&w_empty[wst]);
-          }
           if (lane == 0 && quarter == 0) TRACE(3 + wg, 5);
           tmem_wait_st();
           tc_fence_before();
@@ -508,6 +506,8 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
           aq += Cfg::kWGs;
           if (aq >= (uint32_t)Cfg::kASlots) { aq -= Cfg::kASlots; aph ^= 1; }
         }
+        __syncwarp();  // every lane has read its part of the stage: one arrival per warp
+        if (lane == 0) mbar_arrive(&w_empty[wst]);
         if (++wst == kWStages) { wst = 0; wph ^= 1; }
         if (vs == 0 && pend) {  // previous tile's epilogue, one stage into this tile
           pend = false;
@@ -715,9 +715,10 @@ bool mxfp4_tc_supported(int a_dtype, int64_t M, int64_t hidden, int64_t ispp, in
 }
 
 int mxfp4_tc_block(int64_t numel, int E) {
-  // the gate_up mode needs two issuers and 256-K token stages: token tiles up to 32
-  const double avg = (double)numel / (E > 0 ? E : 1);
-  return avg <= 12 ? 16 : 32;
+  // the gate_up mode keeps four accumulators beside the six A slots in 256 tensor-memory columns:
+  // token tiles of 16 (experts with more tokens take several blocks and re-read their weights from L2)
+  (void)numel; (void)E;
+  return 16;
 }
 
 int64_t mxfp4_tc_workspace_bytes(int64_t numel, int64_t hidden, int64_t ispp, int E) {
@@ -729,7 +730,7 @@ int launch_mxfp4_tc(const void* A, const uint8_t* w13, const uint8_t* w13_scale,
                     const uint8_t* w2_scale, const void* b13, const void* b2, const Routing& r,
                     const float* topk_w, __nv_bfloat16* act, float* scratch, int64_t hidden, int64_t ispp,
                     int E, int top_k, float limit, int mul_w, void* tc_ws, int* status, cudaStream_t stream) {
-  XKB_REQUIRE(r.block == 16 || r.block == 32, "mxfp4 tcgen05 path: unsupported token tile %d", r.block);
+  XKB_REQUIRE(r.block == 16, "mxfp4 tcgen05 path: unsupported token tile %d", r.block);
   XKB_REQUIRE(reinterpret_cast<uintptr_t>(w13_scale) % 8 == 0 && reinterpret_cast<uintptr_t>(w2_scale) % 8 == 0,
               "mxfp4 tcgen05 path: scale tensors must be 8-byte aligned");
   Carver carve(tc_ws);
@@ -774,8 +775,7 @@ int launch_mxfp4_tc(const void* A, const uint8_t* w13, const uint8_t* w13_scale,
   prm.mx_scale = w13_scale;
   prm.bias = static_cast<const __nv_bfloat16*>(b13);
   int64_t max_tiles = r.max_blocks * (ispp / kTileRows);
-  rc = (r.block == 16) ? launch_bt<16, kModeMxGateUp>(tm_w13, tm_w13, tm_tok0, prm, max_tiles, stream)
-                       : launch_bt<32, kModeMxGateUp>(tm_w13, tm_w13, tm_tok0, prm, max_tiles, stream);
+  rc = launch_bt<16, kModeMxGateUp>(tm_w13, tm_w13, tm_tok0, prm, max_tiles, stream);
   if (rc != XKB_OK) return rc;
   // stage 1: down -> fp32 slot rows
   prm.scratch = scratch;
@@ -786,8 +786,7 @@ int launch_mxfp4_tc(const void* A, const uint8_t* w13, const uint8_t* w13_scale,
   prm.mx_scale = w2_scale;
   prm.bias = static_cast<const __nv_bfloat16*>(b2);
   max_tiles = r.max_blocks * (hidden / kTileRows);
-  return (r.block == 16) ? launch_bt<16, kModeMxDown>(tm_w2, tm_w2, tm_tok1, prm, max_tiles, stream)
-                         : launch_bt<32, kModeMxDown>(tm_w2, tm_w2, tm_tok1, prm, max_tiles, stream);
+  return launch_bt<16, kModeMxDown>(tm_w2, tm_w2, tm_tok1, prm, max_tiles, stream);
 }
 
 }  // namespace xkb
