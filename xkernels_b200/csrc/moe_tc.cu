@@ -53,8 +53,8 @@ template <int BT, int MATS = 1> struct TcCfg {
   // Token (B operand) ring: a stage holds kBSub sub-tiles of [BT x 64]; small token tiles
   // are loaded several at a time so that one barrier round trip covers up to 256 K.  With two
   // MMA issuers kBSub must be a multiple of 2 (each issuer waits/releases once per stage).
-  static constexpr int kBSub = (BT <= 32) ? 4 : (BT == 64) ? 2 : 1;
-  static constexpr int kBStages = (BT <= 32) ? 3 : 4;
+  static constexpr int kBSub = (BT <= 32 || MATS == 2) ? 4 : (BT == 64) ? 2 : 1;
+  static constexpr int kBStages = (BT <= 32) ? 3 : (MATS == 2) ? 2 : 4;
   static constexpr int kBSubBytes = BT * kSubK * 2;
   static constexpr int kBStageBytes = kBSub * kBSubBytes;
   // MMA issuers: narrow token tiles make the MMAs short (about 45 cycles each whatever N <= 64),
@@ -106,6 +106,10 @@ constexpr int kModeInt4 = 0;      // INT4 W4A16: rows = N, bf16 group scales by 
 constexpr int kModeMxGateUp = 1;  // MXFP4 w13: a tile is 128 gate rows + the 128 matching up rows, the
                                   // two matrices alternate 256-K stages and accumulators; SwiGLU epilogue
 constexpr int kModeMxDown = 2;    // MXFP4 w2: rows = hidden, bf16-rounded result x routing weight out
+constexpr int kModeInt4Pair = 3;  // INT4 with TWO 128-row weight tiles per token tile (they alternate
+                                  // 256-K stages like gate/up): halves the token-tile traffic per flop
+constexpr int mode_mats(int mode) { return (mode == kModeMxGateUp || mode == kModeInt4Pair) ? 2 : 1; }
+constexpr bool mode_is_int4(int mode) { return mode == kModeInt4 || mode == kModeInt4Pair; }
 
 struct TcParams {
   const int32_t* sorted_ids;
@@ -174,10 +178,10 @@ __device__ __forceinline__ void mx_word(uint32_t x, uint32_t c1, uint32_t c2, ui
 }
 
 template <int BT, int MODE>
-__global__ void __launch_bounds__(TcCfg<BT, (MODE == 1 ? 2 : 1)>::kThreads, (BT <= 32) ? 2 : 1)
+__global__ void __launch_bounds__(TcCfg<BT, mode_mats(MODE)>::kThreads, (BT <= 32) ? 2 : 1)
 moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_constant__ CUtensorMap tm_scale,
                const __grid_constant__ CUtensorMap tm_tokens, const TcParams p) {
-  using Cfg = TcCfg<BT, (MODE == kModeMxGateUp ? 2 : 1)>;
+  using Cfg = TcCfg<BT, mode_mats(MODE)>;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                                          ~uintptr_t(1023));
@@ -211,7 +215,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
     mbar_fence_init();
   }
   if (warp == 1) tmem_alloc(tmem_slot, Cfg::kTmemCols);
-  if (warp == 0 && lane == 0) { prefetch_tensormap(&tm_packed); if (MODE == kModeInt4) prefetch_tensormap(&tm_scale); }
+  if (warp == 0 && lane == 0) { prefetch_tensormap(&tm_packed); if (mode_is_int4(MODE)) prefetch_tensormap(&tm_scale); }
   if (warp == 1 && lane == 0) prefetch_tensormap(&tm_tokens);
   tc_fence_before();
   __syncthreads();
@@ -220,19 +224,20 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
 
   // tile index t -> (K part, token block, row tile); the row tile varies fastest so that CTAs that run
   // together share the token block and walk through one expert's weights
-  const int n_row_tiles = p.N / kTileRows;
+  const int n_row_tiles = p.N / (MODE == kModeInt4Pair ? 2 * kTileRows : kTileRows);
   const int n_tiles = n_row_tiles * p.ksplit;
   const int n_blocks = p.num_post[0] / BT;
   const int64_t total_tiles = (int64_t)n_blocks * n_tiles;
   const int k_stages = p.K / kStageK / p.ksplit;   // 256-K stages per tile
   // "virtual" weight stages of a tile: gate_up mode alternates the gate and the up matrix
-  constexpr int kMats = (MODE == kModeMxGateUp) ? 2 : 1;
+  constexpr int kMats = mode_mats(MODE);
   const int v_stages = kMats * k_stages;
-  static_assert(MODE != kModeMxGateUp || Cfg::kBSub == kSubs, "gate_up mode needs 256-K token stages");
+  static_assert(kMats == 1 || Cfg::kBSub == kSubs, "two-matrix modes need 256-K token stages");
   // first weight row (in the [E * rows_per_expert] row space) of virtual stage vs of tile (b, nt)
   auto tile_row = [&](int b, int nt, int vs) -> int {
     const int e = p.expert_ids[b];
     if (MODE == kModeInt4) return e * p.N + nt * kTileRows;
+    if (MODE == kModeInt4Pair) return e * p.N + (2 * nt + (vs & 1)) * kTileRows;
     if (MODE == kModeMxDown) return e * p.rows_per_expert + nt * kTileRows;
     return e * p.rows_per_expert + (vs & 1) * p.N + nt * kTileRows;  // gate rows, then up rows
   };
@@ -250,7 +255,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
           TRACE(0, 1);
           if (!mbar_wait(&w_empty[st], ph ^ 1, guard, 1, 400)) break;
           TRACE(0, 2);
-          if (MODE == kModeInt4) {
+          if (mode_is_int4(MODE)) {
             mbar_expect_tx(&w_full[st], kPackedStageBytes + kScaleStageBytes);
             tma_load_2d(s_packed + st * kPackedStageBytes, &tm_packed, &w_full[st], ks * (kStageK / 2), row0);
             tma_load_2d(s_scale + st * kScaleStageBytes, &tm_scale, &w_full[st], ks * (kStageK / 32), row0);
@@ -361,10 +366,10 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
       // ---- epilogue (the warpgroups take the 16-column groups round robin) ----
       if (!mbar_wait(&d_full[dbuf], duse & 1u, guard, 7)) return false;
       tc_fence_after();
-      const int64_t n_glob = (int64_t)nt * kTileRows + row;
+      const int64_t n_glob = (int64_t)nt * (MODE == kModeInt4Pair ? 2 * kTileRows : kTileRows) + row;
       const int32_t* slots = p.sorted_ids + (int64_t)b * BT;
       float bias0 = 0.f, bias1 = 0.f;
-      if (MODE != kModeInt4 && p.bias != nullptr) {
+      if (!mode_is_int4(MODE) && p.bias != nullptr) {
         const int64_t e_row = (int64_t)p.expert_ids[b] * p.rows_per_expert;
         bias0 = __bfloat162float(p.bias[e_row + n_glob]);
         if (MODE == kModeMxGateUp) bias1 = __bfloat162float(p.bias[e_row + p.N + n_glob]);
@@ -425,6 +430,11 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
               v = p.topk_w[slot] * v;
             }
             p.scratch[((int64_t)kpart * p.numel + slot) * p.N + n_glob] = v;
+            if (MODE == kModeInt4Pair) {  // the second weight tile: rows 128 further down
+              float v2 = __uint_as_float(more[j]);
+              if (p.mul_w) v2 = p.topk_w[slot] * v2;
+              p.scratch[((int64_t)kpart * p.numel + slot) * p.N + n_glob + kTileRows] = v2;
+            }
           }
         }
       }
@@ -437,7 +447,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
     int pend_b = 0, pend_nt = 0, pend_kpart = 0;
     uint32_t pend_it = 0, it = 0;
     uint2 mx_next = make_uint2(0, 0);
-    if (MODE != kModeInt4 && (int64_t)blockIdx.x < total_tiles) mx_next = mx_scale_load(blockIdx.x, 0);
+    if (!mode_is_int4(MODE) && (int64_t)blockIdx.x < total_tiles) mx_next = mx_scale_load(blockIdx.x, 0);
     for (int64_t t = blockIdx.x; t < total_tiles; t += gridDim.x, ++it) {
       const int rt = (int)(t % n_tiles), b = (int)(t / n_tiles);
       const int nt = rt % n_row_tiles, kpart = rt / n_row_tiles;
@@ -449,7 +459,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
         const unsigned char* pk = s_packed + wst * kPackedStageBytes + row * 128;
         uint32_t sc_w[4] = {0, 0, 0, 0};
         uint64_t mx_sc = 0;
-        if (MODE == kModeInt4) {
+        if (mode_is_int4(MODE)) {
           const uint4 sc = *reinterpret_cast<const uint4*>(s_scale + wst * kScaleStageBytes + row * 16);
           sc_w[0] = sc.x; sc_w[1] = sc.y; sc_w[2] = sc.z; sc_w[3] = sc.w;
         } else {
@@ -474,7 +484,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
             const int chunk = sub * 2 + h;  // 16-byte chunk = 32 weights = one scale group
             const uint4 w4 = *reinterpret_cast<const uint4*>(pk + ((chunk ^ (row & 7)) << 4));
             const uint32_t words[4] = {w4.x, w4.y, w4.z, w4.w};
-            if (MODE == kModeInt4) {
+            if (mode_is_int4(MODE)) {
               const uint32_t s2 = h ? __byte_perm(sw, sw, 0x3232) : __byte_perm(sw, sw, 0x1010);
 #pragma unroll
               for (int wp = 0; wp < 2; ++wp) {  // two words = 16 weights = 8 columns
@@ -599,7 +609,7 @@ int make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const 
 template <int BT, int MODE>
 int launch_bt(const CUtensorMap& tmp, const CUtensorMap& tms, const CUtensorMap& tmt, const TcParams& prm,
               int64_t max_tiles, cudaStream_t stream) {
-  using Cfg = TcCfg<BT, (MODE == kModeMxGateUp ? 2 : 1)>;
+  using Cfg = TcCfg<BT, mode_mats(MODE)>;
   XKB_CHECK_CUDA(cudaFuncSetAttribute(moe_tc_kernel<BT, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)Cfg::kSmemBytes));
   int dev = 0, sms = 148;
@@ -633,8 +643,7 @@ int int4_tc_block(int64_t numel, int E) {
   if (avg <= 12) return 16;
   if (avg <= 24) return 32;
   if (avg <= 48) return 64;
-  if (avg <= 96) return 128;
-  return 256;
+  return 128;  // wide: 128 tokens x two 128-row weight tiles per CTA (256 tokens x one tile if N % 256 != 0)
 }
 
 int64_t int4_tc_workspace_bytes(int64_t numel, int64_t N, int64_t K, int E) {
@@ -699,7 +708,10 @@ int launch_int4_tc(const void* A, const int32_t* packed, const void* scale, cons
     case 16: return launch_bt<16, kModeInt4>(tm_packed, tm_scale, tm_tokens, prm, max_tiles, stream);
     case 32: return launch_bt<32, kModeInt4>(tm_packed, tm_scale, tm_tokens, prm, max_tiles, stream);
     case 64: return launch_bt<64, kModeInt4>(tm_packed, tm_scale, tm_tokens, prm, max_tiles, stream);
-    case 128: return launch_bt<128, kModeInt4>(tm_packed, tm_scale, tm_tokens, prm, max_tiles, stream);
+    case 128:
+      if (N % (2 * kTileRows) == 0)
+        return launch_bt<128, kModeInt4Pair>(tm_packed, tm_scale, tm_tokens, prm, max_tiles / 2, stream);
+      return launch_bt<128, kModeInt4>(tm_packed, tm_scale, tm_tokens, prm, max_tiles, stream);
     case 256: return launch_bt<256, kModeInt4>(tm_packed, tm_scale, tm_tokens, prm, max_tiles, stream);
     default: return fail(XKB_ERR_ARG, "int4 tcgen05 path: unsupported token tile %d", r.block);
   }
