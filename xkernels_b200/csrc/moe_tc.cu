@@ -39,48 +39,57 @@ namespace {
 using namespace tc;
 
 constexpr int kTileRows = 128;   // weight rows per tile (UMMA M)
-constexpr int kStageK = 256;     // K per weight pipeline stage
-constexpr int kSubK = 64;        // K per token stage / tensor-memory A slot
+constexpr int kStageK = 256;     // K per pipeline stage (weights, tokens and the tensor-memory A slot alike)
+constexpr int kSubK = 64;        // K per 128-byte swizzled token sub-tile / per dequantiser warpgroup
 constexpr int kSubs = kStageK / kSubK;
-constexpr int kAColsPerSlot = kSubK / 2;               // 32 columns of bf16 pairs per A slot
-constexpr int kWStages = 4;
-constexpr int kCtrlWarps = 4;      // weight producer, token producer (+ tensor-memory owner), two MMA issuers
+constexpr int kSlotCols = kStageK / 2;                 // 128 columns of bf16 pairs per A slot
+constexpr int kSubCols = kSubK / 2;                    // 32 of them per warpgroup
+constexpr int kMaxIssuers = 3;
+constexpr int kCtrlWarps = 1 + kMaxIssuers;  // warp 0: the two TMA producers (lanes 0 and 1); warps 1-3: MMA issuers
+                                             // (20 warps in all: register files are handed out four warps at a time)
+constexpr int kWGs = kSubs;        // dequantiser warpgroups: warpgroup w converts K slice w of every stage
+constexpr int kDequantWarps = 4 * kWGs;
+constexpr int kGroups = 2;         // dequantiser groups that take alternate stages
+constexpr int kGroupWarps = kDequantWarps / kGroups;
+constexpr int kThreads = 32 * (kCtrlWarps + kDequantWarps);
+constexpr int kTmemCols = 512;     // one CTA per SM owns all of tensor memory
 constexpr int kPackedStageBytes = kTileRows * (kStageK / 2);  // 16 KiB
 constexpr int kScaleStageBytes = kTileRows * (kStageK / 32) * 2;  // 2 KiB
 
-// MATS = weight matrices that alternate 256-K stages inside one tile (2 in the MXFP4 gate_up mode)
+// MATS = weight matrices that alternate 256-K stages inside one tile (MXFP4 gate/up, INT4 row-tile pairs)
+//
+// The hand-off between the dequantisers and the MMA issuer is one whole 256-K stage: sixteen warps
+// fill a 128-column slot, the issuer waits once, issues sixteen MMAs back to back and commits
+// once.  A finer hand-off (64 K) was measured to be bound by the issuing thread's own loop
+// (about 1000 cycles per slice under the dequantisers' issue pressure) and not by the tensor pipe.
 template <int BT, int MATS = 1> struct TcCfg {
-  // Token (B operand) ring: a stage holds kBSub sub-tiles of [BT x 64]; small token tiles
-  // are loaded several at a time so that one barrier round trip covers up to 256 K.  With two
-  // MMA issuers kBSub must be a multiple of 2 (each issuer waits/releases once per stage).
-  static constexpr int kBSub = (BT <= 32 || MATS == 2) ? 4 : (BT == 64) ? 2 : 1;
-  static constexpr int kBStages = (BT <= 32) ? 3 : (MATS == 2) ? 2 : 4;
+  static constexpr int kBStages = (BT <= 64) ? 3 : 2;
   static constexpr int kBSubBytes = BT * kSubK * 2;
-  static constexpr int kBStageBytes = kBSub * kBSubBytes;
-  // MMA issuers: narrow token tiles make the MMAs short (about 45 cycles each whatever N <= 64),
-  // so the issuing thread's own instruction stream becomes the limit; two issuer warps then
-  // take alternate K slices, each into its own accumulator (summed in the epilogue).
-  static constexpr int kIssuers = (BT <= 64) ? 2 : 1;
-  // Dequantiser warpgroups (4 warps each).  Two CTAs share an SM for narrow tiles (2 x 2
-  // warpgroups); wider tiles run one CTA per SM with four.  K slice g (numbered across stages and
-  // tiles) belongs to warpgroup g % kWGs; kWGs divides the four slices of a stage.
-  static constexpr int kWGs = (BT <= 32) ? 2 : 4;   // (three per CTA at 64 registers measured slower: 283 vs 245 us)
-  static_assert(kSubs % kWGs == 0, "the warpgroups must divide the slices of a stage");
-  static constexpr int kDequantWarps = 4 * kWGs;
-  static constexpr int kThreads = 32 * (kCtrlWarps + kDequantWarps);
-  static constexpr int kAcc = kIssuers * MATS;   // accumulator a = issuer * MATS + matrix
-  static constexpr int kTmemCols = (BT <= 32) ? 256 : 512;
-  // ring of A slots: a multiple of kIssuers and of kWGs; the narrowest tile has room for six
-  static constexpr int kASlots = (BT <= 32) ? 6 : 8;
+  static constexpr int kBStageBytes = kSubs * kBSubBytes;   // [4][BT x 64] bf16
+  static constexpr int kWStages = (BT <= 32) ? 6 : 4;
   // Two accumulator sets when tensor memory has room: the MMAs of the next tile start while the
   // previous tile's accumulators are still being read out.
-  static constexpr int kDBuf = (2 * kAcc * BT + kASlots * kAColsPerSlot <= kTmemCols) ? 2 : 1;
-  static constexpr int kDCols = kDBuf * kAcc * BT;
-  static constexpr int kACol0 = kDCols;                  // A ring starts after the accumulators
-  static_assert(kDCols + kASlots * kAColsPerSlot <= kTmemCols, "tensor memory overcommitted");
+  // MMA issuers.  One thread sustains one tcgen05.mma per ~45 cycles (65-100 beside busy
+  // dequantiser warps) whatever the shape, and that is an issue limit of the thread, not of the
+  // tensor pipe: measured aggregate rates for N = 16 are 45 / 27 / 13 cycles per MMA with 1 / 2 / 4
+  // issuing warps, while N = 128 is pipe-bound at 64 cycles.  The time a stage's MMAs take to issue
+  // is part of the A slot's round trip (fill -> MMAs -> commit -> fill), and with three slots that
+  // round trip bounds the whole kernel, so narrow token tiles split the sixteen MMAs of a stage
+  // over three issuers: issuer j takes the K=16 steps j, j + kIssuers, ... of EVERY stage into its
+  // own accumulators, which the epilogue adds.  (Three, because with the producer warp and the
+  // sixteen dequantiser warps that makes 20 warps; registers are handed out four warps at a time.)
+  static constexpr int kIssuers = (BT <= 32) ? 3 : (BT <= 64) ? 2 : 1;
+  static constexpr int kAccs = kIssuers * MATS;             // accumulator (issuer j, matrix m) = j * MATS + m
+  static constexpr int kDBuf = (2 * kAccs * BT + 3 * kSlotCols <= kTmemCols) ? 2 : 1;
+  static constexpr int kDCols = kDBuf * kAccs * BT;         // accumulator a of set d at (d * kAccs + a) * BT
+  static constexpr int kACol0 = kDCols;                     // the A slots follow the accumulators
+  static constexpr int kASlotsFit = (kTmemCols - kDCols) / kSlotCols;
+  static constexpr int kASlots = kASlotsFit > 3 ? 3 : kASlotsFit;
+  static_assert(kASlots >= 2, "need two A slots so that conversion and MMA overlap");
   static constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + (size_t)kWStages * kPackedStageBytes +
                                        (size_t)kBStages * kBStageBytes + (size_t)kWStages * kScaleStageBytes +
                                        1024 /*barriers*/;
+  static_assert(kSmemBytes <= 227 * 1024, "shared memory overcommitted");
 };
 
 #ifdef XKB_TC_TRACE
@@ -100,6 +109,7 @@ namespace {
 #else
 #define TRACE(role, tag) do {} while (0)
 #endif
+#define TRACE_ISS(tag) do { if (me < 2) TRACE(me == 0 ? 2 : 7, tag); } while (0)
 
 // Kernel modes: which weights are streamed and what the epilogue does.
 constexpr int kModeInt4 = 0;      // INT4 W4A16: rows = N, bf16 group scales by TMA, fp32 slot rows out
@@ -178,15 +188,17 @@ __device__ __forceinline__ void mx_word(uint32_t x, uint32_t c1, uint32_t c2, ui
 }
 
 template <int BT, int MODE>
-__global__ void __launch_bounds__(TcCfg<BT, mode_mats(MODE)>::kThreads, (BT <= 32) ? 2 : 1)
+__global__ void __launch_bounds__(kThreads, 1)
 moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_constant__ CUtensorMap tm_scale,
                const __grid_constant__ CUtensorMap tm_tokens, const TcParams p) {
   using Cfg = TcCfg<BT, mode_mats(MODE)>;
+  constexpr int kWStages = Cfg::kWStages;
+  constexpr int kMatsC = mode_mats(MODE);
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                                          ~uintptr_t(1023));
   unsigned char* s_packed = smem;                                         // kWStages x 16 KiB
-  unsigned char* s_tokens = s_packed + kWStages * kPackedStageBytes;      // kBStages x BT*128
+  unsigned char* s_tokens = s_packed + kWStages * kPackedStageBytes;      // kBStages x 4 x [BT x 64] bf16
   unsigned char* s_scale = s_tokens + Cfg::kBStages * Cfg::kBStageBytes;  // kWStages x 2 KiB
   uint64_t* bars = reinterpret_cast<uint64_t*>(s_scale + kWStages * kScaleStageBytes);
   uint64_t* w_full = bars;                       // [kWStages]
@@ -200,23 +212,25 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(d_empty + Cfg::kDBuf);
   int* abort_word = reinterpret_cast<int*>(tmem_slot + 1);
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // broadcast so that the compiler knows the warp index is warp-uniform (tensor-memory addresses and
+  // role branches then live in uniform registers)
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
   Guard guard{abort_word, p.status};
 #ifdef XKB_TC_TRACE
   int trace_i = 0;
 #endif
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < kWStages; ++i) { mbar_init(&w_full[i], 1); mbar_init(&w_empty[i], Cfg::kDequantWarps); }
-    for (int i = 0; i < Cfg::kBStages; ++i) { mbar_init(&b_full[i], 1); mbar_init(&b_empty[i], Cfg::kIssuers); }
-    for (int i = 0; i < Cfg::kASlots; ++i) { mbar_init(&a_full[i], 4); mbar_init(&a_empty[i], 1); }
-    for (int i = 0; i < Cfg::kDBuf; ++i) { mbar_init(&d_full[i], Cfg::kIssuers); mbar_init(&d_empty[i], Cfg::kDequantWarps); }
+    for (int i = 0; i < kWStages; ++i) { mbar_init(&w_full[i], 1); mbar_init(&w_empty[i], 1); }
+    for (int i = 0; i < Cfg::kBStages; ++i) { mbar_init(&b_full[i], 1); mbar_init(&b_empty[i], Cfg::kIssuers * kMatsC); }
+    for (int i = 0; i < Cfg::kASlots; ++i) { mbar_init(&a_full[i], kGroupWarps); mbar_init(&a_empty[i], Cfg::kIssuers); }
+    for (int i = 0; i < Cfg::kDBuf; ++i) { mbar_init(&d_full[i], Cfg::kIssuers); mbar_init(&d_empty[i], kDequantWarps); }
     *abort_word = 0;
     mbar_fence_init();
   }
-  if (warp == 1) tmem_alloc(tmem_slot, Cfg::kTmemCols);
+  if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
   if (warp == 0 && lane == 0) { prefetch_tensormap(&tm_packed); if (mode_is_int4(MODE)) prefetch_tensormap(&tm_scale); }
-  if (warp == 1 && lane == 0) prefetch_tensormap(&tm_tokens);
+  if (warp == 0 && lane == 1) prefetch_tensormap(&tm_tokens);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -229,10 +243,9 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
   const int n_blocks = p.num_post[0] / BT;
   const int64_t total_tiles = (int64_t)n_blocks * n_tiles;
   const int k_stages = p.K / kStageK / p.ksplit;   // 256-K stages per tile
-  // "virtual" weight stages of a tile: gate_up mode alternates the gate and the up matrix
+  // "virtual" weight stages of a tile: two-matrix modes alternate the matrices stage by stage
   constexpr int kMats = mode_mats(MODE);
   const int v_stages = kMats * k_stages;
-  static_assert(kMats == 1 || Cfg::kBSub == kSubs, "two-matrix modes need 256-K token stages");
   // first weight row (in the [E * rows_per_expert] row space) of virtual stage vs of tile (b, nt)
   auto tile_row = [&](int b, int nt, int vs) -> int {
     const int e = p.expert_ids[b];
@@ -242,9 +255,9 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
     return e * p.rows_per_expert + (vs & 1) * p.N + nt * kTileRows;  // gate rows, then up rows
   };
 
-  if (warp == 0) {
+  if (warp == 0 && lane == 0) {
     // ---------------- weight producer ----------------
-    if (lane == 0) {
+    {
       uint32_t st = 0, ph = 0;
       for (int64_t t = blockIdx.x; t < total_tiles && !guard.aborted(); t += gridDim.x) {
         const int rt = (int)(t % n_tiles), b = (int)(t / n_tiles);
@@ -267,103 +280,116 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
         }
       }
     }
-  } else if (warp == 1) {
-    // ---------------- token producer ----------------
-    if (lane == 0) {
+  } else if (warp == 0 && lane == 1) {
+    // ---------------- token producer (diverged from lane 0; both make progress independently) ----------------
+    {
       uint32_t st = 0, ph = 0;
       for (int64_t t = blockIdx.x; t < total_tiles && !guard.aborted(); t += gridDim.x) {
         const int b = (int)(t / n_tiles);
         const int pos0 = b * BT;
-        const int s0 = ((int)(t % n_tiles) / n_row_tiles) * k_stages * kSubs;  // first 64-K slice of this K part
-        for (int s = 0; s < k_stages * kSubs; s += Cfg::kBSub) {
+        const int ks0 = ((int)(t % n_tiles) / n_row_tiles) * k_stages;  // first 256-K stage of this K part
+        for (int ks = 0; ks < k_stages; ++ks) {
           TRACE(1, 1);
           if (!mbar_wait(&b_empty[st], ph ^ 1, guard, 2, 400)) break;
           TRACE(1, 2);
           mbar_expect_tx(&b_full[st], Cfg::kBStageBytes);
 #pragma unroll
-          for (int j = 0; j < Cfg::kBSub; ++j)
+          for (int j = 0; j < kSubs; ++j)
             tma_load_2d(s_tokens + st * Cfg::kBStageBytes + j * Cfg::kBSubBytes, &tm_tokens, &b_full[st],
-                        (s0 + s + j) * kSubK, pos0);
+                        ((ks0 + ks) * kSubs + j) * kSubK, pos0);
           if (++st == Cfg::kBStages) { st = 0; ph ^= 1; }
         }
       }
     }
-  } else if (warp < kCtrlWarps) {
-    // ---------------- MMA issuer(s) ----------------
-    // Issuer i takes the K slices g with g % kIssuers == i and accumulates into accumulator i.
-    const int me = warp - 2;
-    if (lane == 0 && me < Cfg::kIssuers) {
+  } else if (warp >= 1 && warp < kCtrlWarps) {
+    // ---------------- MMA issuers ----------------
+    // Every issuer visits every stage: it waits for the A slot and the token stage, issues the
+    // M=128 N=BT K=16 MMAs of its K slices into its own accumulator and commits; slot and token
+    // stage are free again when all issuers' commits have arrived.
+    constexpr int kIssuers = Cfg::kIssuers;
+    const uint32_t me = warp - 1;
+    if (lane == 0 && me < (uint32_t)kIssuers) {
       constexpr uint32_t idesc = umma_idesc_bf16(kTileRows, BT);
-      constexpr int kStep = Cfg::kIssuers;
-      uint32_t bst = 0, bph = 0, aq = me, aph = 0, it = 0;
+      uint32_t aq = 0, aph = 0, bst = 0, bph = 0, wst = 0, it = 0;
+      // this issuer's K=16 steps of a stage: m = me, me + kIssuers, ... < 16; step m reads A columns
+      // [8 m, 8 m + 8) of the slot and token sub-tile m / 4 at K offset (m % 4) * 32 bytes
+      constexpr int kMyMax = (kSubs * (kSubK / 16) + kIssuers - 1) / kIssuers;
+      uint32_t b_off[kMyMax];
+#pragma unroll
+      for (int i = 0; i < kMyMax; ++i) {
+        const uint32_t m = me + (uint32_t)(i * kIssuers);
+        b_off[i] = (((m >> 2) * (uint32_t)Cfg::kBSubBytes) >> 4) + (m & 3u) * 2u;
+      }
       for (int64_t t = blockIdx.x; t < total_tiles && !guard.aborted(); t += gridDim.x, ++it) {
-        // accumulator set of this tile; its previous user must have been read out by every epilogue thread
+        // accumulator set of this tile; its previous user must have been read out by every epilogue warp
         const uint32_t dbuf = it % Cfg::kDBuf, duse = it / Cfg::kDBuf;
         bool ok = mbar_wait(&d_empty[dbuf], (duse & 1u) ^ 1u, guard, 8, 100);
         if (ok) tc_fence_after();
-        // slices of the tile in order: virtual stage vs = v / 4 (gate_up: even = gate, odd = up),
-        // slice sub = v % 4; this issuer takes every kStep-th one
-        for (int v = me; v < v_stages * kSubs && ok; v += kStep) {
-          const int vs = v / kSubs, sub = v % kSubs;
+        for (int vs = 0; vs < v_stages && ok; ++vs) {
           const int mat = vs % kMats;                       // which matrix this stage belongs to
-          const int bsub = sub % Cfg::kBSub;                // sub-tile inside the token stage
-          TRACE(2, 1);
-          ok = mbar_wait(&a_full[aq], aph, guard, 3, 100);
-          TRACE(2, 2);
-          // first slice of this issuer inside a token stage: the stage must have landed
-          // (in gate_up mode the up stage re-uses the token stage of the gate stage before it)
-          if (ok && mat == 0 && bsub < kStep) ok = mbar_wait(&b_full[bst], bph, guard, 4);
+          TRACE_ISS(1);
+          ok = mbar_wait(&a_full[aq], aph, guard, 3, 32);
+          TRACE_ISS(2);
+          // every dequantiser warp has arrived, so all of them are done with the weight stage in
+          // shared memory: hand it back to the producer on their behalf
+          if (ok && me == 0) mbar_arrive(&w_empty[wst]);
+          // two-matrix modes: the second matrix re-uses the token stage of the first
+          if (ok && mat == 0) ok = mbar_wait(&b_full[bst], bph, guard, 4);
           if (!ok) break;
           tc_fence_after();
-          TRACE(2, 3);
-          const uint32_t d_tmem = tmem_base + (uint32_t)(((int)dbuf * Cfg::kAcc + me * kMats + mat) * BT);
-          const uint32_t a_tmem = tmem_base + Cfg::kACol0 + aq * kAColsPerSlot;
-          const uint64_t b_desc =
-              umma_desc_k_sw128(smem_u32(s_tokens + bst * Cfg::kBStageBytes + bsub * Cfg::kBSubBytes));
-          const bool first = (vs < kMats) && (sub == me);   // first MMA into this accumulator
+          TRACE_ISS(3);
+          const uint32_t d_tmem = tmem_base + (uint32_t)((((int)dbuf * kIssuers + (int)me) * kMats + mat) * BT);
+          const uint32_t a_tmem = tmem_base + Cfg::kACol0 + aq * kSlotCols;
+          const uint64_t b_desc = umma_desc_k_sw128(smem_u32(s_tokens + bst * Cfg::kBStageBytes));
 #pragma unroll
-          for (int kk = 0; kk < kSubK / 16; ++kk)
-            umma_ts_bf16(d_tmem, a_tmem + kk * 8, b_desc + (uint64_t)(kk * 2), idesc, (first && kk == 0) ? 0u : 1u);
-          TRACE(2, 4);
-          tc_commit(&a_empty[aq]);
-          TRACE(2, 5);
-          aq += kStep;
-          if (aq >= (uint32_t)Cfg::kASlots) { aq -= Cfg::kASlots; aph ^= 1; }
-          // last slice of this issuer inside the token stage (of the last matrix): release it
-          if (mat == kMats - 1 && bsub + kStep >= Cfg::kBSub) {
-            tc_commit(&b_empty[bst]);
-            if (++bst == Cfg::kBStages) { bst = 0; bph ^= 1; }
+          for (int i = 0; i < kMyMax; ++i) {
+            const uint32_t m = me + (uint32_t)(i * kIssuers);
+            if (m < (uint32_t)(kSubs * (kSubK / 16)))
+              umma_ts_bf16(d_tmem, a_tmem + m * 8, b_desc + (uint64_t)b_off[i], idesc,
+                           (vs < kMats && i == 0) ? 0u : 1u);
           }
+          TRACE_ISS(4);
+          tc_commit(&a_empty[aq]);
+          if (++aq == (uint32_t)Cfg::kASlots) { aq = 0; aph ^= 1; }
+          if (++wst == (uint32_t)kWStages) wst = 0;
+          tc_commit(&b_empty[bst]);   // kIssuers * kMats arrivals release the token stage
+          if (mat == kMats - 1) {
+            if (++bst == (uint32_t)Cfg::kBStages) { bst = 0; bph ^= 1; }
+          }
+          TRACE_ISS(5);
         }
         if (!ok) break;
         tc_commit(&d_full[dbuf]);
       }
     }
-  } else {
+  } else if (warp >= kCtrlWarps) {
     // ---------------- dequantisers + epilogue ----------------
-    // K slices of 64 are numbered g = 0,1,2,... across stages and tiles; slice g goes to
-    // tensor-memory slot g % kASlots and is produced by warpgroup g % kWGs.
-    // A slice is stored eight columns at a time as its words are dequantised and published
-    // as soon as the stores have completed.
+    // Thread = weight row (the four warps of a warpgroup cover the four tensor-memory lane
+    // quarters).  The sixteen warps form two groups of two warpgroups; stages (numbered g across
+    // the tiles of the CTA) alternate between the groups, so that one group's barrier waits,
+    // shared-memory loads and tensor-memory store drains overlap the other group's arithmetic.
+    // Inside a group, warpgroup h converts the K slices 2h and 2h+1 (128 of the stage's 256 K) into
+    // columns [64 h, 64 h + 64) of the stage's A slot, eight columns per tcgen05.st.
     const int wg = (warp - kCtrlWarps) >> 2;
+    const uint32_t grp = (uint32_t)wg >> 1;
+    const int half = wg & 1;
     const int quarter = warp & 3;              // tensor-memory lane quarter this warp may access
     const int row = quarter * 32 + lane;       // weight row inside the tile
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-    uint32_t wst = 0, wph = 0;
-    uint32_t aq = wg, aph = 0;                 // next slot of this warpgroup and its phase
-    // MXFP4: the 8 e8m0 bytes of this row for one 256-K stage, fetched one stage ahead
-    auto mx_scale_load = [&](int64_t t, int vs) -> uint2 {
+    const uint32_t s_packed_u32 = smem_u32(s_packed), s_scale_u32 = smem_u32(s_scale);
+    // MXFP4: the four e8m0 bytes of this row's half stage, fetched one stage ahead
+    auto mx_scale_load = [&](int64_t t, int vs) -> uint32_t {
       const int rt = (int)(t % n_tiles), b = (int)(t / n_tiles);
       const int nt = rt % n_row_tiles, ks0 = (rt / n_row_tiles) * k_stages;
       const int64_t grow = (int64_t)tile_row(b, nt, vs) + row;
-      return __ldg(reinterpret_cast<const uint2*>(p.mx_scale + grow * (p.K / 32) + (ks0 + vs / kMats) * (kStageK / 32)));
+      return __ldg(reinterpret_cast<const uint32_t*>(p.mx_scale + grow * (p.K / 32) +
+                                                     (ks0 + vs / kMats) * (kStageK / 32) + half * 4));
     };
     // Epilogue of tile (b, nt, kpart) whose accumulators sit in set `dbuf` (use number `duse` of that
     // set).  It runs one weight stage into the NEXT tile (or after the last tile), so that the MMAs
     // it waits for have long finished and the pipeline never drains at a tile boundary.
     auto run_epilogue = [&](int b, int nt, int kpart, uint32_t dbuf, uint32_t duse) -> bool {
-      const uint32_t d_base = tmem_base + lane_base + dbuf * (uint32_t)(Cfg::kAcc * BT);
-      // ---- epilogue (the warpgroups take the 16-column groups round robin) ----
+      const uint32_t d_base = tmem_base + lane_base + dbuf * (uint32_t)(Cfg::kAccs * BT);
       if (!mbar_wait(&d_full[dbuf], duse & 1u, guard, 7)) return false;
       tc_fence_after();
       const int64_t n_glob = (int64_t)nt * (MODE == kModeInt4Pair ? 2 * kTileRows : kTileRows) + row;
@@ -374,29 +400,27 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
         bias0 = __bfloat162float(p.bias[e_row + n_glob]);
         if (MODE == kModeMxGateUp) bias1 = __bfloat162float(p.bias[e_row + p.N + n_glob]);
       }
+      // the warpgroups take the 16-column groups round robin
 #pragma unroll 1
-      for (int c0 = wg * 16; c0 < BT; c0 += 16 * Cfg::kWGs) {
-        // acc = matrix 0 (INT4 / down: the only one; gate_up: gate), more = matrix 1 (up); each is
-        // the sum over the issuers' accumulators
+      for (int c0 = wg * 16; c0 < BT; c0 += 16 * kWGs) {
+        // acc = matrix 0 (INT4 / down: the only one; gate_up: gate; pair: first row tile), more = matrix 1,
+        // each the sum over the issuers' accumulators (issuer j, matrix m) at (j * kMats + m) * BT
         uint32_t acc[16], more[16];
         tmem_ld_32x16(d_base + c0, acc);
+        if (kMats == 2) tmem_ld_32x16(d_base + BT + c0, more);
         tmem_wait_ld();
-        if (kMats > 1) {
-          tmem_ld_32x16(d_base + BT + c0, more);
-          tmem_wait_ld();
-        }
 #pragma unroll
-        for (int is = 1; is < Cfg::kIssuers; ++is) {
+        for (int j = 1; j < Cfg::kIssuers; ++j) {
           uint32_t part[16];
-          tmem_ld_32x16(d_base + (is * kMats) * BT + c0, part);
+          tmem_ld_32x16(d_base + (j * kMats) * BT + c0, part);
           tmem_wait_ld();
 #pragma unroll
-          for (int j = 0; j < 16; ++j) acc[j] = __float_as_uint(__uint_as_float(acc[j]) + __uint_as_float(part[j]));
-          if (kMats > 1) {
-            tmem_ld_32x16(d_base + (is * kMats + 1) * BT + c0, part);
+          for (int q = 0; q < 16; ++q) acc[q] = __float_as_uint(__uint_as_float(acc[q]) + __uint_as_float(part[q]));
+          if (kMats == 2) {
+            tmem_ld_32x16(d_base + (j * kMats + 1) * BT + c0, part);
             tmem_wait_ld();
 #pragma unroll
-            for (int j = 0; j < 16; ++j) more[j] = __float_as_uint(__uint_as_float(more[j]) + __uint_as_float(part[j]));
+            for (int q = 0; q < 16; ++q) more[q] = __float_as_uint(__uint_as_float(more[q]) + __uint_as_float(part[q]));
           }
         }
         if (MODE == kModeMxGateUp) {
@@ -445,86 +469,99 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
     };
     bool pend = false;
     int pend_b = 0, pend_nt = 0, pend_kpart = 0;
-    uint32_t pend_it = 0, it = 0;
-    uint2 mx_next = make_uint2(0, 0);
-    if (!mode_is_int4(MODE) && (int64_t)blockIdx.x < total_tiles) mx_next = mx_scale_load(blockIdx.x, 0);
-    for (int64_t t = blockIdx.x; t < total_tiles; t += gridDim.x, ++it) {
+    uint32_t pend_it = 0, it = 0, g0 = 0;      // g0 = number of the tile's first stage
+    const bool tracer = (lane == 0 && quarter == 0);
+    (void)tracer;
+    // the stage this group converts after (t, vs, g0): two further on, or the first own stage of a later tile
+    auto next_own = [&](int64_t& t, int& vs, uint32_t& gbase) -> bool {
+      vs += kGroups;
+      while (vs >= v_stages) {
+        t += gridDim.x;
+        if (t >= total_tiles) return false;
+        gbase += (uint32_t)v_stages;
+        vs = (int)((grp - gbase) & (uint32_t)(kGroups - 1));
+      }
+      return true;
+    };
+    uint32_t mx_next = 0;
+    if (!mode_is_int4(MODE)) {
+      int64_t tn = blockIdx.x; int vn = (int)grp - kGroups; uint32_t gn = 0;
+      if (tn < total_tiles && next_own(tn, vn, gn)) mx_next = mx_scale_load(tn, vn);
+    }
+    for (int64_t t = blockIdx.x; t < total_tiles; t += gridDim.x, ++it, g0 += (uint32_t)v_stages) {
       const int rt = (int)(t % n_tiles), b = (int)(t / n_tiles);
       const int nt = rt % n_row_tiles, kpart = rt / n_row_tiles;
       bool ok = true;
-      for (int vs = 0; vs < v_stages && ok; ++vs) {
-        if (lane == 0 && quarter == 0) TRACE(3 + wg, 1);
+      bool epi_due = pend;   // the previous tile's epilogue runs after this group's first stage of this tile
+      for (int vs = (int)((grp - g0) & (uint32_t)(kGroups - 1)); vs < v_stages && ok; vs += kGroups) {
+        const uint32_t g = g0 + (uint32_t)vs;
+        const uint32_t wst = g % kWStages, wph = (g / kWStages) & 1u;
+        const uint32_t aq = g % Cfg::kASlots, aph = (g / Cfg::kASlots) & 1u;
+        if (tracer) TRACE(3 + wg, 1);
         if (!mbar_wait(&w_full[wst], wph, guard, 5)) { ok = false; break; }
-        if (lane == 0 && quarter == 0) TRACE(3 + wg, 2);
-        const unsigned char* pk = s_packed + wst * kPackedStageBytes + row * 128;
-        uint32_t sc_w[4] = {0, 0, 0, 0};
-        uint64_t mx_sc = 0;
+        if (tracer) TRACE(3 + wg, 2);
+        const uint32_t pk = s_packed_u32 + wst * kPackedStageBytes + row * 128;
+        uint2 sw = make_uint2(0, 0);  // INT4: the four bf16 group scales of this half stage; MXFP4: .x = its four e8m0 bytes
         if (mode_is_int4(MODE)) {
-          const uint4 sc = *reinterpret_cast<const uint4*>(s_scale + wst * kScaleStageBytes + row * 16);
-          sc_w[0] = sc.x; sc_w[1] = sc.y; sc_w[2] = sc.z; sc_w[3] = sc.w;
+          sw = lds64(s_scale_u32 + wst * kScaleStageBytes + row * 16 + half * 8);
         } else {
-          mx_sc = (uint64_t)mx_next.x | ((uint64_t)mx_next.y << 32);
-          if (vs + 1 < v_stages) mx_next = mx_scale_load(t, vs + 1);
-          else if (t + gridDim.x < total_tiles) mx_next = mx_scale_load(t + gridDim.x, 0);
+          sw.x = mx_next;
+          int64_t tn = t; int vn = vs; uint32_t gn = g0;
+          if (next_own(tn, vn, gn)) mx_next = mx_scale_load(tn, vn);
         }
+        // 16-byte chunk = 32 weights = one scale group; this half stage is chunks 4 half .. 4 half + 3
+        uint4 w4[4];
 #pragma unroll
-        for (int i = 0; i < kSubs / Cfg::kWGs; ++i) {
-          const int sub = wg + Cfg::kWGs * i;  // kWGs divides 4: the same slices in every stage
-          if (lane == 0 && quarter == 0) TRACE(3 + wg, 3);
-          if (!mbar_wait(&a_empty[aq], aph ^ 1, guard, 6)) { ok = false; break; }
-          tc_fence_after();
-          if (lane == 0 && quarter == 0) TRACE(3 + wg, 4);
-          const uint32_t dst = tmem_base + lane_base + Cfg::kACol0 + aq * kAColsPerSlot;
-          uint32_t sw = sc_w[0];  // INT4: the two group scales of slice `sub` (static indices only)
+        for (int c = 0; c < 4; ++c) w4[c] = lds128(pk + (((half * 4 + c) ^ (row & 7)) << 4));
+        // (the stage is handed back to the producer by the MMA issuer once all warps of the group have
+        // published the converted slices, which they do after these loads)
+        if (tracer) TRACE(3 + wg, 3);
+        if (!mbar_wait(&a_empty[aq], aph ^ 1, guard, 6)) { ok = false; break; }
+        tc_fence_after();
+        if (tracer) TRACE(3 + wg, 4);
+        const uint32_t dst = tmem_base + lane_base + Cfg::kACol0 + aq * kSlotCols + half * (2 * kSubCols);
 #pragma unroll
-          for (int q = 1; q < kSubs; ++q)
-            if (q == sub) sw = sc_w[q];
+        for (int c = 0; c < 4; ++c) {
+          const uint32_t words[4] = {w4[c].x, w4[c].y, w4[c].z, w4[c].w};
+          if (mode_is_int4(MODE)) {
+            const uint32_t s01 = (c < 2) ? sw.x : sw.y;
+            const uint32_t s2 = (c & 1) ? __byte_perm(s01, s01, 0x3232) : __byte_perm(s01, s01, 0x1010);
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const int chunk = sub * 2 + h;  // 16-byte chunk = 32 weights = one scale group
-            const uint4 w4 = *reinterpret_cast<const uint4*>(pk + ((chunk ^ (row & 7)) << 4));
-            const uint32_t words[4] = {w4.x, w4.y, w4.z, w4.w};
-            if (mode_is_int4(MODE)) {
-              const uint32_t s2 = h ? __byte_perm(sw, sw, 0x3232) : __byte_perm(sw, sw, 0x1010);
+            for (int wp = 0; wp < 2; ++wp) {  // two words = 16 weights = 8 columns
+              const uint32_t x0 = words[2 * wp], x1 = words[2 * wp + 1];
+              tmem_st_32x8(dst + c * 16 + wp * 8,
+                           dequant_pair(nib_pair(x0), s2), dequant_pair(nib_pair(x0 >> 4), s2),
+                           dequant_pair(nib_pair(x0 >> 8), s2), dequant_pair(nib_pair(x0 >> 12), s2),
+                           dequant_pair(nib_pair(x1), s2), dequant_pair(nib_pair(x1 >> 4), s2),
+                           dequant_pair(nib_pair(x1 >> 8), s2), dequant_pair(nib_pair(x1 >> 12), s2));
+            }
+          } else {
+            uint32_t c1, c2;
+            mx_scale_factors((sw.x >> (8 * c)) & 0xFFu, c1, c2);
 #pragma unroll
-              for (int wp = 0; wp < 2; ++wp) {  // two words = 16 weights = 8 columns
-                const uint32_t x0 = words[2 * wp], x1 = words[2 * wp + 1];
-                tmem_st_32x8(dst + h * 16 + wp * 8,
-                             dequant_pair(nib_pair(x0), s2), dequant_pair(nib_pair(x0 >> 4), s2),
-                             dequant_pair(nib_pair(x0 >> 8), s2), dequant_pair(nib_pair(x0 >> 12), s2),
-                             dequant_pair(nib_pair(x1), s2), dequant_pair(nib_pair(x1 >> 4), s2),
-                             dequant_pair(nib_pair(x1 >> 8), s2), dequant_pair(nib_pair(x1 >> 12), s2));
-              }
-            } else {
-              uint32_t c1, c2;
-              mx_scale_factors((uint32_t)(mx_sc >> (8 * chunk)) & 0xFFu, c1, c2);
-#pragma unroll
-              for (int wp = 0; wp < 2; ++wp) {
-                uint32_t r[8];
-                mx_word(words[2 * wp], c1, c2, r[0], r[1], r[2], r[3]);
-                mx_word(words[2 * wp + 1], c1, c2, r[4], r[5], r[6], r[7]);
-                tmem_st_32x8(dst + h * 16 + wp * 8, r[0], r[1], r[2], r[3], r[4], r[5], r[6], r[7]);
-              }
+            for (int wp = 0; wp < 2; ++wp) {
+              uint32_t r[8];
+              mx_word(words[2 * wp], c1, c2, r[0], r[1], r[2], r[3]);
+              mx_word(words[2 * wp + 1], c1, c2, r[4], r[5], r[6], r[7]);
+              tmem_st_32x8(dst + c * 16 + wp * 8, r[0], r[1], r[2], r[3], r[4], r[5], r[6], r[7]);
             }
           }
-          if (lane == 0 && quarter == 0) TRACE(3 + wg, 5);
-          tmem_wait_st();
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&a_full[aq]);
-          if (lane == 0 && quarter == 0) TRACE(3 + wg, 6);
-          aq += Cfg::kWGs;
-          if (aq >= (uint32_t)Cfg::kASlots) { aq -= Cfg::kASlots; aph ^= 1; }
         }
-        __syncwarp();  // every lane has read its part of the stage: one arrival per warp
-        if (lane == 0) mbar_arrive(&w_empty[wst]);
-        if (++wst == kWStages) { wst = 0; wph ^= 1; }
-        if (vs == 0 && pend) {  // previous tile's epilogue, one stage into this tile
-          pend = false;
+        if (tracer) TRACE(3 + wg, 5);
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&a_full[aq]);
+        if (tracer) TRACE(3 + wg, 6);
+        if (epi_due) {
+          epi_due = false;
           if (!run_epilogue(pend_b, pend_nt, pend_kpart, pend_it % Cfg::kDBuf, pend_it / Cfg::kDBuf)) { ok = false; break; }
         }
       }
       if (!ok) break;
+      if (epi_due) {  // this group had no stage in this tile
+        if (!run_epilogue(pend_b, pend_nt, pend_kpart, pend_it % Cfg::kDBuf, pend_it / Cfg::kDBuf)) break;
+      }
       // the epilogue is deferred: see run_epilogue
       pend = true; pend_b = b; pend_nt = nt; pend_kpart = kpart; pend_it = it;
     }
@@ -535,7 +572,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    tmem_dealloc(tmem_base, kTmemCols);
   }
 }
 
@@ -615,17 +652,13 @@ int launch_bt(const CUtensorMap& tmp, const CUtensorMap& tms, const CUtensorMap&
   int dev = 0, sms = 148;
   XKB_CHECK_CUDA(cudaGetDevice(&dev));
   XKB_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  // resident CTAs per SM: bounded by shared memory and by 512 tensor-memory columns
-  int per_sm = (int)((227 * 1024) / Cfg::kSmemBytes);
-  const int by_tmem = 512 / Cfg::kTmemCols;
-  if (per_sm > by_tmem) per_sm = by_tmem;
-  if (per_sm < 1) per_sm = 1;
+  const int per_sm = 1;  // the CTA owns the SM: all 512 tensor-memory columns, 20 warps
   int64_t grid = (int64_t)sms * per_sm;
   if (grid > max_tiles) grid = max_tiles;
   if (grid < 1) grid = 1;
   {
     GemmTimerScope timed(stream);
-    moe_tc_kernel<BT, MODE><<<(unsigned)grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tmp, tms, tmt, prm);
+    moe_tc_kernel<BT, MODE><<<(unsigned)grid, kThreads, Cfg::kSmemBytes, stream>>>(tmp, tms, tmt, prm);
   }
   XKB_CHECK_LAUNCH("moe_tc_kernel");
   return XKB_OK;
@@ -643,7 +676,7 @@ int int4_tc_block(int64_t numel, int E) {
   if (avg <= 12) return 16;
   if (avg <= 24) return 32;
   if (avg <= 48) return 64;
-  return 128;  // wide: 128 tokens x two 128-row weight tiles per CTA (256 tokens x one tile if N % 256 != 0)
+  return 128;  // wide: 128 tokens x two 128-row weight tiles per CTA (one tile if N % 256 != 0)
 }
 
 int64_t int4_tc_workspace_bytes(int64_t numel, int64_t N, int64_t K, int E) {
@@ -712,7 +745,6 @@ int launch_int4_tc(const void* A, const int32_t* packed, const void* scale, cons
       if (N % (2 * kTileRows) == 0)
         return launch_bt<128, kModeInt4Pair>(tm_packed, tm_scale, tm_tokens, prm, max_tiles / 2, stream);
       return launch_bt<128, kModeInt4>(tm_packed, tm_scale, tm_tokens, prm, max_tiles, stream);
-    case 256: return launch_bt<256, kModeInt4>(tm_packed, tm_scale, tm_tokens, prm, max_tiles, stream);
     default: return fail(XKB_ERR_ARG, "int4 tcgen05 path: unsupported token tile %d", r.block);
   }
 }

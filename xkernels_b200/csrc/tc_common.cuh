@@ -69,13 +69,31 @@ struct Guard {
 // would otherwise spend issue slots on probes that the dequantiser warps need.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Guard& g, int where,
                                           uint32_t sleep_ns = 0) {
+  if (mbar_try(bar, parity, 1000)) return true;   // the common case: already complete
   for (uint32_t i = 0; i < kMaxPolls; ++i) {
-    if (mbar_try(bar, parity, 1000)) return true;
     if (sleep_ns) __nanosleep(sleep_ns);
+    if (mbar_try(bar, parity, 1000)) return true;
     if ((i & 63u) == 63u && g.aborted()) return false;
   }
   g.raise(kErrWaitTimeout + (where << 8));
   return false;
+}
+
+// ---- shared-memory loads by 32-bit shared address (keeps the loads in the shared state space) ----
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
 }
 
 // ---- TMA (plain tile loads; no multicast anywhere) ---------------------------
