@@ -30,6 +30,7 @@
 // Every mbarrier wait is bounded (tc_common.cuh); on a time-out the CTA records
 // a status code, all roles leave their loops, and tensor memory is released.
 
+#include <cstdlib>
 #include "moe_kernels.h"
 #include "tc_common.cuh"
 
@@ -49,8 +50,6 @@ constexpr int kCtrlWarps = 1 + kMaxIssuers;  // warp 0: the two TMA producers (l
                                              // (20 warps in all: register files are handed out four warps at a time)
 constexpr int kWGs = kSubs;        // dequantiser warpgroups: warpgroup w converts K slice w of every stage
 constexpr int kDequantWarps = 4 * kWGs;
-constexpr int kGroups = 2;         // dequantiser groups that take alternate stages
-constexpr int kGroupWarps = kDequantWarps / kGroups;
 constexpr int kThreads = 32 * (kCtrlWarps + kDequantWarps);
 constexpr int kTmemCols = 512;     // one CTA per SM owns all of tensor memory
 constexpr int kPackedStageBytes = kTileRows * (kStageK / 2);  // 16 KiB
@@ -63,6 +62,14 @@ constexpr int kScaleStageBytes = kTileRows * (kStageK / 32) * 2;  // 2 KiB
 // once.  A finer hand-off (64 K) was measured to be bound by the issuing thread's own loop
 // (about 1000 cycles per slice under the dequantisers' issue pressure) and not by the tensor pipe.
 template <int BT, int MATS = 1> struct TcCfg {
+  // Dequantiser groups that take alternate stages.  Narrow tiles: two groups of eight warps, so
+  // that one group's waits and store drains overlap the other's arithmetic.  Wide tiles are bound by
+  // the tensor pipe and have only two A slots; there all sixteen warps fill one slot together,
+  // which halves the fill latency in the slot's round trip.
+  static constexpr int kGroups = (BT <= 64) ? 2 : 1;
+  static constexpr int kGroupWarps = kDequantWarps / kGroups;
+  static constexpr int kPartsPerStage = kWGs / kGroups;      // warpgroups that share one stage
+  static constexpr int kChunks = 8 / kPartsPerStage;         // 16-byte chunks (32 weights, one scale group) per thread and stage
   static constexpr int kBStages = (BT <= 64) ? 3 : 2;
   static constexpr int kBSubBytes = BT * kSubK * 2;
   static constexpr int kBStageBytes = kSubs * kBSubBytes;   // [4][BT x 64] bf16
@@ -78,8 +85,13 @@ template <int BT, int MATS = 1> struct TcCfg {
   // over three issuers: issuer j takes the K=16 steps j, j + kIssuers, ... of EVERY stage into its
   // own accumulators, which the epilogue adds.  (Three, because with the producer warp and the
   // sixteen dequantiser warps that makes 20 warps; registers are handed out four warps at a time.)
-  static constexpr int kIssuers = (BT <= 32) ? 3 : (BT <= 64) ? 2 : 1;
-  static constexpr int kAccs = kIssuers * MATS;             // accumulator (issuer j, matrix m) = j * MATS + m
+  static constexpr int kPerStage = (BT <= 32) ? 3 : (BT <= 64) ? 2 : 1;   // issuers that share one stage's MMAs
+  // Wide tiles are bound by the tensor pipe, not by the issue rate; in a two-matrix mode they give
+  // each matrix its own issuer (it visits every second stage; the A ring of two slots is then used
+  // by one issuer per slot), so that one issuer's waits and commits overlap the other's MMAs.
+  static constexpr int kMatSplit = (BT > 64 && MATS == 2) ? 2 : 1;
+  static constexpr int kIssuers = kPerStage * kMatSplit;
+  static constexpr int kAccs = kPerStage * MATS;            // accumulator (step share j, matrix m) = j * MATS + m
   static constexpr int kDBuf = (2 * kAccs * BT + 3 * kSlotCols <= kTmemCols) ? 2 : 1;
   static constexpr int kDCols = kDBuf * kAccs * BT;         // accumulator a of set d at (d * kAccs + a) * BT
   static constexpr int kACol0 = kDCols;                     // the A slots follow the accumulators
@@ -222,8 +234,8 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kWStages; ++i) { mbar_init(&w_full[i], 1); mbar_init(&w_empty[i], 1); }
-    for (int i = 0; i < Cfg::kBStages; ++i) { mbar_init(&b_full[i], 1); mbar_init(&b_empty[i], Cfg::kIssuers * kMatsC); }
-    for (int i = 0; i < Cfg::kASlots; ++i) { mbar_init(&a_full[i], kGroupWarps); mbar_init(&a_empty[i], Cfg::kIssuers); }
+    for (int i = 0; i < Cfg::kBStages; ++i) { mbar_init(&b_full[i], 1); mbar_init(&b_empty[i], Cfg::kPerStage * kMatsC); }
+    for (int i = 0; i < Cfg::kASlots; ++i) { mbar_init(&a_full[i], Cfg::kGroupWarps); mbar_init(&a_empty[i], Cfg::kPerStage); }
     for (int i = 0; i < Cfg::kDBuf; ++i) { mbar_init(&d_full[i], Cfg::kIssuers); mbar_init(&d_empty[i], kDequantWarps); }
     *abort_word = 0;
     mbar_fence_init();
@@ -234,7 +246,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_slot, 0);   // (marks it warp-uniform)
 
   // tile index t -> (K part, token block, row tile); the row tile varies fastest so that CTAs that run
   // together share the token block and walk through one expert's weights
@@ -313,11 +325,14 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
       uint32_t aq = 0, aph = 0, bst = 0, bph = 0, wst = 0, it = 0;
       // this issuer's K=16 steps of a stage: m = me, me + kIssuers, ... < 16; step m reads A columns
       // [8 m, 8 m + 8) of the slot and token sub-tile m / 4 at K offset (m % 4) * 32 bytes
-      constexpr int kMyMax = (kSubs * (kSubK / 16) + kIssuers - 1) / kIssuers;
+      constexpr int kPerStage = Cfg::kPerStage;
+      const uint32_t my_share = me / Cfg::kMatSplit;      // which share of a stage's K=16 steps
+      const int my_mat = (int)(me % Cfg::kMatSplit);      // kMatSplit == 2: the matrix this issuer serves
+      constexpr int kMyMax = (kSubs * (kSubK / 16) + kPerStage - 1) / kPerStage;
       uint32_t b_off[kMyMax];
 #pragma unroll
       for (int i = 0; i < kMyMax; ++i) {
-        const uint32_t m = me + (uint32_t)(i * kIssuers);
+        const uint32_t m = my_share + (uint32_t)(i * kPerStage);
         b_off[i] = (((m >> 2) * (uint32_t)Cfg::kBSubBytes) >> 4) + (m & 3u) * 2u;
       }
       for (int64_t t = blockIdx.x; t < total_tiles && !guard.aborted(); t += gridDim.x, ++it) {
@@ -327,23 +342,31 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
         if (ok) tc_fence_after();
         for (int vs = 0; vs < v_stages && ok; ++vs) {
           const int mat = vs % kMats;                       // which matrix this stage belongs to
+          if (Cfg::kMatSplit == 2 && mat != my_mat) {       // the other issuer's stage: only keep the rings in step
+            if (++aq == (uint32_t)Cfg::kASlots) { aq = 0; aph ^= 1; }
+            if (++wst == (uint32_t)kWStages) wst = 0;
+            if (mat == kMats - 1) {
+              if (++bst == (uint32_t)Cfg::kBStages) { bst = 0; bph ^= 1; }
+            }
+            continue;
+          }
           TRACE_ISS(1);
           ok = mbar_wait(&a_full[aq], aph, guard, 3, 32);
           TRACE_ISS(2);
           // every dequantiser warp has arrived, so all of them are done with the weight stage in
           // shared memory: hand it back to the producer on their behalf
-          if (ok && me == 0) mbar_arrive(&w_empty[wst]);
+          if (ok && my_share == 0) mbar_arrive(&w_empty[wst]);
           // two-matrix modes: the second matrix re-uses the token stage of the first
-          if (ok && mat == 0) ok = mbar_wait(&b_full[bst], bph, guard, 4);
+          if (ok && (mat == 0 || Cfg::kMatSplit == 2)) ok = mbar_wait(&b_full[bst], bph, guard, 4);
           if (!ok) break;
           tc_fence_after();
           TRACE_ISS(3);
-          const uint32_t d_tmem = tmem_base + (uint32_t)((((int)dbuf * kIssuers + (int)me) * kMats + mat) * BT);
+          const uint32_t d_tmem = tmem_base + (uint32_t)((((int)dbuf * kPerStage + (int)my_share) * kMats + mat) * BT);
           const uint32_t a_tmem = tmem_base + Cfg::kACol0 + aq * kSlotCols;
           const uint64_t b_desc = umma_desc_k_sw128(smem_u32(s_tokens + bst * Cfg::kBStageBytes));
 #pragma unroll
           for (int i = 0; i < kMyMax; ++i) {
-            const uint32_t m = me + (uint32_t)(i * kIssuers);
+            const uint32_t m = my_share + (uint32_t)(i * kPerStage);
             if (m < (uint32_t)(kSubs * (kSubK / 16)))
               umma_ts_bf16(d_tmem, a_tmem + m * 8, b_desc + (uint64_t)b_off[i], idesc,
                            (vs < kMats && i == 0) ? 0u : 1u);
@@ -352,7 +375,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
           tc_commit(&a_empty[aq]);
           if (++aq == (uint32_t)Cfg::kASlots) { aq = 0; aph ^= 1; }
           if (++wst == (uint32_t)kWStages) wst = 0;
-          tc_commit(&b_empty[bst]);   // kIssuers * kMats arrivals release the token stage
+          tc_commit(&b_empty[bst]);   // kPerStage * kMats arrivals release the token stage
           if (mat == kMats - 1) {
             if (++bst == (uint32_t)Cfg::kBStages) { bst = 0; bph ^= 1; }
           }
@@ -371,8 +394,9 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
     // Inside a group, warpgroup h converts the K slices 2h and 2h+1 (128 of the stage's 256 K) into
     // columns [64 h, 64 h + 64) of the stage's A slot, eight columns per tcgen05.st.
     const int wg = (warp - kCtrlWarps) >> 2;
-    const uint32_t grp = (uint32_t)wg >> 1;
-    const int half = wg & 1;
+    constexpr int kGroups = Cfg::kGroups, kChunks = Cfg::kChunks;
+    const uint32_t grp = (uint32_t)wg / Cfg::kPartsPerStage;
+    const int part = wg % Cfg::kPartsPerStage;   // which share of the stage's chunks this warpgroup converts
     const int quarter = warp & 3;              // tensor-memory lane quarter this warp may access
     const int row = quarter * 32 + lane;       // weight row inside the tile
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
@@ -382,8 +406,9 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
       const int rt = (int)(t % n_tiles), b = (int)(t / n_tiles);
       const int nt = rt % n_row_tiles, ks0 = (rt / n_row_tiles) * k_stages;
       const int64_t grow = (int64_t)tile_row(b, nt, vs) + row;
-      return __ldg(reinterpret_cast<const uint32_t*>(p.mx_scale + grow * (p.K / 32) +
-                                                     (ks0 + vs / kMats) * (kStageK / 32) + half * 4));
+      const uint8_t* sp = p.mx_scale + grow * (p.K / 32) + (ks0 + vs / kMats) * (kStageK / 32) + part * kChunks;
+      if (kChunks == 4) return __ldg(reinterpret_cast<const uint32_t*>(sp));
+      return __ldg(reinterpret_cast<const uint16_t*>(sp));
     };
     // Epilogue of tile (b, nt, kpart) whose accumulators sit in set `dbuf` (use number `duse` of that
     // set).  It runs one weight stage into the NEXT tile (or after the last tile), so that the MMAs
@@ -410,7 +435,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
         if (kMats == 2) tmem_ld_32x16(d_base + BT + c0, more);
         tmem_wait_ld();
 #pragma unroll
-        for (int j = 1; j < Cfg::kIssuers; ++j) {
+        for (int j = 1; j < Cfg::kPerStage; ++j) {
           uint32_t part[16];
           tmem_ld_32x16(d_base + (j * kMats) * BT + c0, part);
           tmem_wait_ld();
@@ -501,27 +526,28 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
         if (!mbar_wait(&w_full[wst], wph, guard, 5)) { ok = false; break; }
         if (tracer) TRACE(3 + wg, 2);
         const uint32_t pk = s_packed_u32 + wst * kPackedStageBytes + row * 128;
-        uint2 sw = make_uint2(0, 0);  // INT4: the four bf16 group scales of this half stage; MXFP4: .x = its four e8m0 bytes
+        uint2 sw = make_uint2(0, 0);  // INT4: the kChunks bf16 group scales of this share; MXFP4: .x = its e8m0 bytes
         if (mode_is_int4(MODE)) {
-          sw = lds64(s_scale_u32 + wst * kScaleStageBytes + row * 16 + half * 8);
+          if (kChunks == 4) sw = lds64(s_scale_u32 + wst * kScaleStageBytes + row * 16 + part * 8);
+          else sw.x = lds32(s_scale_u32 + wst * kScaleStageBytes + row * 16 + part * 4);
         } else {
           sw.x = mx_next;
           int64_t tn = t; int vn = vs; uint32_t gn = g0;
           if (next_own(tn, vn, gn)) mx_next = mx_scale_load(tn, vn);
         }
-        // 16-byte chunk = 32 weights = one scale group; this half stage is chunks 4 half .. 4 half + 3
-        uint4 w4[4];
+        // 16-byte chunk = 32 weights = one scale group; this share is chunks kChunks * part ...
+        uint4 w4[kChunks];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) w4[c] = lds128(pk + (((half * 4 + c) ^ (row & 7)) << 4));
+        for (int c = 0; c < kChunks; ++c) w4[c] = lds128(pk + (((part * kChunks + c) ^ (row & 7)) << 4));
         // (the stage is handed back to the producer by the MMA issuer once all warps of the group have
         // published the converted slices, which they do after these loads)
         if (tracer) TRACE(3 + wg, 3);
         if (!mbar_wait(&a_empty[aq], aph ^ 1, guard, 6)) { ok = false; break; }
         tc_fence_after();
         if (tracer) TRACE(3 + wg, 4);
-        const uint32_t dst = tmem_base + lane_base + Cfg::kACol0 + aq * kSlotCols + half * (2 * kSubCols);
+        const uint32_t dst = tmem_base + lane_base + Cfg::kACol0 + aq * kSlotCols + part * (kChunks * 16);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < kChunks; ++c) {
           const uint32_t words[4] = {w4[c].x, w4[c].y, w4[c].z, w4[c].w};
           if (mode_is_int4(MODE)) {
             const uint32_t s01 = (c < 2) ? sw.x : sw.y;
@@ -742,7 +768,7 @@ int launch_int4_tc(const void* A, const int32_t* packed, const void* scale, cons
     case 32: return launch_bt<32, kModeInt4>(tm_packed, tm_scale, tm_tokens, prm, max_tiles, stream);
     case 64: return launch_bt<64, kModeInt4>(tm_packed, tm_scale, tm_tokens, prm, max_tiles, stream);
     case 128:
-      if (N % (2 * kTileRows) == 0)
+      if (N % (2 * kTileRows) == 0 && getenv("XKB_NO_PAIR") == nullptr)
         return launch_bt<128, kModeInt4Pair>(tm_packed, tm_scale, tm_tokens, prm, max_tiles / 2, stream);
       return launch_bt<128, kModeInt4>(tm_packed, tm_scale, tm_tokens, prm, max_tiles, stream);
     default: return fail(XKB_ERR_ARG, "int4 tcgen05 path: unsupported token tile %d", r.block);
