@@ -37,6 +37,8 @@ def test_golden(name, path, cuda_device):
 @pytest.mark.parametrize("M,hidden,ispp,E,top_k,bias", [
     (1, 64, 32, 4, 2, False), (37, 96, 64, 8, 3, True), (16, 256, 128, 5, 4, False),
     (48, 512, 256, 16, 6, True),
+    (640, 512, 256, 4, 2, True),      # more than 48 slots per expert: the 128-token tiles
+    (300, 256, 512, 3, 2, False),     # ragged last blocks in the wide mode
 ])
 def test_against_oracle_with_repeated_ids(M, hidden, ispp, E, top_k, bias, cuda_device):
     g = torch.Generator().manual_seed(M + hidden)

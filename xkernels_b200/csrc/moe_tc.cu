@@ -1,31 +1,42 @@
-// tcgen05 grouped expert GEMM for INT4 W4A16 (sm_100a).
+// tcgen05 grouped expert GEMM for INT4 W4A16 and MXFP4 weights (sm_100a).
 //
 // Swap-AB formulation: the 4-bit weights are the UMMA "A" operand (M = 128
 // weight rows per CTA tile) and the routed tokens the "B" operand (N = BT
 // tokens of one expert block), so a decode batch with a handful of tokens per
 // expert still fills the 128-row datapath and the kernel's cost is the weight
-// stream.  Per CTA, twelve warps:
+// stream.  One persistent CTA per SM (it owns all 512 tensor-memory columns),
+// twenty warps, everything handed over in whole 256-K stages:
 //
-//   warp 0   TMA producer, weights: packed int32 tile [128 rows x 128 B] (128B
+//   warp 0   lane 0: TMA producer, weights: packed tile [128 rows x 128 B] (128B
 //            swizzle, so that one row per thread reads conflict-free) + bf16
-//            scale tile [128 x 8] per 256-wide K stage.
-//   warp 1   TMA producer, tokens: [BT x 64] bf16 tiles (128B swizzle = the UMMA
-//            K-major canonical layout) from the gathered activation buffer.
-//            It also allocates and releases tensor memory.
-//   warps 2-3 MMA issuers: tcgen05.mma kind::f16, A from tensor memory, B from
-//            shared memory, fp32 accumulators in tensor memory (two issuers with
-//            one accumulator each for token tiles <= 64, one issuer above).
-//   warps 4-11 dequantisers: thread = weight row; nibbles -> exact bf16 integers
+//            scale tile [128 x 8] per stage (MXFP4 scales are read from global
+//            memory by the dequantisers).
+//            lane 1: TMA producer, tokens: four [BT x 64] bf16 sub-tiles per stage
+//            (128B swizzle = the UMMA K-major canonical layout) from the gathered
+//            activation buffer.
+//   warps 1-3 MMA issuers (lane 0 each; warp 1 also allocates and frees tensor
+//            memory): tcgen05.mma kind::f16, A from tensor memory, B from shared
+//            memory, fp32 accumulators in tensor memory.  The sixteen K=16 steps of
+//            a stage are split over the issuers, each into its own accumulator.
+//   warps 4-19 dequantisers: thread = weight row; nibbles -> exact bf16 integers
 //            by the 0x4300|nib trick, minus 136, times the group scale in one
 //            bf16 multiply (= the reference's single rounding,
 //            src/xkernels/ops/moe/w4a16.py:44-50), written to tensor memory with
-//            tcgen05.st as the next 64-wide A slice.  They also run the epilogue:
-//            tcgen05.ld, x topk_w in fp32, store to the fp32 slot-indexed rows.
+//            tcgen05.st as (their share of) the stage's 128-column A slot.  They
+//            also run the epilogue, one stage into the next tile: tcgen05.ld, sum
+//            of the issuers' partial accumulators, x topk_w in fp32, store to the
+//            fp32 slot-indexed rows (or the fused SwiGLU of the MXFP4 gate_up mode).
 //
 // The dequantiser emits each packed word's nibbles in the order 0,4,1,5,2,6,3,7
 // (two nibbles per mask, no cross-lane moves); the activation gather kernel
 // writes A with the same permutation inside every group of eight K elements, so
 // the dot products are unchanged.
+//
+// mbarrier parity waits only tell "the phase with this parity is over", so a
+// waiter must never fall two phases behind a barrier.  Every role here either
+// visits every use of a barrier in order or skips uses in a pattern for which the
+// previous use is implied by something it has already seen; the configuration
+// comments say which.
 //
 // Every mbarrier wait is bounded (tc_common.cuh); on a time-out the CTA records
 // a status code, all roles leave their loops, and tensor memory is released.
@@ -42,13 +53,13 @@ using namespace tc;
 constexpr int kTileRows = 128;   // weight rows per tile (UMMA M)
 constexpr int kStageK = 256;     // K per pipeline stage (weights, tokens and the tensor-memory A slot alike)
 constexpr int kSubK = 64;        // K per 128-byte swizzled token sub-tile / per dequantiser warpgroup
-constexpr int kSubs = kStageK / kSubK;
+constexpr int kSubs = kStageK / kSubK;  // 4
 constexpr int kSlotCols = kStageK / 2;                 // 128 columns of bf16 pairs per A slot
 constexpr int kSubCols = kSubK / 2;                    // 32 of them per warpgroup
 constexpr int kMaxIssuers = 3;
 constexpr int kCtrlWarps = 1 + kMaxIssuers;  // warp 0: the two TMA producers (lanes 0 and 1); warps 1-3: MMA issuers
                                              // (20 warps in all: register files are handed out four warps at a time)
-constexpr int kWGs = kSubs;        // dequantiser warpgroups: warpgroup w converts K slice w of every stage
+constexpr int kWGs = 4;            // dequantiser warpgroups (the four warps of one cover the four tensor-memory lane quarters)
 constexpr int kDequantWarps = 4 * kWGs;
 constexpr int kThreads = 32 * (kCtrlWarps + kDequantWarps);
 constexpr int kTmemCols = 512;     // one CTA per SM owns all of tensor memory
@@ -57,15 +68,18 @@ constexpr int kScaleStageBytes = kTileRows * (kStageK / 32) * 2;  // 2 KiB
 
 // MATS = weight matrices that alternate 256-K stages inside one tile (MXFP4 gate/up, INT4 row-tile pairs)
 //
-// The hand-off between the dequantisers and the MMA issuer is one whole 256-K stage: sixteen warps
-// fill a 128-column slot, the issuer waits once, issues sixteen MMAs back to back and commits
-// once.  A finer hand-off (64 K) was measured to be bound by the issuing thread's own loop
-// (about 1000 cycles per slice under the dequantisers' issue pressure) and not by the tensor pipe.
+// The hand-off between the dequantisers and the MMA issuers is one whole 256-K stage.  A finer
+// hand-off (64 K) was measured to be bound by the issuing thread's own loop (about 1000 cycles
+// per 64-K slice under the dequantisers' issue pressure) and not by the tensor pipe.
 template <int BT, int MATS = 1> struct TcCfg {
   // Dequantiser groups that take alternate stages.  Narrow tiles: two groups of eight warps, so
   // that one group's waits and store drains overlap the other's arithmetic.  Wide tiles are bound by
   // the tensor pipe and have only two A slots; there all sixteen warps fill one slot together,
   // which halves the fill latency in the slot's round trip.
+  // (Parity safety with two groups: a group re-uses a weight stage only after its own previous use
+  // of it, since the ring depths are even; on the three-slot A ring it waits for the MMAs of stage
+  // g - 3 having seen those of stage g - 5 complete, and each issuer's commits arrive in stage order,
+  // so the MMAs of stage g - 6, the slot's previous round, are over as well.)
   static constexpr int kGroups = (BT <= 64) ? 2 : 1;
   static constexpr int kGroupWarps = kDequantWarps / kGroups;
   static constexpr int kPartsPerStage = kWGs / kGroups;      // warpgroups that share one stage
@@ -74,30 +88,33 @@ template <int BT, int MATS = 1> struct TcCfg {
   static constexpr int kBSubBytes = BT * kSubK * 2;
   static constexpr int kBStageBytes = kSubs * kBSubBytes;   // [4][BT x 64] bf16
   static constexpr int kWStages = (BT <= 32) ? 6 : 4;
-  // Two accumulator sets when tensor memory has room: the MMAs of the next tile start while the
-  // previous tile's accumulators are still being read out.
+  static_assert(kWStages % kGroups == 0, "a weight stage must always be converted by the same group");
   // MMA issuers.  One thread sustains one tcgen05.mma per ~45 cycles (65-100 beside busy
   // dequantiser warps) whatever the shape, and that is an issue limit of the thread, not of the
   // tensor pipe: measured aggregate rates for N = 16 are 45 / 27 / 13 cycles per MMA with 1 / 2 / 4
   // issuing warps, while N = 128 is pipe-bound at 64 cycles.  The time a stage's MMAs take to issue
   // is part of the A slot's round trip (fill -> MMAs -> commit -> fill), and with three slots that
-  // round trip bounds the whole kernel, so narrow token tiles split the sixteen MMAs of a stage
-  // over three issuers: issuer j takes the K=16 steps j, j + kIssuers, ... of EVERY stage into its
-  // own accumulators, which the epilogue adds.  (Three, because with the producer warp and the
-  // sixteen dequantiser warps that makes 20 warps; registers are handed out four warps at a time.)
+  // round trip bounds the kernel, so narrow token tiles split the sixteen MMAs of a stage over
+  // three issuers: issuer j takes the K=16 steps j, j + 3, ... of EVERY stage into its own
+  // accumulators, which the epilogue adds.  (Three, because with the producer warp and the sixteen
+  // dequantiser warps that makes 20 warps; register files are handed out four warps at a time.)
   static constexpr int kPerStage = (BT <= 32) ? 3 : (BT <= 64) ? 2 : 1;   // issuers that share one stage's MMAs
   // Wide tiles are bound by the tensor pipe, not by the issue rate; in a two-matrix mode they give
-  // each matrix its own issuer (it visits every second stage; the A ring of two slots is then used
-  // by one issuer per slot), so that one issuer's waits and commits overlap the other's MMAs.
+  // each matrix its own issuer (it visits every second stage; of the two A slots each is then
+  // always used by the same issuer), so that one issuer's waits and commits overlap the other's MMAs.
   static constexpr int kMatSplit = (BT > 64 && MATS == 2) ? 2 : 1;
   static constexpr int kIssuers = kPerStage * kMatSplit;
+  static_assert(kIssuers <= kMaxIssuers, "not enough issuer warps");
   static constexpr int kAccs = kPerStage * MATS;            // accumulator (step share j, matrix m) = j * MATS + m
+  // Two accumulator sets when tensor memory has room: the MMAs of the next tile start while the
+  // previous tile's accumulators are still being read out.
   static constexpr int kDBuf = (2 * kAccs * BT + 3 * kSlotCols <= kTmemCols) ? 2 : 1;
   static constexpr int kDCols = kDBuf * kAccs * BT;         // accumulator a of set d at (d * kAccs + a) * BT
   static constexpr int kACol0 = kDCols;                     // the A slots follow the accumulators
   static constexpr int kASlotsFit = (kTmemCols - kDCols) / kSlotCols;
   static constexpr int kASlots = kASlotsFit > 3 ? 3 : kASlotsFit;
   static_assert(kASlots >= 2, "need two A slots so that conversion and MMA overlap");
+  static_assert(kMatSplit == 1 || kASlots == 2, "per-matrix issuers rely on slot parity = matrix");
   static constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + (size_t)kWStages * kPackedStageBytes +
                                        (size_t)kBStages * kBStageBytes + (size_t)kWStages * kScaleStageBytes +
                                        1024 /*barriers*/;
@@ -785,10 +802,10 @@ bool mxfp4_tc_supported(int a_dtype, int64_t M, int64_t hidden, int64_t ispp, in
 }
 
 int mxfp4_tc_block(int64_t numel, int E) {
-  // the gate_up mode keeps four accumulators beside the six A slots in 256 tensor-memory columns:
-  // token tiles of 16 (experts with more tokens take several blocks and re-read their weights from L2)
-  (void)numel; (void)E;
-  return 16;
+  // decode-sized batches: token tiles of 16; prefill-sized ones: 128 (gate and up then get one
+  // MMA issuer each, like the row-tile pairs of the INT4 wide mode)
+  const double avg = (double)numel / (E > 0 ? E : 1);
+  return avg <= 48 ? 16 : 128;
 }
 
 int64_t mxfp4_tc_workspace_bytes(int64_t numel, int64_t hidden, int64_t ispp, int E) {
@@ -800,7 +817,7 @@ int launch_mxfp4_tc(const void* A, const uint8_t* w13, const uint8_t* w13_scale,
                     const uint8_t* w2_scale, const void* b13, const void* b2, const Routing& r,
                     const float* topk_w, __nv_bfloat16* act, float* scratch, int64_t hidden, int64_t ispp,
                     int E, int top_k, float limit, int mul_w, void* tc_ws, int* status, cudaStream_t stream) {
-  XKB_REQUIRE(r.block == 16, "mxfp4 tcgen05 path: unsupported token tile %d", r.block);
+  XKB_REQUIRE(r.block == 16 || r.block == 128, "mxfp4 tcgen05 path: unsupported token tile %d", r.block);
   XKB_REQUIRE(reinterpret_cast<uintptr_t>(w13_scale) % 8 == 0 && reinterpret_cast<uintptr_t>(w2_scale) % 8 == 0,
               "mxfp4 tcgen05 path: scale tensors must be 8-byte aligned");
   Carver carve(tc_ws);
@@ -845,7 +862,8 @@ int launch_mxfp4_tc(const void* A, const uint8_t* w13, const uint8_t* w13_scale,
   prm.mx_scale = w13_scale;
   prm.bias = static_cast<const __nv_bfloat16*>(b13);
   int64_t max_tiles = r.max_blocks * (ispp / kTileRows);
-  rc = launch_bt<16, kModeMxGateUp>(tm_w13, tm_w13, tm_tok0, prm, max_tiles, stream);
+  rc = r.block == 16 ? launch_bt<16, kModeMxGateUp>(tm_w13, tm_w13, tm_tok0, prm, max_tiles, stream)
+                     : launch_bt<128, kModeMxGateUp>(tm_w13, tm_w13, tm_tok0, prm, max_tiles, stream);
   if (rc != XKB_OK) return rc;
   // stage 1: down -> fp32 slot rows
   prm.scratch = scratch;
@@ -856,7 +874,8 @@ int launch_mxfp4_tc(const void* A, const uint8_t* w13, const uint8_t* w13_scale,
   prm.mx_scale = w2_scale;
   prm.bias = static_cast<const __nv_bfloat16*>(b2);
   max_tiles = r.max_blocks * (hidden / kTileRows);
-  return launch_bt<16, kModeMxDown>(tm_w2, tm_w2, tm_tok1, prm, max_tiles, stream);
+  return r.block == 16 ? launch_bt<16, kModeMxDown>(tm_w2, tm_w2, tm_tok1, prm, max_tiles, stream)
+                       : launch_bt<128, kModeMxDown>(tm_w2, tm_w2, tm_tok1, prm, max_tiles, stream);
 }
 
 }  // namespace xkb
