@@ -71,15 +71,14 @@ constexpr int kScaleStageBytes = kTileRows * (kStageK / 32) * 2;  // 2 KiB
 // The hand-off between the dequantisers and the MMA issuers is one whole 256-K stage.  A finer
 // hand-off (64 K) was measured to be bound by the issuing thread's own loop (about 1000 cycles
 // per 64-K slice under the dequantisers' issue pressure) and not by the tensor pipe.
+constexpr int gcd_c(int a, int b) { return b == 0 ? a : gcd_c(b, a % b); }
+constexpr int lcm_c(int a, int b) { return a / gcd_c(a, b) * b; }
+
 template <int BT, int MATS = 1> struct TcCfg {
   // Dequantiser groups that take alternate stages.  Narrow tiles: two groups of eight warps, so
   // that one group's waits and store drains overlap the other's arithmetic.  Wide tiles are bound by
   // the tensor pipe and have only two A slots; there all sixteen warps fill one slot together,
   // which halves the fill latency in the slot's round trip.
-  // (Parity safety with two groups: a group re-uses a weight stage only after its own previous use
-  // of it, since the ring depths are even; on the three-slot A ring it waits for the MMAs of stage
-  // g - 3 having seen those of stage g - 5 complete, and each issuer's commits arrive in stage order,
-  // so the MMAs of stage g - 6, the slot's previous round, are over as well.)
   static constexpr int kGroups = (BT <= 64) ? 2 : 1;
   static constexpr int kGroupWarps = kDequantWarps / kGroups;
   static constexpr int kPartsPerStage = kWGs / kGroups;      // warpgroups that share one stage
@@ -92,20 +91,18 @@ template <int BT, int MATS = 1> struct TcCfg {
   // MMA issuers.  One thread sustains one tcgen05.mma per ~45 cycles (65-100 beside busy
   // dequantiser warps) whatever the shape, and that is an issue limit of the thread, not of the
   // tensor pipe: measured aggregate rates for N = 16 are 45 / 27 / 13 cycles per MMA with 1 / 2 / 4
-  // issuing warps, while N = 128 is pipe-bound at 64 cycles.  The time a stage's MMAs take to issue
-  // is part of the A slot's round trip (fill -> MMAs -> commit -> fill), and with three slots that
-  // round trip bounds the kernel, so narrow token tiles split the sixteen MMAs of a stage over
-  // three issuers: issuer j takes the K=16 steps j, j + 3, ... of EVERY stage into its own
-  // accumulators, which the epilogue adds.  (Three, because with the producer warp and the sixteen
-  // dequantiser warps that makes 20 warps; register files are handed out four warps at a time.)
-  static constexpr int kPerStage = (BT <= 32) ? 3 : (BT <= 64) ? 2 : 1;   // issuers that share one stage's MMAs
-  // Wide tiles are bound by the tensor pipe, not by the issue rate; in a two-matrix mode they give
-  // each matrix its own issuer (it visits every second stage; of the two A slots each is then
-  // always used by the same issuer), so that one issuer's waits and commits overlap the other's MMAs.
-  static constexpr int kMatSplit = (BT > 64 && MATS == 2) ? 2 : 1;
-  static constexpr int kIssuers = kPerStage * kMatSplit;
+  // issuing warps, while N = 128 is pipe-bound at 64 cycles.  Besides the MMAs a visit to a stage
+  // costs the issuing thread several hundred cycles of waits, fences and commits, so the issuers
+  // take whole stages in turn: stage g (numbered across the tiles of the CTA) belongs to issuer
+  // g % kIssuers, which puts it into its own accumulator (per matrix); the epilogue adds them.
+  // (Three issuers, because with the producer warp and the sixteen dequantiser warps that makes 20
+  // warps; register files are handed out four warps at a time.)
+  static constexpr int kIssuers = (BT <= 32) ? 3 : 2;
   static_assert(kIssuers <= kMaxIssuers, "not enough issuer warps");
-  static constexpr int kAccs = kPerStage * MATS;            // accumulator (step share j, matrix m) = j * MATS + m
+  // kIssuers == MATS: the stage's parity is its matrix and its issuer at once (a tile has a multiple
+  // of MATS stages), so one accumulator per matrix is enough.
+  static constexpr bool kLocked = (kIssuers == MATS);
+  static constexpr int kAccs = kLocked ? MATS : kIssuers * MATS;   // accumulator (issuer j, matrix m) = j * MATS + m
   // Two accumulator sets when tensor memory has room: the MMAs of the next tile start while the
   // previous tile's accumulators are still being read out.
   static constexpr int kDBuf = (2 * kAccs * BT + 3 * kSlotCols <= kTmemCols) ? 2 : 1;
@@ -114,7 +111,14 @@ template <int BT, int MATS = 1> struct TcCfg {
   static constexpr int kASlotsFit = (kTmemCols - kDCols) / kSlotCols;
   static constexpr int kASlots = kASlotsFit > 3 ? 3 : kASlotsFit;
   static_assert(kASlots >= 2, "need two A slots so that conversion and MMA overlap");
-  static_assert(kMatSplit == 1 || kASlots == 2, "per-matrix issuers rely on slot parity = matrix");
+  // mbarrier parity waits only tell "the phase with this parity is over", so a waiter must see every
+  // phase of a barrier it waits on.  Stage g is filled by group g % kGroups and consumed by issuer
+  // g % kIssuers; its barriers are therefore number g % kABars with kABars a common multiple of the
+  // slot count, kGroups and kIssuers (the slot itself is g % kASlots): every barrier then always
+  // has the same producer group and the same consumer, and both pass through all of its phases.
+  // The token ring does the same with kBBars (the producer thread visits every token stage).
+  static constexpr int kABars = lcm_c(lcm_c(kASlots, kGroups), kIssuers);
+  static constexpr int kBBars = lcm_c(kBStages, kIssuers);
   static constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + (size_t)kWStages * kPackedStageBytes +
                                        (size_t)kBStages * kBStageBytes + (size_t)kWStages * kScaleStageBytes +
                                        1024 /*barriers*/;
@@ -232,11 +236,11 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
   uint64_t* bars = reinterpret_cast<uint64_t*>(s_scale + kWStages * kScaleStageBytes);
   uint64_t* w_full = bars;                       // [kWStages]
   uint64_t* w_empty = w_full + kWStages;         // [kWStages]
-  uint64_t* b_full = w_empty + kWStages;         // [kBStages]
-  uint64_t* b_empty = b_full + Cfg::kBStages;    // [kBStages]
-  uint64_t* a_full = b_empty + Cfg::kBStages;    // [kASlots]
-  uint64_t* a_empty = a_full + Cfg::kASlots;     // [kASlots]
-  uint64_t* d_full = a_empty + Cfg::kASlots;     // [kDBuf]
+  uint64_t* b_full = w_empty + kWStages;         // [kBBars]
+  uint64_t* b_empty = b_full + Cfg::kBBars;      // [kBBars]
+  uint64_t* a_full = b_empty + Cfg::kBBars;      // [kABars]
+  uint64_t* a_empty = a_full + Cfg::kABars;      // [kABars]
+  uint64_t* d_full = a_empty + Cfg::kABars;      // [kDBuf]
   uint64_t* d_empty = d_full + Cfg::kDBuf;       // [kDBuf]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(d_empty + Cfg::kDBuf);
   int* abort_word = reinterpret_cast<int*>(tmem_slot + 1);
@@ -251,8 +255,8 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kWStages; ++i) { mbar_init(&w_full[i], 1); mbar_init(&w_empty[i], 1); }
-    for (int i = 0; i < Cfg::kBStages; ++i) { mbar_init(&b_full[i], 1); mbar_init(&b_empty[i], Cfg::kPerStage * kMatsC); }
-    for (int i = 0; i < Cfg::kASlots; ++i) { mbar_init(&a_full[i], Cfg::kGroupWarps); mbar_init(&a_empty[i], Cfg::kPerStage); }
+    for (int i = 0; i < Cfg::kBBars; ++i) { mbar_init(&b_full[i], 1); mbar_init(&b_empty[i], kMatsC); }
+    for (int i = 0; i < Cfg::kABars; ++i) { mbar_init(&a_full[i], Cfg::kGroupWarps); mbar_init(&a_empty[i], 1); }
     for (int i = 0; i < Cfg::kDBuf; ++i) { mbar_init(&d_full[i], Cfg::kIssuers); mbar_init(&d_empty[i], kDequantWarps); }
     *abort_word = 0;
     mbar_fence_init();
@@ -312,90 +316,79 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
   } else if (warp == 0 && lane == 1) {
     // ---------------- token producer (diverged from lane 0; both make progress independently) ----------------
     {
-      uint32_t st = 0, ph = 0;
+      uint32_t st = 0, tb = 0;   // token stage slot and running number of the token stage
       for (int64_t t = blockIdx.x; t < total_tiles && !guard.aborted(); t += gridDim.x) {
         const int b = (int)(t / n_tiles);
         const int pos0 = b * BT;
         const int ks0 = ((int)(t % n_tiles) / n_row_tiles) * k_stages;  // first 256-K stage of this K part
         for (int ks = 0; ks < k_stages; ++ks) {
           TRACE(1, 1);
-          if (!mbar_wait(&b_empty[st], ph ^ 1, guard, 2, 400)) break;
+          // the slot's previous user was token stage tb - kBStages: wait for its readers' commits
+          if (tb >= (uint32_t)Cfg::kBStages) {
+            const uint32_t tp = tb - Cfg::kBStages;
+            if (!mbar_wait(&b_empty[tp % Cfg::kBBars], (tp / Cfg::kBBars) & 1u, guard, 2, 400)) break;
+          }
+          const uint32_t bar = tb % Cfg::kBBars;
           TRACE(1, 2);
-          mbar_expect_tx(&b_full[st], Cfg::kBStageBytes);
+          mbar_expect_tx(&b_full[bar], Cfg::kBStageBytes);
 #pragma unroll
           for (int j = 0; j < kSubs; ++j)
-            tma_load_2d(s_tokens + st * Cfg::kBStageBytes + j * Cfg::kBSubBytes, &tm_tokens, &b_full[st],
+            tma_load_2d(s_tokens + st * Cfg::kBStageBytes + j * Cfg::kBSubBytes, &tm_tokens, &b_full[bar],
                         ((ks0 + ks) * kSubs + j) * kSubK, pos0);
-          if (++st == Cfg::kBStages) { st = 0; ph ^= 1; }
+          if (++st == Cfg::kBStages) st = 0;
+          ++tb;
         }
       }
     }
   } else if (warp >= 1 && warp < kCtrlWarps) {
     // ---------------- MMA issuers ----------------
-    // Every issuer visits every stage: it waits for the A slot and the token stage, issues the
-    // M=128 N=BT K=16 MMAs of its K slices into its own accumulator and commits; slot and token
-    // stage are free again when all issuers' commits have arrived.
+    // Stage g (numbered across the tiles of this CTA) belongs to issuer g % kIssuers: it waits for
+    // the A slot and the token stage, hands the weight stage back to the producer, issues the
+    // sixteen M=128 N=BT K=16 MMAs into its own accumulator of the stage's matrix and commits.
     constexpr int kIssuers = Cfg::kIssuers;
     const uint32_t me = warp - 1;
     if (lane == 0 && me < (uint32_t)kIssuers) {
       constexpr uint32_t idesc = umma_idesc_bf16(kTileRows, BT);
-      uint32_t aq = 0, aph = 0, bst = 0, bph = 0, wst = 0, it = 0;
-      // this issuer's K=16 steps of a stage: m = me, me + kIssuers, ... < 16; step m reads A columns
-      // [8 m, 8 m + 8) of the slot and token sub-tile m / 4 at K offset (m % 4) * 32 bytes
-      constexpr int kPerStage = Cfg::kPerStage;
-      const uint32_t my_share = me / Cfg::kMatSplit;      // which share of a stage's K=16 steps
-      const int my_mat = (int)(me % Cfg::kMatSplit);      // kMatSplit == 2: the matrix this issuer serves
-      constexpr int kMyMax = (kSubs * (kSubK / 16) + kPerStage - 1) / kPerStage;
-      uint32_t b_off[kMyMax];
-#pragma unroll
-      for (int i = 0; i < kMyMax; ++i) {
-        const uint32_t m = my_share + (uint32_t)(i * kPerStage);
-        b_off[i] = (((m >> 2) * (uint32_t)Cfg::kBSubBytes) >> 4) + (m & 3u) * 2u;
-      }
-      for (int64_t t = blockIdx.x; t < total_tiles && !guard.aborted(); t += gridDim.x, ++it) {
+      uint32_t it = 0, g0 = 0;                            // g0 = number of the tile's first stage
+      for (int64_t t = blockIdx.x; t < total_tiles && !guard.aborted(); t += gridDim.x, ++it, g0 += (uint32_t)v_stages) {
         // accumulator set of this tile; its previous user must have been read out by every epilogue warp
         const uint32_t dbuf = it % Cfg::kDBuf, duse = it / Cfg::kDBuf;
         bool ok = mbar_wait(&d_empty[dbuf], (duse & 1u) ^ 1u, guard, 8, 100);
         if (ok) tc_fence_after();
-        for (int vs = 0; vs < v_stages && ok; ++vs) {
+        uint32_t started = 0;   // bit m: this issuer has already written its accumulator of matrix m in this tile
+        for (int vs = (int)((me + kIssuers - g0 % kIssuers) % kIssuers); vs < v_stages && ok; vs += kIssuers) {
+          const uint32_t g = g0 + (uint32_t)vs;
           const int mat = vs % kMats;                       // which matrix this stage belongs to
-          if (Cfg::kMatSplit == 2 && mat != my_mat) {       // the other issuer's stage: only keep the rings in step
-            if (++aq == (uint32_t)Cfg::kASlots) { aq = 0; aph ^= 1; }
-            if (++wst == (uint32_t)kWStages) wst = 0;
-            if (mat == kMats - 1) {
-              if (++bst == (uint32_t)Cfg::kBStages) { bst = 0; bph ^= 1; }
-            }
-            continue;
-          }
+          const uint32_t aq = g % Cfg::kASlots, abar = g % Cfg::kABars, aph = (g / Cfg::kABars) & 1u;
+          const uint32_t tb = g / kMats;                    // token stage read by stage g
+          const uint32_t bst = tb % Cfg::kBStages, bbar = tb % Cfg::kBBars, bph = (tb / Cfg::kBBars) & 1u;
           TRACE_ISS(1);
-          ok = mbar_wait(&a_full[aq], aph, guard, 3, 32);
+          ok = mbar_wait(&a_full[abar], aph, guard, 3, 32);
           TRACE_ISS(2);
-          // every dequantiser warp has arrived, so all of them are done with the weight stage in
-          // shared memory: hand it back to the producer on their behalf
-          if (ok && my_share == 0) mbar_arrive(&w_empty[wst]);
-          // two-matrix modes: the second matrix re-uses the token stage of the first
-          if (ok && (mat == 0 || Cfg::kMatSplit == 2)) ok = mbar_wait(&b_full[bst], bph, guard, 4);
+          // every dequantiser warp of the stage's group has arrived, so all of them are done with the
+          // weight stage in shared memory: hand it back to the producer on their behalf
+          if (ok) mbar_arrive(&w_empty[g % kWStages]);
+          if (ok) ok = mbar_wait(&b_full[bbar], bph, guard, 4);
           if (!ok) break;
           tc_fence_after();
           TRACE_ISS(3);
-          const uint32_t d_tmem = tmem_base + (uint32_t)((((int)dbuf * kPerStage + (int)my_share) * kMats + mat) * BT);
+          const int acc = Cfg::kLocked ? mat : (int)me * kMats + mat;
+          const uint32_t d_tmem = tmem_base + (uint32_t)(((int)dbuf * Cfg::kAccs + acc) * BT);
           const uint32_t a_tmem = tmem_base + Cfg::kACol0 + aq * kSlotCols;
           const uint64_t b_desc = umma_desc_k_sw128(smem_u32(s_tokens + bst * Cfg::kBStageBytes));
+          const bool fresh = ((started >> mat) & 1u) == 0;
+          started |= 1u << mat;
 #pragma unroll
-          for (int i = 0; i < kMyMax; ++i) {
-            const uint32_t m = my_share + (uint32_t)(i * kPerStage);
-            if (m < (uint32_t)(kSubs * (kSubK / 16)))
-              umma_ts_bf16(d_tmem, a_tmem + m * 8, b_desc + (uint64_t)b_off[i], idesc,
-                           (vs < kMats && i == 0) ? 0u : 1u);
+          for (int sub = 0; sub < kSubs; ++sub) {
+#pragma unroll
+            for (int kk = 0; kk < kSubK / 16; ++kk)
+              umma_ts_bf16(d_tmem, a_tmem + sub * kSubCols + kk * 8,
+                           b_desc + (uint64_t)((sub * Cfg::kBSubBytes) >> 4) + (uint64_t)(kk * 2), idesc,
+                           (fresh && sub == 0 && kk == 0) ? 0u : 1u);
           }
           TRACE_ISS(4);
-          tc_commit(&a_empty[aq]);
-          if (++aq == (uint32_t)Cfg::kASlots) { aq = 0; aph ^= 1; }
-          if (++wst == (uint32_t)kWStages) wst = 0;
-          tc_commit(&b_empty[bst]);   // kPerStage * kMats arrivals release the token stage
-          if (mat == kMats - 1) {
-            if (++bst == (uint32_t)Cfg::kBStages) { bst = 0; bph ^= 1; }
-          }
+          tc_commit(&a_empty[abar]);
+          tc_commit(&b_empty[bbar]);   // kMats arrivals release the token stage
           TRACE_ISS(5);
         }
         if (!ok) break;
@@ -430,8 +423,16 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
     // Epilogue of tile (b, nt, kpart) whose accumulators sit in set `dbuf` (use number `duse` of that
     // set).  It runs one weight stage into the NEXT tile (or after the last tile), so that the MMAs
     // it waits for have long finished and the pipeline never drains at a tile boundary.
-    auto run_epilogue = [&](int b, int nt, int kpart, uint32_t dbuf, uint32_t duse) -> bool {
+    auto run_epilogue = [&](int b, int nt, int kpart, uint32_t dbuf, uint32_t duse, uint32_t tile_g0) -> bool {
       const uint32_t d_base = tmem_base + lane_base + dbuf * (uint32_t)(Cfg::kAccs * BT);
+      // which accumulators the tile's stages went to: stage vs -> (issuer (g0 + vs) % kIssuers, matrix vs % kMats)
+      uint32_t valid = 0;
+      if (Cfg::kLocked) {
+        valid = (1u << kMats) - 1u;
+      } else {
+        for (int vs = 0; vs < v_stages && vs < Cfg::kIssuers * kMats; ++vs)
+          valid |= 1u << (((tile_g0 + (uint32_t)vs) % Cfg::kIssuers) * kMats + vs % kMats);
+      }
       if (!mbar_wait(&d_full[dbuf], duse & 1u, guard, 7)) return false;
       tc_fence_after();
       const int64_t n_glob = (int64_t)nt * (MODE == kModeInt4Pair ? 2 * kTileRows : kTileRows) + row;
@@ -446,23 +447,23 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
 #pragma unroll 1
       for (int c0 = wg * 16; c0 < BT; c0 += 16 * kWGs) {
         // acc = matrix 0 (INT4 / down: the only one; gate_up: gate; pair: first row tile), more = matrix 1,
-        // each the sum over the issuers' accumulators (issuer j, matrix m) at (j * kMats + m) * BT
+        // each the sum of the accumulators that were written in this tile
         uint32_t acc[16], more[16];
-        tmem_ld_32x16(d_base + c0, acc);
-        if (kMats == 2) tmem_ld_32x16(d_base + BT + c0, more);
-        tmem_wait_ld();
 #pragma unroll
-        for (int j = 1; j < Cfg::kPerStage; ++j) {
-          uint32_t part[16];
-          tmem_ld_32x16(d_base + (j * kMats) * BT + c0, part);
-          tmem_wait_ld();
+        for (int q = 0; q < 16; ++q) { acc[q] = 0u; more[q] = 0u; }
 #pragma unroll
-          for (int q = 0; q < 16; ++q) acc[q] = __float_as_uint(__uint_as_float(acc[q]) + __uint_as_float(part[q]));
-          if (kMats == 2) {
-            tmem_ld_32x16(d_base + (j * kMats + 1) * BT + c0, part);
+        for (int a = 0; a < Cfg::kAccs; ++a) {
+          if ((valid >> a) & 1u) {
+            uint32_t part[16];
+            tmem_ld_32x16(d_base + a * BT + c0, part);
             tmem_wait_ld();
+            if (kMats == 2 && (a & 1)) {
 #pragma unroll
-            for (int q = 0; q < 16; ++q) more[q] = __float_as_uint(__uint_as_float(more[q]) + __uint_as_float(part[q]));
+              for (int q = 0; q < 16; ++q) more[q] = __float_as_uint(__uint_as_float(more[q]) + __uint_as_float(part[q]));
+            } else {
+#pragma unroll
+              for (int q = 0; q < 16; ++q) acc[q] = __float_as_uint(__uint_as_float(acc[q]) + __uint_as_float(part[q]));
+            }
           }
         }
         if (MODE == kModeMxGateUp) {
@@ -511,7 +512,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
     };
     bool pend = false;
     int pend_b = 0, pend_nt = 0, pend_kpart = 0;
-    uint32_t pend_it = 0, it = 0, g0 = 0;      // g0 = number of the tile's first stage
+    uint32_t pend_it = 0, pend_g0 = 0, it = 0, g0 = 0;      // g0 = number of the tile's first stage
     const bool tracer = (lane == 0 && quarter == 0);
     (void)tracer;
     // the stage this group converts after (t, vs, g0): two further on, or the first own stage of a later tile
@@ -538,7 +539,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
       for (int vs = (int)((grp - g0) & (uint32_t)(kGroups - 1)); vs < v_stages && ok; vs += kGroups) {
         const uint32_t g = g0 + (uint32_t)vs;
         const uint32_t wst = g % kWStages, wph = (g / kWStages) & 1u;
-        const uint32_t aq = g % Cfg::kASlots, aph = (g / Cfg::kASlots) & 1u;
+        const uint32_t aq = g % Cfg::kASlots, abar = g % Cfg::kABars, aph = (g / Cfg::kABars) & 1u;
         if (tracer) TRACE(3 + wg, 1);
         if (!mbar_wait(&w_full[wst], wph, guard, 5)) { ok = false; break; }
         if (tracer) TRACE(3 + wg, 2);
@@ -559,7 +560,11 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
         // (the stage is handed back to the producer by the MMA issuer once all warps of the group have
         // published the converted slices, which they do after these loads)
         if (tracer) TRACE(3 + wg, 3);
-        if (!mbar_wait(&a_empty[aq], aph ^ 1, guard, 6)) { ok = false; break; }
+        // the slot's previous user was stage g - kASlots: wait until its MMAs have completed
+        if (g >= (uint32_t)Cfg::kASlots) {
+          const uint32_t gp = g - Cfg::kASlots;
+          if (!mbar_wait(&a_empty[gp % Cfg::kABars], (gp / Cfg::kABars) & 1u, guard, 6)) { ok = false; break; }
+        }
         tc_fence_after();
         if (tracer) TRACE(3 + wg, 4);
         const uint32_t dst = tmem_base + lane_base + Cfg::kACol0 + aq * kSlotCols + part * (kChunks * 16);
@@ -594,21 +599,21 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&a_full[aq]);
+        if (lane == 0) mbar_arrive(&a_full[abar]);
         if (tracer) TRACE(3 + wg, 6);
         if (epi_due) {
           epi_due = false;
-          if (!run_epilogue(pend_b, pend_nt, pend_kpart, pend_it % Cfg::kDBuf, pend_it / Cfg::kDBuf)) { ok = false; break; }
+          if (!run_epilogue(pend_b, pend_nt, pend_kpart, pend_it % Cfg::kDBuf, pend_it / Cfg::kDBuf, pend_g0)) { ok = false; break; }
         }
       }
       if (!ok) break;
       if (epi_due) {  // this group had no stage in this tile
-        if (!run_epilogue(pend_b, pend_nt, pend_kpart, pend_it % Cfg::kDBuf, pend_it / Cfg::kDBuf)) break;
+        if (!run_epilogue(pend_b, pend_nt, pend_kpart, pend_it % Cfg::kDBuf, pend_it / Cfg::kDBuf, pend_g0)) break;
       }
       // the epilogue is deferred: see run_epilogue
-      pend = true; pend_b = b; pend_nt = nt; pend_kpart = kpart; pend_it = it;
+      pend = true; pend_b = b; pend_nt = nt; pend_kpart = kpart; pend_it = it; pend_g0 = g0;
     }
-    if (pend && !guard.aborted()) run_epilogue(pend_b, pend_nt, pend_kpart, pend_it % Cfg::kDBuf, pend_it / Cfg::kDBuf);
+    if (pend && !guard.aborted()) run_epilogue(pend_b, pend_nt, pend_kpart, pend_it % Cfg::kDBuf, pend_it / Cfg::kDBuf, pend_g0);
   }
 
   tc_fence_before();
