@@ -67,12 +67,16 @@ struct Guard {
 // `sleep_ns` > 0 backs off between probes: roles that run ahead of the pipeline
 // (the TMA producers) and roles that wait on the slower side (the MMA issuers)
 // would otherwise spend issue slots on probes that the dequantiser warps need.
+#ifndef XKB_TRY_HINT_NS
+#define XKB_TRY_HINT_NS 1000
+#endif
+constexpr uint32_t kTryHintNs = XKB_TRY_HINT_NS;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Guard& g, int where,
                                           uint32_t sleep_ns = 0) {
-  if (mbar_try(bar, parity, 1000)) return true;   // the common case: already complete
+  if (mbar_try(bar, parity, kTryHintNs)) return true;   // the common case: already complete
   for (uint32_t i = 0; i < kMaxPolls; ++i) {
     if (sleep_ns) __nanosleep(sleep_ns);
-    if (mbar_try(bar, parity, 1000)) return true;
+    if (mbar_try(bar, parity, kTryHintNs)) return true;
     if ((i & 63u) == 63u && g.aborted()) return false;
   }
   g.raise(kErrWaitTimeout + (where << 8));
