@@ -83,7 +83,10 @@ template <int BT, int MATS = 1> struct TcCfg {
   static constexpr int kGroupWarps = kDequantWarps / kGroups;
   static constexpr int kPartsPerStage = kWGs / kGroups;      // warpgroups that share one stage
   static constexpr int kChunks = 8 / kPartsPerStage;         // 16-byte chunks (32 weights, one scale group) per thread and stage
-  static constexpr int kBStages = (BT <= 64) ? 3 : 2;
+  // Token ring.  A token stage is released by the commit of the MMAs that read it and re-filled by
+  // TMA from L2 about a microsecond later; narrow tiles are small, so their ring is made deep
+  // enough that the issuers never wait for tokens.
+  static constexpr int kBStages = (BT <= 16) ? 9 : (BT <= 32) ? 6 : (BT <= 64) ? 4 : 2;
   static constexpr int kBSubBytes = BT * kSubK * 2;
   static constexpr int kBStageBytes = kSubs * kBSubBytes;   // [4][BT x 64] bf16
   static constexpr int kWStages = (BT <= 32) ? 6 : 4;
