@@ -426,13 +426,14 @@ def run_multi_gpu(args, world: int, rank: int, local_rank: int):
     launches = _lib.launch_count() - launches0
     gemm_ms = _lib.gemm_timer_read()
     _lib.gemm_timer_enable(0)
-    t = torch.tensor([ms, sum(gemm_ms) / max(len(gemm_ms), 1), float(layer.last_recv_slots)], device=dev,
-                     dtype=torch.float64)
+    t = torch.tensor([ms, sum(gemm_ms) / max(len(gemm_ms), 1), float(layer.count_recv_slots()),
+                      float(layer.last_recv_rows)], device=dev, dtype=torch.float64)
     gathered = [torch.zeros_like(t) for _ in range(world)]
     dist.all_gather(gathered, t)
     ms_max = max(float(g[0]) for g in gathered)
     gemm_max = max(float(g[1]) for g in gathered)
     slots = [int(g[2]) for g in gathered]
+    rows_in = [int(g[3]) for g in gathered]
 
     # end to end: pinned host activations/routing in, result out
     hA, hI, hW = A.cpu().pin_memory(), ids.cpu().pin_memory(), w.cpu().pin_memory()
@@ -475,6 +476,7 @@ def run_multi_gpu(args, world: int, rank: int, local_rank: int):
                          "kernel": "moe_tc_kernel (busiest rank)", "kernel_ms": gemm_max,
                          "peak_source": peaks["source"] + " (sustained)"},
             "slots_received_per_rank": slots,
+            "rows_received_per_rank": rows_in,   # one activation row per (token, rank) pair crosses the wire
             "ep": {"placement": args.ep_placement, "chunks": args.ep_chunks,
                    "same_config_on_one_gpu": single},
         }

@@ -1,5 +1,5 @@
 """Expert-parallel dispatch/combine logic on CPU: world_size-2 (and 4) gloo ranks, the local expert
-GEMM replaced by the oracle.  Checks the routing plan, the count exchange, both payload all-to-alls
+GEMM and per-row sum replaced by the oracle.  Checks the routing plan, the count exchange, both payload all-to-alls
 and the final ordering against the dense single-rank oracle on each rank's own tokens."""
 
 import os
@@ -22,25 +22,28 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _oracle_rows(packed, scale):
-    def rows_fn(rows_A, local_expert):
-        ids = local_expert.view(-1, 1)
-        ones = torch.ones(ids.shape, dtype=torch.float32)
+def _oracle_partial(packed, scale):
+    """CPU stand-in for the local compute: per received row the weighted fp32 sum over its experts."""
+    def partial_fn(rows_A, ids, w):
         R = rows_A.shape[0]
         out = torch.zeros(R, packed.shape[1], dtype=torch.float32)
-        for e in torch.unique(ids).tolist():
-            sel = (ids[:, 0] == e).nonzero(as_tuple=True)[0]
-            W = oracle.dequant_w4a16(packed[e], scale[e], 32, out_dtype=rows_A.dtype).float()
-            out[sel] = rows_A[sel].float() @ W.T
-        del ones
+        for j in range(ids.shape[1]):                      # ascending slot order, like the kernel path
+            for e in torch.unique(ids[:, j]).tolist():
+                if e < 0:
+                    continue
+                sel = (ids[:, j] == e).nonzero(as_tuple=True)[0]
+                W = oracle.dequant_w4a16(packed[e], scale[e], 32, out_dtype=rows_A.dtype).float()
+                out[sel] += w[sel, j:j + 1] * (rows_A[sel].float() @ W.T)
         return out
-    return rows_fn
+    return partial_fn
 
 
-def _cpu_reduce(rows, row_index, w, M, dtype):
+def _cpu_reduce(rows, row_index, M, dtype):
     out = torch.zeros(M, rows.shape[1], dtype=torch.float32)
     for k in range(row_index.shape[1]):
-        out += w[:, k:k + 1] * rows[row_index[:, k].long()]
+        idx = row_index[:, k].long()
+        ok = idx >= 0
+        out[ok] += rows[idx[ok]]
     return out.to(dtype)
 
 
@@ -54,9 +57,9 @@ def _worker(rank: int, world: int, port: int, fail_rank: int, placement: str = "
         A = synth.activations(CFG.M, CFG.K, seed=100 + rank)
         ids, w = synth.routing(CFG.M, CFG.E, CFG.top_k, seed=200 + rank, zipf_scale=CFG.zipf_scale)
         layer = ep.ExpertParallelInt4(packed[sl], scale[sl], num_global_experts=CFG.E, group_size=32,
-                                      rows_fn=_oracle_rows(packed[sl], scale[sl]), reduce_fn=_cpu_reduce,
+                                      partial_fn=_oracle_partial(packed[sl], scale[sl]), reduce_fn=_cpu_reduce,
                                       placement=placement, chunks=chunks,
-                                      max_recv_slots=0 if rank == fail_rank else None)
+                                      max_recv_rows=0 if rank == fail_rank else None)
         if fail_rank >= 0:
             # capacity check: the overloaded rank raises on the host before any payload moves
             raised = False
@@ -69,11 +72,17 @@ def _worker(rank: int, world: int, port: int, fail_rank: int, placement: str = "
         out = layer(A, ids, w)
         want = oracle.moe_w4a16(A, packed, scale, ids, w, 32)
         assert oracle.count_violations(out, want, 2e-2, 1e-2) == 0, f"rank {rank} differs from the dense oracle"
-        # every slot was sent exactly once and the receive counts add up over the ranks
-        assert sum(layer.last_send_counts) == CFG.M * CFG.top_k
-        total = torch.tensor([layer.last_recv_slots])
+        # every token went once to each rank that owns one of its experts, every slot is computed
+        # exactly once, and the receive counts add up over the ranks
+        plan = ep.plan_dispatch(ids, e_local, world, placement, chunks)
+        owners = ep.owner_and_local(ids.long(), e_local, world, placement)[0]
+        n_pairs = sum(len(set(row.tolist())) for row in owners)
+        assert sum(layer.last_send_counts) == n_pairs == plan.pair_token.numel() <= CFG.M * CFG.top_k
+        total = torch.tensor([layer.last_recv_rows, layer.count_recv_slots()])
         dist.all_reduce(total)
-        assert int(total) == world * CFG.M * CFG.top_k
+        pairs_all = torch.tensor([n_pairs])
+        dist.all_reduce(pairs_all)
+        assert int(total[0]) == int(pairs_all) and int(total[1]) == world * CFG.M * CFG.top_k
     finally:
         dist.destroy_process_group()
 
@@ -84,21 +93,28 @@ def test_all_to_all_matches_dense_oracle(world, placement, chunks):
     mp.spawn(_worker, args=(world, _free_port(), -1, placement, chunks), nprocs=world, join=True)
 
 
-def test_plan_dispatch_groups_slots_by_owner():
+def test_plan_dispatch_makes_one_pair_per_token_and_owner():
     ids = torch.tensor([[5, 0, 3], [1, 7, 2]], dtype=torch.int32)
+    # contiguous: experts 0-3 on rank 0, 4-7 on rank 1.  token 0 -> ranks {1, 0}, token 1 -> {0, 1}
     plan = ep.plan_dispatch(ids, experts_per_rank=4, world=2)
-    assert plan.send_counts.tolist() == [[4, 2]]
-    assert plan.order.tolist() == [1, 2, 3, 5, 0, 4]          # stable inside a destination
-    assert plan.local_expert.tolist() == [0, 3, 1, 2, 1, 3]
-    assert plan.token.tolist() == [0, 0, 1, 1, 0, 1]
+    assert plan.send_counts.tolist() == [[2, 2]]
+    assert plan.pair_token.tolist() == [0, 1, 0, 1]            # grouped by destination, stable in the token
+    assert plan.pair_dest.tolist() == [0, 0, 1, 1]
+    assert plan.pair_ids.tolist() == [[-1, 0, 3], [1, -1, 2], [1, -1, -1], [-1, 3, -1]]
+    assert plan.pair_of.tolist() == [[0, 2], [1, 3]]
+    assert plan.n_slots == 6
     with pytest.raises(ValueError):
         ep.plan_dispatch(torch.tensor([[8]], dtype=torch.int32), 4, 2)
     # round robin: expert g on rank g % 2 as local expert g // 2; two token chunks of one token each
     plan = ep.plan_dispatch(ids, experts_per_rank=4, world=2, placement="round_robin", chunks=2)
-    assert plan.send_counts.tolist() == [[1, 2], [1, 2]]
-    assert plan.order.tolist() == [1, 0, 2, 5, 3, 4]
-    assert plan.local_expert.tolist() == [0, 2, 1, 1, 0, 3]
+    assert plan.send_counts.tolist() == [[1, 1], [1, 1]]
+    assert plan.pair_token.tolist() == [0, 0, 1, 1]
+    assert plan.pair_dest.tolist() == [0, 1, 0, 1]
+    assert plan.pair_ids.tolist() == [[-1, 0, -1], [2, -1, 1], [-1, -1, 1], [0, 3, -1]]
     assert ep.local_expert_ids(1, 4, 2, "round_robin") == [1, 3, 5, 7]
+    # a token whose experts all live on one rank crosses the wire once
+    plan = ep.plan_dispatch(torch.tensor([[0, 1, 2]], dtype=torch.int32), 4, 2)
+    assert plan.send_counts.tolist() == [[1, 0]] and plan.pair_ids.tolist() == [[0, 1, 2]]
 
 
 def test_receive_capacity_is_checked_on_the_host():
@@ -107,4 +123,4 @@ def test_receive_capacity_is_checked_on_the_host():
     # every rank completes the count exchange, then only the overloaded one refuses; the others would
     # block in the payload exchange, so the test stops after the count phase on all ranks
     plan = ep.plan_dispatch(torch.zeros((4, 2), dtype=torch.int32), 4, 2)
-    assert plan.send_counts.tolist() == [[8, 0]]
+    assert plan.send_counts.tolist() == [[4, 0]]

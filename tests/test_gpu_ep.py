@@ -41,6 +41,30 @@ def test_rows_and_gather_reduce_equal_the_fused_op(cuda_device):
     assert_within(rows1.bfloat16(), want, 2e-2, 1e-2, what="top_k=1 rows")
 
 
+def test_rows_with_absent_slots_and_per_row_sum(cuda_device):
+    """The expert side of the exchange: a received row carries up to top_k local expert ids, -1 where
+    the token's slot went to another rank.  Absent slots are dropped by the align stage, the
+    weighted rows of the present ones are summed per received row in fp32."""
+    cfg = synth.Int4Config("t", M=200, K=512, N=256, E=6, top_k=4)
+    d = synth.make_int4(cfg, seed=21, device=cuda_device)
+    g = torch.Generator().manual_seed(3)
+    absent = (torch.rand(cfg.M, cfg.top_k, generator=g) < 0.45)
+    absent[0] = True                                   # a row with no local expert at all
+    ids = torch.where(absent.to(cuda_device), torch.full_like(d["topk_ids"], -1), d["topk_ids"])
+    rows = ops.moe_int4_w4a16_rows(d["A"], d["packed"], d["scale"], ids, d["topk_w"])
+    ops.check_status(cuda_device)
+    slot = torch.arange(cfg.M * cfg.top_k, dtype=torch.int32, device=cuda_device).view(cfg.M, cfg.top_k)
+    partial = ops.moe_gather_sum_reduce(rows, torch.where(ids >= 0, slot, torch.full_like(slot, -1)), None,
+                                        torch.float32)
+    assert partial.dtype == torch.float32 and bool((partial[0] == 0).all())
+    # oracle: the replicated expert-parallel form with a map that sends absent slots to -1
+    cpu = {k: (v.cpu() if isinstance(v, torch.Tensor) else v) for k, v in d.items()}
+    ids_cpu = torch.where(absent, torch.full_like(cpu["topk_ids"], cfg.E), cpu["topk_ids"])   # id E = "elsewhere"
+    emap = torch.cat([torch.arange(cfg.E, dtype=torch.int32), torch.tensor([-1], dtype=torch.int32)])
+    want = oracle.moe_w4a16(cpu["A"], cpu["packed"], cpu["scale"], ids_cpu, cpu["topk_w"], 32, expert_map=emap)
+    assert_within(partial.bfloat16(), want, 2e-2, 1e-2, what="partial rows")
+
+
 def _free_port() -> int:
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))

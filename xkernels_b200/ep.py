@@ -2,13 +2,16 @@
 
 One process per GPU; every rank owns ``E/W`` experts and its own batch of tokens.  A call does
 
-  1. plan: group this rank's token-slots by (token chunk, destination rank), stable inside a group,
-  2. exchange the slot-count matrix (one small all-to-all, one host read; counts are validated
-     on the host before any payload moves),
-  3. per chunk: dispatch all-to-all of the routed activation rows and their local expert ids,
-     local grouped GEMM over the received rows (one slot per row, no combine), all-to-all of the
-     fp32 result rows back to the token owners,
-  4. fixed-order weighted top-k reduce on the owner.
+  1. plan: one (token, destination rank) PAIR for every rank that owns at least one of the token's
+     top-k experts, grouped by (token chunk, destination), stable inside a group.  A token whose
+     experts share a rank crosses the wire once, not once per expert;
+  2. exchange the pair-count matrix (one small all-to-all, one host read; counts are validated
+     on the host before any payload moves);
+  3. per chunk: dispatch all-to-all of the pairs' activation rows and of their routing (local expert
+     ids padded with -1, routing weights), local grouped GEMM over the received rows and a weighted
+     fp32 sum over each pair's experts, all-to-all of ONE fp32 partial row per pair back to the
+     token owners;
+  4. fixed-order sum of each token's partial rows (ascending rank) on the owner.
 
 With ``chunks > 1`` the exchanges of chunk c+1 are in flight on NCCL's stream while the GEMM of
 chunk c runs, so transfer and tensor work overlap.
@@ -16,8 +19,9 @@ chunk c runs, so transfer and tensor work overlap.
 The reference has no all-to-all (its expert parallelism replicates tokens and lets the caller
 all-reduce partials, src/xkernels/ops/moe/interface.py:37-57); what it fixes is the result: the
 dense op on each rank's tokens with the global expert set.  fp32 rows travel back so that the
-reduce sees the same operands as the single-GPU op (a bf16 round per expert fails the op tolerance
-on some elements, see meta/docs/wiki/04-gotchas.md:452-454 in the reference).
+sums see the same operands as the single-GPU op (a bf16 round per partial fails the op tolerance
+on some elements, see meta/docs/wiki/04-gotchas.md:452-454 in the reference); only the order of
+the fp32 additions differs (experts of one rank first).
 
 Expert placement: ``"contiguous"`` (rank r owns experts ``[r*E/W, (r+1)*E/W)``, the layout of the
 reference's ``expert_map`` tests, tests/test_moe_int4_ep.py:84-93) or ``"round_robin"`` (expert g
@@ -58,28 +62,36 @@ def local_expert_ids(rank: int, experts_per_rank: int, world: int, placement: st
 
 @dataclass
 class DispatchPlan:
-    order: torch.Tensor         # [numel] slot ids grouped by (chunk, destination rank), stable inside a group
-    send_counts: torch.Tensor   # [chunks, W] int64
-    local_expert: torch.Tensor  # [numel] int32, expert index on the destination rank, in `order`
-    token: torch.Tensor         # [numel] int64, source token row of each sorted slot
+    pair_token: torch.Tensor    # [P] int64 source token row of each pair, grouped by (chunk, destination), stable
+    pair_dest: torch.Tensor     # [P] int64 destination rank of each pair
+    send_counts: torch.Tensor   # [chunks, W] int64 pairs per (chunk, destination)
+    pair_ids: torch.Tensor      # [P, top_k] int32 expert index on the destination rank, -1 where the slot goes elsewhere
+    pair_of: torch.Tensor       # [M, W] int32 position of pair (token, rank) in the sorted order, -1 if none
+    n_slots: int                # M * top_k
 
 
 def plan_dispatch(topk_ids: torch.Tensor, experts_per_rank: int, world: int, placement: str = "contiguous",
                   chunks: int = 1) -> DispatchPlan:
-    """Group the ``M*top_k`` slots by (token chunk, owner rank of their expert)."""
+    """One pair per (token, rank that owns at least one of its experts), grouped by (chunk, rank)."""
     M, top_k = topk_ids.shape
-    flat = topk_ids.reshape(-1).to(torch.int64)
-    if flat.numel() and (int(flat.min()) < 0 or int(flat.max()) >= experts_per_rank * world):
+    ids = topk_ids.to(torch.int64)
+    if ids.numel() and (int(ids.min()) < 0 or int(ids.max()) >= experts_per_rank * world):
         raise ValueError("expert id outside [0, num_global_experts)")
-    dest, local = owner_and_local(flat, experts_per_rank, world, placement)
-    slot = torch.arange(flat.numel(), device=flat.device)
+    dest, local = owner_and_local(ids, experts_per_rank, world, placement)      # [M, top_k] each
+    ranks = torch.arange(world, device=ids.device)
+    has = (dest.unsqueeze(-1) == ranks).any(dim=1)                              # [M, W]
+    tok, dst = has.nonzero(as_tuple=True)                                        # ascending token, then rank
     tokens_per_chunk = -(-M // chunks) if M else 1
-    chunk = torch.div(torch.div(slot, top_k, rounding_mode="floor"), tokens_per_chunk, rounding_mode="floor")
-    key = chunk * world + dest
+    key = torch.div(tok, tokens_per_chunk, rounding_mode="floor") * world + dst
     order = torch.argsort(key, stable=True)
+    pair_token, pair_dest = tok[order], dst[order]
     counts = torch.bincount(key, minlength=chunks * world).view(chunks, world)
-    return DispatchPlan(order=order, send_counts=counts, local_expert=local[order].to(torch.int32),
-                        token=torch.div(order, top_k, rounding_mode="floor"))
+    mine = dest[pair_token] == pair_dest.unsqueeze(1)                            # [P, top_k]
+    pair_ids = torch.where(mine, local[pair_token], torch.full_like(local[pair_token], -1)).to(torch.int32)
+    pair_of = torch.full((M, world), -1, dtype=torch.int32, device=ids.device)
+    pair_of[pair_token, pair_dest] = torch.arange(pair_token.numel(), dtype=torch.int32, device=ids.device)
+    return DispatchPlan(pair_token=pair_token, pair_dest=pair_dest, send_counts=counts, pair_ids=pair_ids,
+                        pair_of=pair_of, n_slots=M * top_k)
 
 
 def exchange_counts(send_counts: torch.Tensor, group) -> tuple[list[list[int]], list[list[int]]]:
@@ -103,15 +115,17 @@ class ExpertParallelInt4:
     """Callable layer: ``out = layer(A, topk_ids, topk_w)`` with ``topk_ids`` global expert ids.
 
     ``packed``/``scale`` are this rank's experts in local-index order (``[E/W, N, K//8]`` int32 and
-    ``[E/W, N, K//group]`` bf16; see :func:`local_expert_ids`).  ``rows_fn(A_rows, local_expert_ids)
-    -> [R, N] fp32`` computes one un-weighted expert GEMM row per received row; by default it is the
-    C-ABI call ``xkb_moe_int4_w4a16_rows`` with ``top_k = 1``.  ``reduce_fn(rows, row_index, w, M,
-    dtype)`` is the final gather + weighted sum; by default ``xkb_moe_gather_sum_reduce``.
+    ``[E/W, N, K//group]`` bf16; see :func:`local_expert_ids`).  ``partial_fn(A_rows, ids, w) ->
+    [R, N] fp32`` computes for every received row the weighted sum over its experts
+    (``ids [R, top_k]`` local expert indices, -1 = none; ``w [R, top_k]``); by default the C-ABI calls
+    ``xkb_moe_int4_w4a16_rows`` + ``xkb_moe_gather_sum_reduce``.  ``reduce_fn(rows, row_index, M,
+    dtype)`` is the final sum of each token's partial rows (``row_index [M, W]``, -1 = none); by
+    default ``xkb_moe_gather_sum_reduce``.
     """
 
     def __init__(self, packed, scale, *, num_global_experts: int, group=None, group_size: int = 32,
-                 placement: str = "contiguous", chunks: int = 1, rows_fn=None, reduce_fn=None,
-                 max_recv_slots: int | None = None):
+                 placement: str = "contiguous", chunks: int = 1, partial_fn=None, reduce_fn=None,
+                 max_recv_rows: int | None = None):
         self.group = group if group is not None else dist.group.WORLD
         self.world = dist.get_world_size(self.group)
         self.rank = dist.get_rank(self.group)
@@ -126,23 +140,29 @@ class ExpertParallelInt4:
         self.packed, self.scale, self.group_size = packed, scale, int(group_size)
         self.placement, self.chunks = placement, int(chunks)
         self.N = packed.shape[1]
-        self.rows_fn = rows_fn or self._rows_cuda
+        self.partial_fn = partial_fn or self._partial_cuda
         self.reduce_fn = reduce_fn or self._reduce_cuda
-        self.max_recv_slots = max_recv_slots
-        self.last_recv_slots = 0
+        self.max_recv_rows = max_recv_rows
+        self.last_recv_rows = 0          # pairs (activation rows) received in the last call
+        self.last_recv_slots = 0         # expert slots among them (the GEMM work of this rank)
         self.last_send_counts: list[int] = []
 
     # ---- default CUDA compute ---------------------------------------------------------
-    def _rows_cuda(self, rows_A: torch.Tensor, local_expert: torch.Tensor) -> torch.Tensor:
+    def _partial_cuda(self, rows_A: torch.Tensor, ids: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
         from . import ops
 
-        return ops.moe_int4_w4a16_rows(rows_A, self.packed, self.scale, local_expert.view(-1, 1),
-                                       group_size=self.group_size)
+        R, top_k = ids.shape
+        # one fp32 row per (received row, expert slot), already times the routing weight ...
+        rows = ops.moe_int4_w4a16_rows(rows_A, self.packed, self.scale, ids, w, group_size=self.group_size)
+        # ... summed per received row in ascending slot order (slots that went to other ranks skip)
+        slot = torch.arange(R * top_k, dtype=torch.int32, device=ids.device).view(R, top_k)
+        row_index = torch.where(ids >= 0, slot, torch.full_like(slot, -1))
+        return ops.moe_gather_sum_reduce(rows, row_index, None, torch.float32)
 
-    def _reduce_cuda(self, rows, row_index, w, M, dtype):
+    def _reduce_cuda(self, rows, row_index, M, dtype):
         from . import ops
 
-        return ops.moe_gather_sum_reduce(rows, row_index, w, dtype)
+        return ops.moe_gather_sum_reduce(rows, row_index, None, dtype)
 
     # ---- one step ----------------------------------------------------------------------
     def __call__(self, A: torch.Tensor, topk_ids: torch.Tensor, topk_w: torch.Tensor) -> torch.Tensor:
@@ -152,14 +172,18 @@ class ExpertParallelInt4:
         plan = plan_dispatch(topk_ids, self.e_local, self.world, self.placement, chunks)
         send_l, recv_l = exchange_counts(plan.send_counts, self.group)
         n_recv = sum(sum(r) for r in recv_l)
-        if self.max_recv_slots is not None and n_recv > self.max_recv_slots:
-            raise RuntimeError(f"rank {self.rank} would receive {n_recv} slots, capacity {self.max_recv_slots}")
-        self.last_recv_slots = n_recv
+        if self.max_recv_rows is not None and n_recv > self.max_recv_rows:
+            raise RuntimeError(f"rank {self.rank} would receive {n_recv} rows, capacity {self.max_recv_rows}")
+        self.last_recv_rows = n_recv
         self.last_send_counts = [sum(send_l[c][p] for c in range(chunks)) for p in range(self.world)]
 
-        numel = plan.order.numel()
-        send_A = A.index_select(0, plan.token)
-        back = torch.empty((numel, self.N), dtype=torch.float32, device=A.device)
+        P = plan.pair_token.numel()
+        send_A = A.index_select(0, plan.pair_token)
+        # routing of a pair in one int32 row: top_k local expert ids, then the top_k weights' bit patterns
+        w_pairs = torch.where(plan.pair_ids >= 0, topk_w.to(torch.float32)[plan.pair_token],
+                              torch.zeros((), dtype=torch.float32, device=A.device))
+        send_R = torch.cat([plan.pair_ids, w_pairs.view(torch.int32)], dim=1).contiguous()
+        back = torch.empty((P, self.N), dtype=torch.float32, device=A.device)
         use_async = A.is_cuda and chunks > 1
 
         # dispatch every chunk (in flight back to back on the communication stream) ...
@@ -167,31 +191,34 @@ class ExpertParallelInt4:
         for c in range(chunks):
             n_send, n_in = sum(send_l[c]), sum(recv_l[c])
             rA = torch.empty((n_in, K), dtype=A.dtype, device=A.device)
-            rE = torch.empty((n_in,), dtype=torch.int32, device=A.device)
+            rR = torch.empty((n_in, 2 * top_k), dtype=torch.int32, device=A.device)
             w1 = dist.all_to_all_single(rA, send_A[off:off + n_send], recv_l[c], send_l[c], group=self.group,
                                         async_op=use_async)
-            w2 = dist.all_to_all_single(rE, plan.local_expert[off:off + n_send], recv_l[c], send_l[c],
-                                        group=self.group, async_op=use_async)
-            recv.append((rA, rE, off, n_send))
+            w2 = dist.all_to_all_single(rR, send_R[off:off + n_send], recv_l[c], send_l[c], group=self.group,
+                                        async_op=use_async)
+            recv.append((rA, rR, off, n_send))
             works.append((w1, w2))
             off += n_send
-        # ... then per chunk: wait for its rows, expert GEMM, send the fp32 rows home
-        back_works = []
+        # ... then per chunk: wait for its rows, expert GEMM + per-row sum, send the fp32 partials home
+        back_works, n_slots_in = [], 0
         for c in range(chunks):
-            rA, rE, coff, n_send = recv[c]
+            rA, rR, coff, n_send = recv[c]
             if use_async:
                 works[c][0].wait()
                 works[c][1].wait()
-            rows = self.rows_fn(rA, rE)  # [n_in, N] fp32, un-weighted
-            wb = dist.all_to_all_single(back[coff:coff + n_send], rows, send_l[c], recv_l[c], group=self.group,
+            r_ids = rR[:, :top_k].contiguous()
+            r_w = rR[:, top_k:].contiguous().view(torch.float32)
+            partial = self.partial_fn(rA, r_ids, r_w)  # [n_in, N] fp32
+            wb = dist.all_to_all_single(back[coff:coff + n_send], partial, send_l[c], recv_l[c], group=self.group,
                                         async_op=use_async)
-            back_works.append((wb, rows))
+            back_works.append((wb, partial, r_ids))
         if use_async:
-            for wb, _rows in back_works:
+            for wb, _p, _i in back_works:
                 wb.wait()
+        self._last_ids = [i for _wb, _p, i in back_works]
+        return self.reduce_fn(back, plan.pair_of, M, A.dtype)
 
-        # slot s sits at sorted position inv[s]
-        inv = torch.empty_like(plan.order)
-        inv[plan.order] = torch.arange(numel, device=A.device)
-        row_index = inv.view(M, top_k).to(torch.int32)
-        return self.reduce_fn(back, row_index, topk_w.to(torch.float32), M, A.dtype)
+    def count_recv_slots(self) -> int:
+        """Expert slots among the rows received in the last call (one host read; diagnostics only)."""
+        self.last_recv_slots = int(sum(int((i >= 0).sum()) for i in self._last_ids))
+        return self.last_recv_slots
