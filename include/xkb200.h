@@ -30,6 +30,7 @@ extern "C" {
 /* dtype codes used by the `*_dtype` parameters */
 #define XKB_BF16 0
 #define XKB_F32 1
+#define XKB_F16 2 /* accepted for router logits only */
 
 /* kernel-path selectors for the `path` parameters */
 #define XKB_PATH_AUTO 0  /* tensor-core kernel when the shape allows, else SIMT */
@@ -101,6 +102,22 @@ int xkb_moe_align_block_size_static(const int32_t* topk_ids, int64_t numel,
                                     int32_t* sorted_ids, int32_t* expert_ids,
                                     int32_t* num_post_pad,
                                     int32_t* expert_offsets, void* stream);
+
+/* ------------------------------------------------------------------------
+ * topk_softmax: the router step immediately before the path.
+ * Replaces: src/xkernels/ops/moe/topk_softmax.py:33-95 (topk_softmax_ref) and
+ * triton/topk_softmax_kernel.py:38- (spec registry/ops/topk_softmax.spec.json).
+ *
+ * gating_output [M, E] logits (dtype XKB_BF16 / XKB_F32 / XKB_F16, row major),
+ * topk_weights [M, topk] fp32, topk_ids [M, topk] int32.  Softmax in fp32 over
+ * all E experts, then the topk largest probabilities in descending order, ties
+ * broken by ascending expert id, then (renormalize != 0) divided by their sum.
+ * E <= 1024; 1 <= topk <= E (XKB_ERR_ARG otherwise, as the reference raises
+ * ValueError).  One launch, no workspace.
+ * ---------------------------------------------------------------------- */
+int xkb_topk_softmax(const void* gating_output, int dtype, float* topk_weights,
+                     int32_t* topk_ids, int64_t M, int E, int topk,
+                     int renormalize, void* stream);
 
 /* ------------------------------------------------------------------------
  * moe_sum_reduce: out[m,:] = rsf * sum_k (w[m,k] or 1) * y[m,k,:]

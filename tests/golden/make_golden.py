@@ -29,6 +29,7 @@ from xkernels.ops.moe.mxfp4 import make_mxfp4_moe_weights  # noqa: E402
 from xkernels.ops.moe.mxfp4_reference import moe_mxfp4_ref  # noqa: E402
 from xkernels.ops.moe.reference import moe_w4a16_ref  # noqa: E402
 from xkernels.ops.moe.sum_reduce import moe_sum_reduce_ref  # noqa: E402
+from xkernels.ops.moe.topk_softmax import topk_softmax_ref  # noqa: E402
 from xkernels.ops.moe.w4a16 import (  # noqa: E402
     dequant_w4a16,
     moe_align_block_size_ep,
@@ -165,12 +166,42 @@ def gen_sum_reduce():
                                    "out": moe_sum_reduce_ref(y, w, 1.0)})
 
 
+# ---- topk_softmax (router) ---------------------------------------------------------
+def gen_topk_softmax():
+    def store(name, gating, topk, renorm):
+        w, ids = topk_softmax_ref(gating, topk, renorm)
+        save_case(name, {"gating_output": gating, "topk": topk, "renormalize": renorm, "topk_weights": w,
+                         "topk_ids": ids})
+
+    for i, pt in enumerate(sweep_points("topk_softmax")):
+        inp = generate_inputs("topk_softmax@1.0.0", pt, SEED, "cpu")
+        store(f"topk_softmax_sweep{i}", inp["gating_output"], inp["topk"], inp["renormalize"])
+    g = torch.Generator().manual_seed(SEED)
+    # heavy ties: logits on a 0.5 grid, so many experts share a probability exactly
+    coarse = (torch.randn(64, 256, generator=g) * 2).round() / 2
+    store("topk_softmax_ties_bf16", coarse.to(torch.bfloat16), 8, True)
+    store("topk_softmax_ties_fp16", coarse[:, :48].to(torch.float16), 5, False)
+    # every expert equal: the first topk ids win
+    store("topk_softmax_all_equal", torch.full((3, 40), 0.25), 6, True)
+    # non power-of-two expert count, more than 32 selected, both renormalisation modes
+    wide = torch.randn(9, 1000, generator=g)
+    store("topk_softmax_wide_renorm", wide, 40, True)
+    store("topk_softmax_wide_raw", wide, 40, False)
+    # one expert, one token
+    store("topk_softmax_single", torch.randn(1, 1, generator=g), 1, True)
+
+
 if __name__ == "__main__":
     torch.manual_seed(0)
+    if "--only-topk-softmax" in sys.argv:      # add the router fixtures without touching the others
+        gen_topk_softmax()
+        print("wrote the topk_softmax cases")
+        sys.exit(0)
     gen_align()
     gen_int4()
     gen_mxfp4()
     gen_sum_reduce()
+    gen_topk_softmax()
     (GOLDEN_DIR / "manifest.json").write_text(json.dumps(manifest, indent=1, sort_keys=True))
     total = sum(p.stat().st_size for p in GOLDEN_DIR.glob("*.npz"))
     print(f"wrote {len(list(GOLDEN_DIR.glob('*.npz')))} cases, {total / 1e6:.2f} MB")

@@ -21,7 +21,8 @@ def installed(tmp_path_factory):
 
 @needs_ref
 @pytest.mark.parametrize("card", ["moe_align_block_size.cuda@1.0.0", "moe_int4_w4a16.cuda@1.0.0",
-                                  "moe_sum_reduce.cuda@1.1.0", "moe_mxfp4.cuda@1.0.0"])
+                                  "moe_sum_reduce.cuda@1.1.0", "moe_mxfp4.cuda@1.0.0",
+                                  "topk_softmax.cuda@1.0.0"])
 def test_reference_verify_passes(card, installed, cuda_device):
     from xkernels import verify
 
@@ -34,7 +35,7 @@ def test_reference_verify_passes(card, installed, cuda_device):
 
 @needs_ref
 @pytest.mark.parametrize("op", ["moe_align_block_size@1.0.0", "moe_int4_w4a16@1.0.0", "moe_sum_reduce@1.0.0",
-                                "moe_mxfp4@1.0.0"])
+                                "moe_mxfp4@1.0.0", "topk_softmax@1.0.0"])
 def test_reference_verify_parity_agrees(op, installed, cuda_device):
     from xkernels import verify_parity
 

@@ -135,3 +135,26 @@ def test_mxfp4_matches_reference(name):
 def test_sum_reduce_matches_reference(name):
     c = load_case(name)
     assert torch.equal(oracle.sum_reduce(c["y"], c["w"], c["routed_scaling_factor"]), c["out"])
+
+
+# ---- topk_softmax (router) -----------------------------------------------------------------
+TOPK_CASES = [f"topk_softmax_sweep{i}" for i in range(6)] + [
+    "topk_softmax_ties_bf16", "topk_softmax_ties_fp16", "topk_softmax_all_equal", "topk_softmax_wide_renorm",
+    "topk_softmax_wide_raw", "topk_softmax_single"]
+
+
+@pytest.mark.parametrize("name", TOPK_CASES)
+def test_topk_softmax(name):
+    c = load_case(name)
+    w, ids = oracle.topk_softmax(c["gating_output"], c["topk"], c["renormalize"])
+    assert ids.dtype == torch.int32 and torch.equal(ids, c["topk_ids"]), "selection differs (ids are exact)"
+    assert torch.equal(w, c["topk_weights"]), "weights differ from the reference's bits"
+
+
+def test_topk_softmax_tie_rule_and_argument_check():
+    c = load_case("topk_softmax_all_equal")
+    assert c["topk_ids"].tolist() == [list(range(6))] * 3          # ties: ascending expert id
+    with pytest.raises(ValueError):
+        oracle.topk_softmax(torch.zeros(2, 4), 5)
+    with pytest.raises(ValueError):
+        oracle.topk_softmax(torch.zeros(2, 4), 0)

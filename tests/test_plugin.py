@@ -17,7 +17,7 @@ needs_ref = pytest.mark.skipif(not HAVE_REF, reason="reference package not avail
 def test_overlay_files_are_well_formed():
     reg = ROOT / "xkernels_b200" / "registry"
     cards = sorted((reg / "impls").glob("*.card.json"))
-    assert len(cards) == 5
+    assert len(cards) == 6
     for c in cards:
         doc = json.loads(c.read_text())
         assert c.name == f"{doc['implements'].split('@')[0]}.{doc['backend']}.card.json"

@@ -16,6 +16,7 @@ from .ops import (  # noqa: F401
     fused_moe_mxfp4,
     moe_align_block_size,
     moe_sum_reduce,
+    topk_softmax,
 )
 
 __all__ = [
@@ -23,5 +24,6 @@ __all__ = [
     "fused_moe_mxfp4",
     "moe_align_block_size",
     "moe_sum_reduce",
+    "topk_softmax",
 ]
 __version__ = "0.1.0"

@@ -18,6 +18,7 @@ LIB_PATH = Path(os.environ.get("XKB200_LIB") or Path(__file__).resolve().parent 
 
 XKB_BF16 = 0
 XKB_F32 = 1
+XKB_F16 = 2
 PATH_AUTO, PATH_SIMT, PATH_TC = 0, 1, 2
 
 # name -> (restype, argtypes); mirrors include/xkb200.h one to one.
@@ -35,6 +36,8 @@ SIGNATURES = {
         c_int,
         [c_void_p, c_int64, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     ),
+    "xkb_topk_softmax": (
+        c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
     "xkb_moe_sum_reduce": (
         c_int,
         [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int64, c_int, c_int64, c_float, c_void_p],

@@ -129,6 +129,37 @@ def moe_align_block_size(topk_ids, block_size, num_experts, truncate=True, works
 
 
 # ---------------------------------------------------------------------------
+_LOGIT_DT = {torch.bfloat16: _lib.XKB_BF16, torch.float32: _lib.XKB_F32, torch.float16: _lib.XKB_F16}
+
+
+def topk_softmax(gating_output, topk, renormalize=True):
+    """MoE router: fp32 softmax over all experts, top-k in descending probability (ties: ascending
+    expert id), optional renormalisation.  Returns ``(topk_weights [M, topk] fp32, topk_ids [M, topk]
+    int32)``.
+
+    Reference: ``topk_softmax_ref`` (src/xkernels/ops/moe/topk_softmax.py:33-95).
+    """
+    lib = _lib.load()
+    dev = _require_cuda("topk_softmax", gating_output)
+    if gating_output.dim() != 2:
+        raise ValueError("gating_output must be [M, E]")
+    if gating_output.dtype not in _LOGIT_DT:
+        raise TypeError(f"topk_softmax: logits must be bf16, fp16 or fp32, got {gating_output.dtype}")
+    M, E = gating_output.shape
+    if not (1 <= int(topk) <= E):
+        raise ValueError(f"topk must satisfy 1 <= topk <= E (got topk={topk}, E={E})")
+    g = gating_output.contiguous()
+    with torch.cuda.device(dev):
+        w = torch.empty((M, int(topk)), dtype=torch.float32, device=dev)
+        ids = torch.empty((M, int(topk)), dtype=torch.int32, device=dev)
+        _lib.check(
+            lib.xkb_topk_softmax(_ptr(g), _LOGIT_DT[g.dtype], _ptr(w), _ptr(ids), M, E, int(topk),
+                                 1 if renormalize else 0, _stream(dev)),
+            "xkb_topk_softmax")
+    return w, ids
+
+
+# ---------------------------------------------------------------------------
 def moe_sum_reduce(y, w=None, routed_scaling_factor=1.0):
     """``out[m] = routed_scaling_factor * sum_k w[m,k] * y[m,k,:]`` in fp32, ascending k.
 

@@ -24,9 +24,9 @@ import tempfile
 from pathlib import Path
 
 OVERLAY_SRC = Path(__file__).resolve().parent / "registry"
-KERNELS = ("moe_int4_w4a16", "moe_mxfp4", "moe_align_block_size", "moe_sum_reduce")
+KERNELS = ("moe_int4_w4a16", "moe_mxfp4", "moe_align_block_size", "moe_sum_reduce", "topk_softmax")
 CARD_IDS = ("moe_int4_w4a16.cuda@1.0.0", "moe_align_block_size.cuda@1.0.0", "moe_sum_reduce.cuda@1.1.0",
-            "moe_mxfp4.cuda@1.0.0")
+            "moe_mxfp4.cuda@1.0.0", "topk_softmax.cuda@1.0.0")
 
 _installed_root: Path | None = None
 
@@ -91,6 +91,7 @@ def install(overlay_dir: str | Path | None = None) -> Path:
     register("moe_mxfp4", Backend.CUDA)(ops.fused_moe_mxfp4)
     register("moe_align_block_size", Backend.CUDA)(_align_backend)
     register("moe_sum_reduce", Backend.CUDA)(ops.moe_sum_reduce)
+    register("topk_softmax", Backend.CUDA)(ops.topk_softmax)
 
     reference_root = Path(schemas.registry_root())
     if not (reference_root / "ops").is_dir():
