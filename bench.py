@@ -362,6 +362,17 @@ def extras(dev, peaks):
         out["mxfp4_decode"] = {"error": repr(exc)[:300]}
     torch.cuda.empty_cache()
     try:
+        M, E, top_k = 16384, 256, 8          # the router in front of the prefill configuration
+        logits = torch.randn(M, E, device=dev).to(torch.bfloat16)
+        ms = time_call(lambda: xkb.topk_softmax(logits, top_k, True), 3, 20)
+        b = M * E * 2 + M * top_k * 8
+        out["topk_softmax_16384x256_top8_bf16"] = {"us_per_call": ms * 1e3, "gbs": b / (ms * 1e-3) / 1e9,
+                                                   "frac_of_hbm_peak": b / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                                                   "note": "8.9 MB per call: fits in L2, launch-latency sized"}
+    except Exception as exc:  # noqa: BLE001
+        out["topk_softmax_16384x256_top8_bf16"] = {"error": repr(exc)[:300]}
+    torch.cuda.empty_cache()
+    try:
         M, top_k, H = 8192, 8, 7168
         y = torch.randn(M, top_k, H, device=dev, dtype=torch.bfloat16)
         w = torch.rand(M, top_k, device=dev)
