@@ -59,9 +59,9 @@ constexpr int kSubCols = kSubK / 2;                    // 32 of them per warpgro
 constexpr int kMaxIssuers = 3;
 constexpr int kCtrlWarps = 1 + kMaxIssuers;  // warp 0: the two TMA producers (lanes 0 and 1); warps 1-3: MMA issuers
                                              // (20 warps in all: register files are handed out four warps at a time)
-constexpr int kWGs = 4;            // dequantiser warpgroups (the four warps of one cover the four tensor-memory lane quarters)
-constexpr int kDequantWarps = 4 * kWGs;
-constexpr int kThreads = 32 * (kCtrlWarps + kDequantWarps);
+#ifndef XKB_NARROW_WGS
+#define XKB_NARROW_WGS 4
+#endif
 constexpr int kTmemCols = 512;     // one CTA per SM owns all of tensor memory
 constexpr int kPackedStageBytes = kTileRows * (kStageK / 2);  // 16 KiB
 constexpr int kScaleStageBytes = kTileRows * (kStageK / 32) * 2;  // 2 KiB
@@ -79,17 +79,21 @@ template <int BT, int MATS = 1> struct TcCfg {
   // that one group's waits and store drains overlap the other's arithmetic.  Wide tiles are bound by
   // the tensor pipe and have only two A slots; there all sixteen warps fill one slot together,
   // which halves the fill latency in the slot's round trip.
-  static constexpr int kGroups = (BT <= 64) ? 2 : 1;
+  // dequantiser warpgroups (the four warps of one cover the four tensor-memory lane quarters)
+  static constexpr int kWGs = (BT <= 64) ? XKB_NARROW_WGS : 4;
+  static constexpr int kDequantWarps = 4 * kWGs;
+  static constexpr int kThreads = 32 * (kCtrlWarps + kDequantWarps);
+  static constexpr int kGroups = (BT <= 64) ? kWGs / 2 : 1;
   static constexpr int kGroupWarps = kDequantWarps / kGroups;
   static constexpr int kPartsPerStage = kWGs / kGroups;      // warpgroups that share one stage
   static constexpr int kChunks = 8 / kPartsPerStage;         // 16-byte chunks (32 weights, one scale group) per thread and stage
   // Token ring.  A token stage is released by the commit of the MMAs that read it and re-filled by
   // TMA from L2 about a microsecond later; narrow tiles are small, so their ring is made deep
   // enough that the issuers never wait for tokens.
-  static constexpr int kBStages = (BT <= 16) ? 9 : (BT <= 32) ? 6 : (BT <= 64) ? 4 : 2;
+  static constexpr int kBStages = (BT <= 16) ? 9 : (BT <= 32) ? 6 : (BT <= 64) ? (kGroups == 3 ? 3 : 4) : 2;
   static constexpr int kBSubBytes = BT * kSubK * 2;
   static constexpr int kBStageBytes = kSubs * kBSubBytes;   // [4][BT x 64] bf16
-  static constexpr int kWStages = (BT <= 32) ? 6 : 4;
+  static constexpr int kWStages = (BT <= 32 || kGroups == 3) ? 6 : 4;
   static_assert(kWStages % kGroups == 0, "a weight stage must always be converted by the same group");
   // MMA issuers.  One thread sustains one tcgen05.mma per ~45 cycles (65-100 beside busy
   // dequantiser warps) whatever the shape, and that is an issue limit of the thread, not of the
@@ -224,7 +228,7 @@ __device__ __forceinline__ void mx_word(uint32_t x, uint32_t c1, uint32_t c2, ui
 }
 
 template <int BT, int MODE>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__((TcCfg<BT, mode_mats(MODE)>::kThreads), 1)
 moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_constant__ CUtensorMap tm_scale,
                const __grid_constant__ CUtensorMap tm_tokens, const TcParams p) {
   using Cfg = TcCfg<BT, mode_mats(MODE)>;
@@ -260,7 +264,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
     for (int i = 0; i < kWStages; ++i) { mbar_init(&w_full[i], 1); mbar_init(&w_empty[i], 1); }
     for (int i = 0; i < Cfg::kBBars; ++i) { mbar_init(&b_full[i], 1); mbar_init(&b_empty[i], kMatsC); }
     for (int i = 0; i < Cfg::kABars; ++i) { mbar_init(&a_full[i], Cfg::kGroupWarps); mbar_init(&a_empty[i], 1); }
-    for (int i = 0; i < Cfg::kDBuf; ++i) { mbar_init(&d_full[i], Cfg::kIssuers); mbar_init(&d_empty[i], kDequantWarps); }
+    for (int i = 0; i < Cfg::kDBuf; ++i) { mbar_init(&d_full[i], Cfg::kIssuers); mbar_init(&d_empty[i], Cfg::kDequantWarps); }
     *abort_word = 0;
     mbar_fence_init();
   }
@@ -448,7 +452,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
       }
       // the warpgroups take the 16-column groups round robin
 #pragma unroll 1
-      for (int c0 = wg * 16; c0 < BT; c0 += 16 * kWGs) {
+      for (int c0 = wg * 16; c0 < BT; c0 += 16 * Cfg::kWGs) {
         // acc = matrix 0 (INT4 / down: the only one; gate_up: gate; pair: first row tile), more = matrix 1,
         // each the sum of the accumulators that were written in this tile
         uint32_t acc[16], more[16];
@@ -525,7 +529,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
         t += gridDim.x;
         if (t >= total_tiles) return false;
         gbase += (uint32_t)v_stages;
-        vs = (int)((grp - gbase) & (uint32_t)(kGroups - 1));
+        vs = (int)((grp + kGroups - gbase % kGroups) % kGroups);
       }
       return true;
     };
@@ -539,7 +543,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
       const int nt = rt % n_row_tiles, kpart = rt / n_row_tiles;
       bool ok = true;
       bool epi_due = pend;   // the previous tile's epilogue runs after this group's first stage of this tile
-      for (int vs = (int)((grp - g0) & (uint32_t)(kGroups - 1)); vs < v_stages && ok; vs += kGroups) {
+      for (int vs = (int)((grp + kGroups - g0 % kGroups) % kGroups); vs < v_stages && ok; vs += kGroups) {
         const uint32_t g = g0 + (uint32_t)vs;
         const uint32_t wst = g % kWStages, wph = (g / kWStages) & 1u;
         const uint32_t aq = g % Cfg::kASlots, abar = g % Cfg::kABars, aph = (g / Cfg::kABars) & 1u;
@@ -709,7 +713,7 @@ int launch_bt(const CUtensorMap& tmp, const CUtensorMap& tms, const CUtensorMap&
   if (grid < 1) grid = 1;
   {
     GemmTimerScope timed(stream);
-    moe_tc_kernel<BT, MODE><<<(unsigned)grid, kThreads, Cfg::kSmemBytes, stream>>>(tmp, tms, tmt, prm);
+    moe_tc_kernel<BT, MODE><<<(unsigned)grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tmp, tms, tmt, prm);
   }
   XKB_CHECK_LAUNCH("moe_tc_kernel");
   return XKB_OK;
