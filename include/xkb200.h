@@ -176,6 +176,27 @@ int xkb_moe_gather_sum_reduce(const float* rows, const int32_t* row_index,
                               const float* w, void* out, int out_dtype,
                               int64_t M, int top_k, int64_t H, void* stream);
 
+/* xkb_ep_plan: the dispatch plan of the all-to-all mode, computed on the device
+ * without a host read (three launches).  No reference counterpart (the
+ * reference replicates tokens, ops/moe/interface.py:37-57); the host-side
+ * statement of the same plan is xkernels_b200/ep.py:plan_dispatch.
+ * A token goes once to every rank that owns one of its top-k experts.  Pairs
+ * (token, rank) are listed grouped by (token chunk, rank), ascending token
+ * inside a group.  Outputs (all int32, sized for the worst case of one pair per
+ * slot): pair_token [M*top_k], pair_dest [M*top_k], routing [M*top_k, 2*top_k]
+ * (top_k local expert ids, -1 where the slot goes elsewhere, then the top_k
+ * routing weights' fp32 bit patterns), pair_of [M, world] (position of pair
+ * (token, rank), -1 if none), counts [chunks*world] pairs per group, info[2] =
+ * {number of pairs, number of expert ids outside [0, experts_per_rank*world)}.
+ * round_robin = 0: rank r owns experts [r*experts_per_rank, ...); 1: expert g
+ * lives on rank g % world as local expert g / world.  top_k <= 32. */
+int64_t xkb_ep_plan_workspace_bytes(int64_t M, int top_k, int world, int chunks);
+int xkb_ep_plan(const int32_t* topk_ids, const float* topk_w, int64_t M, int top_k,
+                int experts_per_rank, int world, int round_robin, int chunks,
+                int32_t* pair_token, int32_t* pair_dest, int32_t* routing,
+                int32_t* pair_of, int32_t* counts, int32_t* info, void* workspace,
+                int64_t workspace_bytes, void* stream);
+
 /* ------------------------------------------------------------------------
  * fused_moe_mxfp4: gate_up GEMM -> clamped SwiGLU -> down GEMM -> combine
  * Replaces: src/xkernels/ops/moe/mxfp4_reference.py:28-112 (moe_mxfp4_ref)

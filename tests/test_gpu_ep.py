@@ -65,6 +65,36 @@ def test_rows_with_absent_slots_and_per_row_sum(cuda_device):
     assert_within(partial.bfloat16(), want, 2e-2, 1e-2, what="partial rows")
 
 
+@pytest.mark.parametrize("M,E,top_k,world,placement,chunks", [
+    (96, 16, 4, 2, "contiguous", 1), (96, 16, 4, 4, "round_robin", 3), (4096, 256, 8, 8, "round_robin", 1),
+    (1, 8, 8, 8, "contiguous", 1), (333, 48, 6, 4, "contiguous", 2), (0, 8, 2, 2, "contiguous", 1),
+])
+def test_device_plan_equals_host_plan(M, E, top_k, world, placement, chunks, cuda_device):
+    """xkb_ep_plan (three launches, no host read) against ep.plan_dispatch (torch ops on the CPU)."""
+    from xkernels_b200 import ep
+
+    ids, w = synth.routing(M, E, top_k, seed=M + world, zipf_scale=2.0) if M else (
+        torch.zeros((0, top_k), dtype=torch.int32), torch.zeros((0, top_k)))
+    want = ep.plan_dispatch(ids, E // world, world, placement, chunks)
+    pt, pd, routing, pair_of, counts, info = ops.ep_plan(ids.to(cuda_device), w.to(cuda_device), E // world, world,
+                                                          placement, chunks)
+    P = want.pair_token.numel()
+    assert info.tolist() == [P, 0]
+    assert counts.cpu().tolist() == want.send_counts.tolist()
+    assert torch.equal(pt[:P].cpu().long(), want.pair_token) and torch.equal(pd[:P].cpu().long(), want.pair_dest)
+    assert torch.equal(routing[:P, :top_k].cpu(), want.pair_ids)
+    want_w = torch.where(want.pair_ids >= 0, w.float()[want.pair_token], torch.zeros(()))
+    assert torch.equal(routing[:P, top_k:].cpu().view(torch.float32), want_w)
+    assert torch.equal(pair_of.cpu(), want.pair_of)
+    # invalid ids are counted, not acted on
+    if M:
+        bad = ids.clone()
+        bad[0, 0] = E
+        bad[-1, -1] = -3
+        info2 = ops.ep_plan(bad.to(cuda_device), w.to(cuda_device), E // world, world, placement, chunks)[5]
+        assert int(info2[1]) == 2
+
+
 def _free_port() -> int:
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))

@@ -62,52 +62,88 @@ def local_expert_ids(rank: int, experts_per_rank: int, world: int, placement: st
 
 @dataclass
 class DispatchPlan:
-    pair_token: torch.Tensor    # [P] int64 source token row of each pair, grouped by (chunk, destination), stable
+    """Pairs in (chunk, destination) order, stable in the token.  Built without a host read: the
+    arrays have one entry per SLOT (``M * top_k``), the first ``n_pairs`` of them are the pairs;
+    ``n_pairs`` is None until :meth:`trim` (or the count exchange) has read it."""
+    pair_token: torch.Tensor    # [P] int64 source token row of each pair
     pair_dest: torch.Tensor     # [P] int64 destination rank of each pair
     send_counts: torch.Tensor   # [chunks, W] int64 pairs per (chunk, destination)
     pair_ids: torch.Tensor      # [P, top_k] int32 expert index on the destination rank, -1 where the slot goes elsewhere
     pair_of: torch.Tensor       # [M, W] int32 position of pair (token, rank) in the sorted order, -1 if none
     n_slots: int                # M * top_k
+    n_bad: torch.Tensor         # 0-d int64: expert ids outside [0, E)
+    n_pairs: int | None = None
+
+    def trim(self, n_pairs: int | None = None) -> "DispatchPlan":
+        """Cut the per-slot arrays down to the pairs (``n_pairs`` from the host if already known)."""
+        P = int(self.send_counts.sum()) if n_pairs is None else int(n_pairs)
+        self.pair_token, self.pair_dest, self.pair_ids = self.pair_token[:P], self.pair_dest[:P], self.pair_ids[:P]
+        self.n_pairs = P
+        return self
 
 
 def plan_dispatch(topk_ids: torch.Tensor, experts_per_rank: int, world: int, placement: str = "contiguous",
-                  chunks: int = 1) -> DispatchPlan:
-    """One pair per (token, rank that owns at least one of its experts), grouped by (chunk, rank)."""
+                  chunks: int = 1, *, host_checks: bool = True) -> DispatchPlan:
+    """One pair per (token, rank that owns at least one of its experts), grouped by (chunk, rank).
+
+    With ``host_checks`` (the default) invalid expert ids raise here and the plan comes back
+    trimmed, at the price of two host reads; the layer passes False and does both with the one
+    read of its count exchange."""
     M, top_k = topk_ids.shape
+    dev = topk_ids.device
+    E = experts_per_rank * world
     ids = topk_ids.to(torch.int64)
-    if ids.numel() and (int(ids.min()) < 0 or int(ids.max()) >= experts_per_rank * world):
+    bad = (ids < 0) | (ids >= E)
+    n_bad = bad.sum()
+    if host_checks and ids.numel() and int(n_bad) != 0:
         raise ValueError("expert id outside [0, num_global_experts)")
-    dest, local = owner_and_local(ids, experts_per_rank, world, placement)      # [M, top_k] each
-    ranks = torch.arange(world, device=ids.device)
-    has = (dest.unsqueeze(-1) == ranks).any(dim=1)                              # [M, W]
-    tok, dst = has.nonzero(as_tuple=True)                                        # ascending token, then rank
+    dest, local = owner_and_local(ids.clamp(0, max(E - 1, 0)), experts_per_rank, world, placement)   # [M, top_k] each
+    # a slot opens a pair if no earlier slot of its token goes to the same rank
+    same = dest.unsqueeze(2) == dest.unsqueeze(1)                                   # [M, j, i]
+    earlier = torch.ones(top_k, top_k, dtype=torch.bool, device=dev).tril(-1)       # i < j
+    first = ~(same & earlier).any(dim=2)
     tokens_per_chunk = -(-M // chunks) if M else 1
-    key = torch.div(tok, tokens_per_chunk, rounding_mode="floor") * world + dst
-    order = torch.argsort(key, stable=True)
-    pair_token, pair_dest = tok[order], dst[order]
-    counts = torch.bincount(key, minlength=chunks * world).view(chunks, world)
-    mine = dest[pair_token] == pair_dest.unsqueeze(1)                            # [P, top_k]
+    chunk = torch.div(torch.arange(M, device=dev), tokens_per_chunk, rounding_mode="floor").unsqueeze(1)
+    sentinel = chunks * world                                                        # sorts behind every pair
+    key = torch.where(first, chunk * world + dest, torch.full_like(dest, sentinel)).reshape(-1)
+    slot = torch.argsort(key, stable=True)             # pairs first, grouped by key, ascending token inside a key
+    counts = torch.bincount(key, minlength=sentinel + 1)[:sentinel].view(chunks, world)
+    pair_token = torch.div(slot, top_k, rounding_mode="floor")
+    pair_dest = dest.reshape(-1)[slot]
+    is_pair = key[slot] < sentinel
+    mine = dest[pair_token] == pair_dest.unsqueeze(1)                               # [numel, top_k]
     pair_ids = torch.where(mine, local[pair_token], torch.full_like(local[pair_token], -1)).to(torch.int32)
-    pair_of = torch.full((M, world), -1, dtype=torch.int32, device=ids.device)
-    pair_of[pair_token, pair_dest] = torch.arange(pair_token.numel(), dtype=torch.int32, device=ids.device)
-    return DispatchPlan(pair_token=pair_token, pair_dest=pair_dest, send_counts=counts, pair_ids=pair_ids,
-                        pair_of=pair_of, n_slots=M * top_k)
+    # pair_of[token, rank] = position; non-pairs write to a spare element behind the table
+    flat = torch.full((M * world + 1,), -1, dtype=torch.int32, device=dev)
+    where = torch.where(is_pair, pair_token * world + pair_dest, torch.full_like(pair_token, M * world))
+    flat.scatter_(0, where, torch.arange(slot.numel(), dtype=torch.int32, device=dev))
+    pair_of = flat[:M * world].view(M, world)
+    plan = DispatchPlan(pair_token=pair_token, pair_dest=pair_dest, send_counts=counts, pair_ids=pair_ids,
+                        pair_of=pair_of, n_slots=M * top_k, n_bad=n_bad)
+    return plan.trim() if host_checks else plan
 
 
-def exchange_counts(send_counts: torch.Tensor, group) -> tuple[list[list[int]], list[list[int]]]:
-    """All-to-all of the [chunks, W] slot-count matrix.  Returns (send, recv) as nested Python lists
-    indexed [chunk][peer] and validates them."""
+def exchange_counts(send_counts: torch.Tensor, group, extra: torch.Tensor | None = None):
+    """All-to-all of the [chunks, W] pair-count matrix.  Returns (send, recv) as nested Python lists
+    indexed [chunk][peer] and validates them.  ``extra`` (a 0-d device tensor) rides along on the
+    one host read and is returned as a third value."""
     world = dist.get_world_size(group)
     chunks = send_counts.shape[0]
     send_t = send_counts.t().contiguous()            # [W, chunks]: row p goes to peer p
     recv_t = torch.empty_like(send_t)
     dist.all_to_all_single(recv_t, send_t, group=group)
-    both = torch.stack([send_t, recv_t]).cpu()
-    send_l = both[0].t().tolist()
-    recv_l = both[1].t().tolist()
+    parts = [send_t.reshape(-1), recv_t.reshape(-1)]
+    if extra is not None:
+        parts.append(extra.reshape(1).to(send_t.dtype))
+    flat_host = torch.cat(parts).cpu().tolist()
+    n = world * chunks
+    send_l = [[flat_host[p * chunks + c] for p in range(world)] for c in range(chunks)]
+    recv_l = [[flat_host[n + p * chunks + c] for p in range(world)] for c in range(chunks)]
     flat = [v for row in send_l + recv_l for v in row]
-    if len(send_l) != chunks or any(len(r) != world for r in send_l + recv_l) or (flat and min(flat) < 0):
+    if flat and min(flat) < 0:
         raise RuntimeError(f"expert-parallel count exchange returned invalid counts: {send_l} / {recv_l}")
+    if extra is not None:
+        return send_l, recv_l, flat_host[2 * n]
     return send_l, recv_l
 
 
@@ -169,20 +205,35 @@ class ExpertParallelInt4:
         M, K = A.shape
         top_k = topk_ids.shape[1]
         chunks = max(1, min(self.chunks, M))
-        plan = plan_dispatch(topk_ids, self.e_local, self.world, self.placement, chunks)
-        send_l, recv_l = exchange_counts(plan.send_counts, self.group)
+        if A.is_cuda:
+            # the plan on the device (three launches, no host read); the one read below also brings
+            # the pair count and the invalid-id count
+            from . import ops
+
+            pair_token, _dest, routing, pair_of, counts, info = ops.ep_plan(
+                topk_ids, topk_w, self.e_local, self.world, self.placement, chunks)
+            send_l, recv_l, n_bad = exchange_counts(counts, self.group, extra=info[1])
+            P = sum(sum(r) for r in send_l)
+            pair_token, send_R = pair_token[:P], routing[:P]
+        else:
+            plan = plan_dispatch(topk_ids, self.e_local, self.world, self.placement, chunks, host_checks=False)
+            send_l, recv_l, n_bad = exchange_counts(plan.send_counts, self.group, extra=plan.n_bad)
+            P = sum(sum(r) for r in send_l)
+            plan.trim(P)
+            pair_token, pair_of = plan.pair_token, plan.pair_of
+            # routing of a pair in one int32 row: top_k local expert ids, then the top_k weights' bit patterns
+            w_pairs = torch.where(plan.pair_ids >= 0, topk_w.to(torch.float32)[pair_token],
+                                  torch.zeros((), dtype=torch.float32, device=A.device))
+            send_R = torch.cat([plan.pair_ids, w_pairs.view(torch.int32)], dim=1).contiguous()
+        if n_bad:
+            raise ValueError("expert id outside [0, num_global_experts)")
         n_recv = sum(sum(r) for r in recv_l)
         if self.max_recv_rows is not None and n_recv > self.max_recv_rows:
             raise RuntimeError(f"rank {self.rank} would receive {n_recv} rows, capacity {self.max_recv_rows}")
         self.last_recv_rows = n_recv
         self.last_send_counts = [sum(send_l[c][p] for c in range(chunks)) for p in range(self.world)]
 
-        P = plan.pair_token.numel()
-        send_A = A.index_select(0, plan.pair_token)
-        # routing of a pair in one int32 row: top_k local expert ids, then the top_k weights' bit patterns
-        w_pairs = torch.where(plan.pair_ids >= 0, topk_w.to(torch.float32)[plan.pair_token],
-                              torch.zeros((), dtype=torch.float32, device=A.device))
-        send_R = torch.cat([plan.pair_ids, w_pairs.view(torch.int32)], dim=1).contiguous()
+        send_A = A.index_select(0, pair_token)
         back = torch.empty((P, self.N), dtype=torch.float32, device=A.device)
         use_async = A.is_cuda and chunks > 1
 
@@ -216,7 +267,7 @@ class ExpertParallelInt4:
             for wb, _p, _i in back_works:
                 wb.wait()
         self._last_ids = [i for _wb, _p, i in back_works]
-        return self.reduce_fn(back, plan.pair_of, M, A.dtype)
+        return self.reduce_fn(back, pair_of, M, A.dtype)
 
     def count_recv_slots(self) -> int:
         """Expert slots among the rows received in the last call (one host read; diagnostics only)."""

@@ -355,3 +355,34 @@ def moe_gather_sum_reduce(rows, row_index, w, out_dtype=torch.bfloat16):
                                           H, _stream(dev)),
             "xkb_moe_gather_sum_reduce")
     return out
+
+
+def ep_plan(topk_ids, topk_w, experts_per_rank, world, placement="contiguous", chunks=1):
+    """Device-side dispatch plan of the all-to-all expert-parallel mode (``xkb_ep_plan``): no host
+    read.  Returns ``(pair_token, pair_dest, routing, pair_of, counts, info)`` with the per-pair
+    arrays sized ``M * top_k`` (the first ``info[0]`` entries are the pairs); see
+    ``xkernels_b200/ep.py:plan_dispatch`` for the meaning of each."""
+    lib = _lib.load()
+    dev = _require_cuda("ep_plan", topk_ids, topk_w)
+    if placement not in ("contiguous", "round_robin"):
+        raise ValueError(f"unknown expert placement {placement!r}")
+    ids = topk_ids.to(torch.int32).contiguous()
+    w = topk_w.to(torch.float32).contiguous()
+    M, top_k = ids.shape
+    numel = M * top_k
+    with torch.cuda.device(dev):
+        pair_token = torch.empty((numel,), dtype=torch.int32, device=dev)
+        pair_dest = torch.empty((numel,), dtype=torch.int32, device=dev)
+        routing = torch.empty((numel, 2 * top_k), dtype=torch.int32, device=dev)
+        pair_of = torch.empty((M, world), dtype=torch.int32, device=dev)
+        counts = torch.empty((chunks, world), dtype=torch.int32, device=dev)
+        info = torch.empty((2,), dtype=torch.int32, device=dev)
+        ws_bytes = int(lib.xkb_ep_plan_workspace_bytes(M, top_k, world, chunks))
+        ws = get_workspace(dev, ws_bytes, tag=1)     # not the fused ops' buffer: that one starts with their status words
+        _lib.check(
+            lib.xkb_ep_plan(_ptr(ids), _ptr(w), M, top_k, int(experts_per_rank), int(world),
+                            1 if placement == "round_robin" else 0, int(chunks), _ptr(pair_token), _ptr(pair_dest),
+                            _ptr(routing), _ptr(pair_of), _ptr(counts), _ptr(info), _ptr(ws), ws.numel(),
+                            _stream(dev)),
+            "xkb_ep_plan")
+    return pair_token, pair_dest, routing, pair_of, counts, info
