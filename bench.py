@@ -362,6 +362,28 @@ def extras(dev, peaks):
         out["mxfp4_decode"] = {"error": repr(exc)[:300]}
     torch.cuda.empty_cache()
     try:
+        # the decode call captured in a CUDA graph (the call is stream-ordered end to end): launch
+        # overhead of its four kernels collapses into one graph launch
+        cfg = synth.CONFIGS["int4_decode"]
+        d = synth.make_int4(cfg, seed=1729, device=dev)
+        fn = lambda: xkb.fused_moe_int4_w4a16(d["A"], d["packed"], d["scale"], d["topk_ids"], d["topk_w"],  # noqa: E731
+                                              group_size=cfg.group_size)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                fn()
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            fn()
+        ms = time_call(graph.replay, 3, 50)
+        out["int4_decode_cuda_graph"] = {"us_per_call": ms * 1e3, "tokens_per_s": cfg.M / (ms * 1e-3)}
+        del d, graph
+    except Exception as exc:  # noqa: BLE001
+        out["int4_decode_cuda_graph"] = {"error": repr(exc)[:300]}
+    torch.cuda.empty_cache()
+    try:
         M, E, top_k = 16384, 256, 8          # the router in front of the prefill configuration
         logits = torch.randn(M, E, device=dev).to(torch.bfloat16)
         ms = time_call(lambda: xkb.topk_softmax(logits, top_k, True), 3, 20)
