@@ -425,7 +425,8 @@ def run_multi_gpu(args, world: int, rank: int, local_rank: int):
     ids, w = synth.routing(cfg.M, cfg.E, cfg.top_k, seed=1732 + 100 * rank, device=dev, zipf_scale=cfg.zipf_scale)
     packed, scale = synth.int4_weights(e_local, cfg.N, cfg.K, cfg.group_size, seed=1730 + 7 * rank, device=dev)
     layer = ep.ExpertParallelInt4(packed, scale, num_global_experts=cfg.E, group=dist.group.WORLD,
-                                  group_size=cfg.group_size, placement=args.ep_placement, chunks=args.ep_chunks)
+                                  group_size=cfg.group_size, placement=args.ep_placement, chunks=args.ep_chunks,
+                                  sm_margin=args.ep_sm_margin)
 
     # reference point for scaling: the SAME configuration on one GPU (all 256 experts local, 4096
     # tokens, no exchange), timed on rank 0 before the group run
@@ -510,7 +511,7 @@ def run_multi_gpu(args, world: int, rank: int, local_rank: int):
                          "peak_source": peaks["source"] + " (sustained)"},
             "slots_received_per_rank": slots,
             "rows_received_per_rank": rows_in,   # one activation row per (token, rank) pair crosses the wire
-            "ep": {"placement": args.ep_placement, "chunks": args.ep_chunks,
+            "ep": {"placement": args.ep_placement, "chunks": args.ep_chunks, "sm_margin": args.ep_sm_margin,
                    "same_config_on_one_gpu": single},
         }
         print(json.dumps(line), flush=True)
@@ -559,6 +560,8 @@ def main():
     ap.add_argument("--ep-placement", default="round_robin", choices=["contiguous", "round_robin"],
                     help="expert -> rank assignment of the expert-parallel run")
     ap.add_argument("--ep-chunks", type=int, default=1, help="token chunks pipelined through the exchanges")
+    ap.add_argument("--ep-sm-margin", type=int, default=16,
+                    help="SMs the GEMM kernels leave to the exchange kernels when chunks > 1")
     ap.add_argument("--case", default=None, choices=sorted(PROFILE_CASES),
                     help="run one small profiling case instead of the benchmark")
     args = ap.parse_args()

@@ -176,6 +176,13 @@ int xkb_moe_gather_sum_reduce(const float* rows, const int32_t* row_index,
                               const float* w, void* out, int out_dtype,
                               int64_t M, int top_k, int64_t H, void* stream);
 
+/* xkb_set_sm_margin: the grouped-GEMM kernels are persistent, one CTA per SM.
+ * A margin of n keeps n SMs free (process-wide, until changed), so that
+ * kernels launched on other streams -- NCCL's exchanges in the chunked
+ * expert-parallel pipeline -- can run beside them instead of behind them.
+ * No reference counterpart.  0 <= n <= 128; default 0. */
+int xkb_set_sm_margin(int sms);
+
 /* xkb_ep_plan: the dispatch plan of the all-to-all mode, computed on the device
  * without a host read (three launches).  No reference counterpart (the
  * reference replicates tokens, ops/moe/interface.py:37-57); the host-side

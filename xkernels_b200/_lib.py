@@ -53,6 +53,7 @@ SIGNATURES = {
         [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
          c_int, c_int, c_int, c_int, c_int, c_void_p, c_int64, c_void_p],
     ),
+    "xkb_set_sm_margin": (c_int, [c_int]),
     "xkb_ep_plan_workspace_bytes": (c_int64, [c_int64, c_int, c_int, c_int]),
     "xkb_ep_plan": (
         c_int,
@@ -107,6 +108,11 @@ def check(status: int, what: str) -> None:
 
 def launch_count() -> int:
     return int(load().xkb_launch_count())
+
+
+def set_sm_margin(sms: int) -> None:
+    """Keep ``sms`` SMs free of the persistent grouped-GEMM kernels (for kernels on other streams)."""
+    check(load().xkb_set_sm_margin(int(sms)), "xkb_set_sm_margin")
 
 
 def gemm_timer_enable(max_calls: int) -> None:

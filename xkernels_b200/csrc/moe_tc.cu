@@ -41,11 +41,13 @@
 // Every mbarrier wait is bounded (tc_common.cuh); on a time-out the CTA records
 // a status code, all roles leave their loops, and tensor memory is released.
 
+#include <atomic>
 #include <cstdlib>
 #include "moe_kernels.h"
 #include "tc_common.cuh"
 
 namespace xkb {
+std::atomic<int> g_sm_margin{0};
 namespace {
 
 using namespace tc;
@@ -707,8 +709,10 @@ int launch_bt(const CUtensorMap& tmp, const CUtensorMap& tms, const CUtensorMap&
   int dev = 0, sms = 148;
   XKB_CHECK_CUDA(cudaGetDevice(&dev));
   XKB_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  const int per_sm = 1;  // the CTA owns the SM: all 512 tensor-memory columns, 20 warps
-  int64_t grid = (int64_t)sms * per_sm;
+  // one persistent CTA per SM (it owns all 512 tensor-memory columns), minus the SMs the caller
+  // asked to keep free for kernels that should run beside this one (xkb_set_sm_margin)
+  int64_t grid = (int64_t)sms - g_sm_margin.load(std::memory_order_relaxed);
+  if (grid < 8) grid = 8;
   if (grid > max_tiles) grid = max_tiles;
   if (grid < 1) grid = 1;
   {
@@ -902,3 +906,9 @@ extern "C" int xkb_debug_trace(long long* host, int* counts_host) {
   return 0;
 }
 #endif
+
+extern "C" int xkb_set_sm_margin(int sms) {
+  if (sms < 0 || sms > 128) return xkb::fail(XKB_ERR_ARG, "xkb_set_sm_margin: %d outside [0,128]", sms);
+  xkb::g_sm_margin.store(sms, std::memory_order_relaxed);
+  return XKB_OK;
+}

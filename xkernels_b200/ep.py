@@ -161,7 +161,7 @@ class ExpertParallelInt4:
 
     def __init__(self, packed, scale, *, num_global_experts: int, group=None, group_size: int = 32,
                  placement: str = "contiguous", chunks: int = 1, partial_fn=None, reduce_fn=None,
-                 max_recv_rows: int | None = None):
+                 max_recv_rows: int | None = None, sm_margin: int = 16):
         self.group = group if group is not None else dist.group.WORLD
         self.world = dist.get_world_size(self.group)
         self.rank = dist.get_rank(self.group)
@@ -179,6 +179,9 @@ class ExpertParallelInt4:
         self.partial_fn = partial_fn or self._partial_cuda
         self.reduce_fn = reduce_fn or self._reduce_cuda
         self.max_recv_rows = max_recv_rows
+        # chunked pipeline on GPUs: SMs the persistent GEMM kernels leave to NCCL's exchange kernels,
+        # which would otherwise queue behind them instead of running beside them
+        self.sm_margin = int(sm_margin)
         self.last_recv_rows = 0          # pairs (activation rows) received in the last call
         self.last_recv_slots = 0         # expert slots among them (the GEMM work of this rank)
         self.last_send_counts: list[int] = []
@@ -251,18 +254,27 @@ class ExpertParallelInt4:
             works.append((w1, w2))
             off += n_send
         # ... then per chunk: wait for its rows, expert GEMM + per-row sum, send the fp32 partials home
-        back_works, n_slots_in = [], 0
-        for c in range(chunks):
-            rA, rR, coff, n_send = recv[c]
-            if use_async:
-                works[c][0].wait()
-                works[c][1].wait()
-            r_ids = rR[:, :top_k].contiguous()
-            r_w = rR[:, top_k:].contiguous().view(torch.float32)
-            partial = self.partial_fn(rA, r_ids, r_w)  # [n_in, N] fp32
-            wb = dist.all_to_all_single(back[coff:coff + n_send], partial, send_l[c], recv_l[c], group=self.group,
-                                        async_op=use_async)
-            back_works.append((wb, partial, r_ids))
+        back_works = []
+        margin = use_async and self.partial_fn == self._partial_cuda and self.sm_margin > 0
+        if margin:
+            from . import _lib
+
+            _lib.set_sm_margin(self.sm_margin)
+        try:
+            for c in range(chunks):
+                rA, rR, coff, n_send = recv[c]
+                if use_async:
+                    works[c][0].wait()
+                    works[c][1].wait()
+                r_ids = rR[:, :top_k].contiguous()
+                r_w = rR[:, top_k:].contiguous().view(torch.float32)
+                partial = self.partial_fn(rA, r_ids, r_w)  # [n_in, N] fp32
+                wb = dist.all_to_all_single(back[coff:coff + n_send], partial, send_l[c], recv_l[c], group=self.group,
+                                            async_op=use_async)
+                back_works.append((wb, partial, r_ids))
+        finally:
+            if margin:
+                _lib.set_sm_margin(0)
         if use_async:
             for wb, _p, _i in back_works:
                 wb.wait()
