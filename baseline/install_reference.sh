@@ -4,7 +4,7 @@
 # The wheel omits the reference's registry/ data directory (JSON specs, cards, sweeps, schemas), so
 # it is copied next to the package.  Usage:  baseline/install_reference.sh /path/to/xkernels
 set -euo pipefail
-REF="${1:-/root/reference}"
+REF="${1:?usage: baseline/install_reference.sh /path/to/xkernels}"
 HERE="$(cd "$(dirname "$0")" && pwd)"
 TMP="$(mktemp -d)"
 cp -r "$REF" "$TMP/src"            # the build writes into the source tree; the original may be read-only
