@@ -61,6 +61,22 @@ constexpr int kSubCols = kSubK / 2;                    // 32 of them per warpgro
 constexpr int kMaxIssuers = 3;
 constexpr int kCtrlWarps = 1 + kMaxIssuers;  // warp 0: the two TMA producers (lanes 0 and 1); warps 1-3: MMA issuers
                                              // (20 warps in all: register files are handed out four warps at a time)
+#ifndef XKB_NARROW_ISSUERS
+#define XKB_NARROW_ISSUERS 2
+#endif
+#define XKB_NARROW_ISSUERS_SEL(bt) (((bt) <= 32) ? XKB_NARROW_ISSUERS : 2)
+#ifndef XKB_W_STAGES_NARROW
+#define XKB_W_STAGES_NARROW 6
+#endif
+#ifndef XKB_B_STAGES_16
+#define XKB_B_STAGES_16 9
+#endif
+#ifndef XKB_PROD_SLEEP
+#define XKB_PROD_SLEEP 400
+#endif
+#ifndef XKB_ISS_SLEEP
+#define XKB_ISS_SLEEP 32
+#endif
 #ifndef XKB_NARROW_WGS
 #define XKB_NARROW_WGS 4
 #endif
@@ -92,10 +108,10 @@ template <int BT, int MATS = 1> struct TcCfg {
   // Token ring.  A token stage is released by the commit of the MMAs that read it and re-filled by
   // TMA from L2 about a microsecond later; narrow tiles are small, so their ring is made deep
   // enough that the issuers never wait for tokens.
-  static constexpr int kBStages = (BT <= 16) ? 9 : (BT <= 32) ? 6 : (BT <= 64) ? (kGroups == 3 ? 3 : 4) : 2;
+  static constexpr int kBStages = (BT <= 16) ? XKB_B_STAGES_16 : (BT <= 32) ? 6 : (BT <= 64) ? (kGroups == 3 ? 3 : 4) : 2;
   static constexpr int kBSubBytes = BT * kSubK * 2;
   static constexpr int kBStageBytes = kSubs * kBSubBytes;   // [4][BT x 64] bf16
-  static constexpr int kWStages = (BT <= 32 || kGroups == 3) ? 6 : 4;
+  static constexpr int kWStages = (BT <= 16) ? XKB_W_STAGES_NARROW : (BT <= 32 || kGroups == 3) ? 6 : 4;
   static_assert(kWStages % kGroups == 0, "a weight stage must always be converted by the same group");
   // MMA issuers.  One thread sustains one tcgen05.mma per ~45 cycles (65-100 beside busy
   // dequantiser warps) whatever the shape, and that is an issue limit of the thread, not of the
@@ -106,7 +122,7 @@ template <int BT, int MATS = 1> struct TcCfg {
   // g % kIssuers, which puts it into its own accumulator (per matrix); the epilogue adds them.
   // (Three issuers, because with the producer warp and the sixteen dequantiser warps that makes 20
   // warps; register files are handed out four warps at a time.)
-  static constexpr int kIssuers = (BT <= 32) ? 3 : 2;
+  static constexpr int kIssuers = XKB_NARROW_ISSUERS_SEL(BT);
   static_assert(kIssuers <= kMaxIssuers, "not enough issuer warps");
   // kIssuers == MATS: the stage's parity is its matrix and its issuer at once (a tile has a multiple
   // of MATS stages), so one accumulator per matrix is enough.
@@ -270,9 +286,13 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
     *abort_word = 0;
     mbar_fence_init();
   }
+  // the token producer gets a warp of its own when the issuers leave one free (two threads of one warp
+  // that both poll with back-off slow each other down); otherwise it shares the weight producer's
+  constexpr int kTokWarp = (Cfg::kIssuers < kMaxIssuers) ? kCtrlWarps - 1 : 0;
+  constexpr int kTokLane = (Cfg::kIssuers < kMaxIssuers) ? 0 : 1;
   if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
   if (warp == 0 && lane == 0) { prefetch_tensormap(&tm_packed); if (mode_is_int4(MODE)) prefetch_tensormap(&tm_scale); }
-  if (warp == 0 && lane == 1) prefetch_tensormap(&tm_tokens);
+  if (warp == kTokWarp && lane == kTokLane) prefetch_tensormap(&tm_tokens);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -308,7 +328,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
           const int ks = ks0 + vs / kMats;
           const int row0 = tile_row(b, nt, vs);
           TRACE(0, 1);
-          if (!mbar_wait(&w_empty[st], ph ^ 1, guard, 1, 400)) break;
+          if (!mbar_wait(&w_empty[st], ph ^ 1, guard, 1, XKB_PROD_SLEEP)) break;
           TRACE(0, 2);
           if (mode_is_int4(MODE)) {
             mbar_expect_tx(&w_full[st], kPackedStageBytes + kScaleStageBytes);
@@ -322,7 +342,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
         }
       }
     }
-  } else if (warp == 0 && lane == 1) {
+  } else if (warp == kTokWarp && lane == kTokLane) {
     // ---------------- token producer (diverged from lane 0; both make progress independently) ----------------
     {
       uint32_t st = 0, tb = 0;   // token stage slot and running number of the token stage
@@ -335,7 +355,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
           // the slot's previous user was token stage tb - kBStages: wait for its readers' commits
           if (tb >= (uint32_t)Cfg::kBStages) {
             const uint32_t tp = tb - Cfg::kBStages;
-            if (!mbar_wait(&b_empty[tp % Cfg::kBBars], (tp / Cfg::kBBars) & 1u, guard, 2, 400)) break;
+            if (!mbar_wait(&b_empty[tp % Cfg::kBBars], (tp / Cfg::kBBars) & 1u, guard, 2, XKB_PROD_SLEEP)) break;
           }
           const uint32_t bar = tb % Cfg::kBBars;
           TRACE(1, 2);
@@ -372,7 +392,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
           const uint32_t tb = g / kMats;                    // token stage read by stage g
           const uint32_t bst = tb % Cfg::kBStages, bbar = tb % Cfg::kBBars, bph = (tb / Cfg::kBBars) & 1u;
           TRACE_ISS(1);
-          ok = mbar_wait(&a_full[abar], aph, guard, 3, 32);
+          ok = mbar_wait(&a_full[abar], aph, guard, 3, XKB_ISS_SLEEP);
           TRACE_ISS(2);
           // every dequantiser warp of the stage's group has arrived, so all of them are done with the
           // weight stage in shared memory: hand it back to the producer on their behalf
