@@ -7,17 +7,16 @@
 // stream.  One persistent CTA per SM (it owns all 512 tensor-memory columns),
 // twenty warps, everything handed over in whole 256-K stages:
 //
-//   warp 0   lane 0: TMA producer, weights: packed tile [128 rows x 128 B] (128B
-//            swizzle, so that one row per thread reads conflict-free) + bf16
-//            scale tile [128 x 8] per stage (MXFP4 scales are read from global
-//            memory by the dequantisers).
-//            lane 1: TMA producer, tokens: four [BT x 64] bf16 sub-tiles per stage
-//            (128B swizzle = the UMMA K-major canonical layout) from the gathered
-//            activation buffer.
-//   warps 1-3 MMA issuers (lane 0 each; warp 1 also allocates and frees tensor
+//   warp 0   TMA producer, weights: packed tile [128 rows x 128 B] (128B swizzle, so that one
+//            row per thread reads conflict-free) + bf16 scale tile [128 x 8] per stage (MXFP4
+//            scales are read from global memory by the dequantisers).
+//   warps 1-2 MMA issuers (lane 0 each; warp 1 also allocates and frees tensor
 //            memory): tcgen05.mma kind::f16, A from tensor memory, B from shared
-//            memory, fp32 accumulators in tensor memory.  The sixteen K=16 steps of
-//            a stage are split over the issuers, each into its own accumulator.
+//            memory, fp32 accumulators in tensor memory.  They take whole stages in
+//            turn, each into its own accumulator.
+//   warp 3   TMA producer, tokens: four [BT x 64] bf16 sub-tiles per stage (128B swizzle =
+//            the UMMA K-major canonical layout) from the gathered activation buffer.  (In a
+//            warp of its own: two polling threads in one warp slow each other down.)
 //   warps 4-19 dequantisers: thread = weight row; nibbles -> exact bf16 integers
 //            by the 0x4300|nib trick, minus 136, times the group scale in one
 //            bf16 multiply (= the reference's single rounding,
@@ -59,7 +58,8 @@ constexpr int kSubs = kStageK / kSubK;  // 4
 constexpr int kSlotCols = kStageK / 2;                 // 128 columns of bf16 pairs per A slot
 constexpr int kSubCols = kSubK / 2;                    // 32 of them per warpgroup
 constexpr int kMaxIssuers = 3;
-constexpr int kCtrlWarps = 1 + kMaxIssuers;  // warp 0: the two TMA producers (lanes 0 and 1); warps 1-3: MMA issuers
+constexpr int kCtrlWarps = 1 + kMaxIssuers;  // warp 0: weight producer; then the issuers; the last control warp hosts the
+                                             // token producer when the issuers leave it free
                                              // (20 warps in all: register files are handed out four warps at a time)
 #ifndef XKB_NARROW_ISSUERS
 #define XKB_NARROW_ISSUERS 2
@@ -120,8 +120,8 @@ template <int BT, int MATS = 1> struct TcCfg {
   // costs the issuing thread several hundred cycles of waits, fences and commits, so the issuers
   // take whole stages in turn: stage g (numbered across the tiles of the CTA) belongs to issuer
   // g % kIssuers, which puts it into its own accumulator (per matrix); the epilogue adds them.
-  // (Three issuers, because with the producer warp and the sixteen dequantiser warps that makes 20
-  // warps; register files are handed out four warps at a time.)
+  // (Two issuers: the fourth control warp then belongs to the token producer, which measured
+  // better than a third issuer with both producers in one warp, 222 against 238 us at decode.)
   static constexpr int kIssuers = XKB_NARROW_ISSUERS_SEL(BT);
   static_assert(kIssuers <= kMaxIssuers, "not enough issuer warps");
   // kIssuers == MATS: the stage's parity is its matrix and its issuer at once (a tile has a multiple
