@@ -58,13 +58,9 @@ constexpr int kSubs = kStageK / kSubK;  // 4
 constexpr int kSlotCols = kStageK / 2;                 // 128 columns of bf16 pairs per A slot
 constexpr int kSubCols = kSubK / 2;                    // 32 of them per warpgroup
 constexpr int kMaxIssuers = 3;
-constexpr int kCtrlWarps = 1 + kMaxIssuers;  // warp 0: weight producer; then the issuers; the last control warp hosts the
+constexpr int kMaxCtrlWarps = 2 + kMaxIssuers;  // warp 0: weight producer; then the issuers; the last control warp hosts the
                                              // token producer when the issuers leave it free
                                              // (20 warps in all: register files are handed out four warps at a time)
-#ifndef XKB_NARROW_ISSUERS
-#define XKB_NARROW_ISSUERS 2
-#endif
-#define XKB_NARROW_ISSUERS_SEL(bt) (((bt) <= 32) ? XKB_NARROW_ISSUERS : 2)
 #ifndef XKB_W_STAGES_NARROW
 #define XKB_W_STAGES_NARROW 6
 #endif
@@ -92,7 +88,7 @@ constexpr int kScaleStageBytes = kTileRows * (kStageK / 32) * 2;  // 2 KiB
 constexpr int gcd_c(int a, int b) { return b == 0 ? a : gcd_c(b, a % b); }
 constexpr int lcm_c(int a, int b) { return a / gcd_c(a, b) * b; }
 
-template <int BT, int MATS = 1> struct TcCfg {
+template <int BT, int MATS = 1, bool INT4 = true> struct TcCfg {
   // Dequantiser groups that take alternate stages.  Narrow tiles: two groups of eight warps, so
   // that one group's waits and store drains overlap the other's arithmetic.  Wide tiles are bound by
   // the tensor pipe and have only two A slots; there all sixteen warps fill one slot together,
@@ -100,6 +96,10 @@ template <int BT, int MATS = 1> struct TcCfg {
   // dequantiser warpgroups (the four warps of one cover the four tensor-memory lane quarters)
   static constexpr int kWGs = (BT <= 64) ? XKB_NARROW_WGS : 4;
   static constexpr int kDequantWarps = 4 * kWGs;
+  // Control warps: weight producer, the issuers, token producer.  Narrow INT4 tiles run three
+  // issuers (five control warps; 21 warps get 80 registers each, enough for the INT4 dequantiser);
+  // the others two issuers (four control warps, 96 registers, which the E2M1 dequantiser needs).
+  static constexpr int kCtrlWarps = (INT4 && BT <= 32) ? 5 : 4;
   static constexpr int kThreads = 32 * (kCtrlWarps + kDequantWarps);
   static constexpr int kGroups = (BT <= 64) ? kWGs / 2 : 1;
   static constexpr int kGroupWarps = kDequantWarps / kGroups;
@@ -120,9 +120,9 @@ template <int BT, int MATS = 1> struct TcCfg {
   // costs the issuing thread several hundred cycles of waits, fences and commits, so the issuers
   // take whole stages in turn: stage g (numbered across the tiles of the CTA) belongs to issuer
   // g % kIssuers, which puts it into its own accumulator (per matrix); the epilogue adds them.
-  // (Two issuers: the fourth control warp then belongs to the token producer, which measured
-  // better than a third issuer with both producers in one warp, 222 against 238 us at decode.)
-  static constexpr int kIssuers = XKB_NARROW_ISSUERS_SEL(BT);
+  // (Measured at decode: two issuers + token producer in its own warp 222 us, three issuers with
+  // both producers in one warp 238 us, three issuers + five control warps 210 us.)
+  static constexpr int kIssuers = kCtrlWarps - 2;
   static_assert(kIssuers <= kMaxIssuers, "not enough issuer warps");
   // kIssuers == MATS: the stage's parity is its matrix and its issuer at once (a tile has a multiple
   // of MATS stages), so one accumulator per matrix is enough.
@@ -246,10 +246,10 @@ __device__ __forceinline__ void mx_word(uint32_t x, uint32_t c1, uint32_t c2, ui
 }
 
 template <int BT, int MODE>
-__global__ void __launch_bounds__((TcCfg<BT, mode_mats(MODE)>::kThreads), 1)
+__global__ void __launch_bounds__((TcCfg<BT, mode_mats(MODE), mode_is_int4(MODE)>::kThreads), 1)
 moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_constant__ CUtensorMap tm_scale,
                const __grid_constant__ CUtensorMap tm_tokens, const TcParams p) {
-  using Cfg = TcCfg<BT, mode_mats(MODE)>;
+  using Cfg = TcCfg<BT, mode_mats(MODE), mode_is_int4(MODE)>;
   constexpr int kWStages = Cfg::kWStages;
   constexpr int kMatsC = mode_mats(MODE);
   extern __shared__ unsigned char smem_raw[];
@@ -288,8 +288,8 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
   }
   // the token producer gets a warp of its own when the issuers leave one free (two threads of one warp
   // that both poll with back-off slow each other down); otherwise it shares the weight producer's
-  constexpr int kTokWarp = (Cfg::kIssuers < kMaxIssuers) ? kCtrlWarps - 1 : 0;
-  constexpr int kTokLane = (Cfg::kIssuers < kMaxIssuers) ? 0 : 1;
+  constexpr int kCtrlWarps = Cfg::kCtrlWarps;
+  constexpr int kTokWarp = kCtrlWarps - 1, kTokLane = 0;   // a warp of its own: two polling threads in one warp slow each other down
   if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
   if (warp == 0 && lane == 0) { prefetch_tensormap(&tm_packed); if (mode_is_int4(MODE)) prefetch_tensormap(&tm_scale); }
   if (warp == kTokWarp && lane == kTokLane) prefetch_tensormap(&tm_tokens);
@@ -723,7 +723,7 @@ int make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const 
 template <int BT, int MODE>
 int launch_bt(const CUtensorMap& tmp, const CUtensorMap& tms, const CUtensorMap& tmt, const TcParams& prm,
               int64_t max_tiles, cudaStream_t stream) {
-  using Cfg = TcCfg<BT, mode_mats(MODE)>;
+  using Cfg = TcCfg<BT, mode_mats(MODE), mode_is_int4(MODE)>;
   XKB_CHECK_CUDA(cudaFuncSetAttribute(moe_tc_kernel<BT, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)Cfg::kSmemBytes));
   int dev = 0, sms = 148;
