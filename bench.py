@@ -248,9 +248,9 @@ def run_single_gpu(args):
     gemm_avg_ms = sum(gemm_ms) / max(len(gemm_ms), 1)
     achieved = alg_bytes / (gemm_avg_ms * 1e-3) / 1e9
     # DRAM traffic per launch from the ncu capture of the 16-expert relative of this workload
-    # (profiles/moe_tc_kernel_int4_decode_small.md: 273.6 MB read+write for 264.2 MB of weights and
+    # (profiles/moe_tc_kernel_int4_decode_small.md: 273.9 MB read+write for 264.2 MB of weights and
     # scales); traffic grows with the experts touched, so it is scaled by n_active / 16.
-    traffic = 273.6e6 * n_active / 16.0
+    traffic = 273.9e6 * n_active / 16.0
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "frac": achieved / peaks["hbm_gbs"], "traffic": traffic,
                 "kernel": "moe_tc_kernel<16, int4>", "kernel_us": gemm_avg_ms * 1e3,

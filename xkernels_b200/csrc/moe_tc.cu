@@ -5,19 +5,19 @@
 // tokens of one expert block), so a decode batch with a handful of tokens per
 // expert still fills the 128-row datapath and the kernel's cost is the weight
 // stream.  One persistent CTA per SM (it owns all 512 tensor-memory columns),
-// twenty warps, everything handed over in whole 256-K stages:
+// twenty or twenty-one warps, everything handed over in whole 256-K stages:
 //
 //   warp 0   TMA producer, weights: packed tile [128 rows x 128 B] (128B swizzle, so that one
 //            row per thread reads conflict-free) + bf16 scale tile [128 x 8] per stage (MXFP4
 //            scales are read from global memory by the dequantisers).
-//   warps 1-2 MMA issuers (lane 0 each; warp 1 also allocates and frees tensor
+//   then     two or three MMA issuer warps (lane 0 each; warp 1 also allocates and frees tensor
 //            memory): tcgen05.mma kind::f16, A from tensor memory, B from shared
 //            memory, fp32 accumulators in tensor memory.  They take whole stages in
 //            turn, each into its own accumulator.
-//   warp 3   TMA producer, tokens: four [BT x 64] bf16 sub-tiles per stage (128B swizzle =
+//   then     TMA producer, tokens: four [BT x 64] bf16 sub-tiles per stage (128B swizzle =
 //            the UMMA K-major canonical layout) from the gathered activation buffer.  (In a
 //            warp of its own: two polling threads in one warp slow each other down.)
-//   warps 4-19 dequantisers: thread = weight row; nibbles -> exact bf16 integers
+//   then     sixteen dequantiser warps: thread = weight row; nibbles -> exact bf16 integers
 //            by the 0x4300|nib trick, minus 136, times the group scale in one
 //            bf16 multiply (= the reference's single rounding,
 //            src/xkernels/ops/moe/w4a16.py:44-50), written to tensor memory with
@@ -58,9 +58,6 @@ constexpr int kSubs = kStageK / kSubK;  // 4
 constexpr int kSlotCols = kStageK / 2;                 // 128 columns of bf16 pairs per A slot
 constexpr int kSubCols = kSubK / 2;                    // 32 of them per warpgroup
 constexpr int kMaxIssuers = 3;
-constexpr int kMaxCtrlWarps = 2 + kMaxIssuers;  // warp 0: weight producer; then the issuers; the last control warp hosts the
-                                             // token producer when the issuers leave it free
-                                             // (20 warps in all: register files are handed out four warps at a time)
 #ifndef XKB_W_STAGES_NARROW
 #define XKB_W_STAGES_NARROW 6
 #endif
