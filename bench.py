@@ -557,7 +557,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the other single-GPU configurations")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
-    ap.add_argument("--ep-placement", default="round_robin", choices=["contiguous", "round_robin"],
+    ap.add_argument("--ep-placement", default="round_robin", choices=["contiguous", "round_robin", "snake"],
                     help="expert -> rank assignment of the expert-parallel run")
     ap.add_argument("--ep-chunks", type=int, default=1, help="token chunks pipelined through the exchanges")
     ap.add_argument("--ep-sm-margin", type=int, default=16,

@@ -196,7 +196,8 @@ int xkb_set_sm_margin(int sms);
  * (token, rank), -1 if none), counts [chunks*world] pairs per group, info[2] =
  * {number of pairs, number of expert ids outside [0, experts_per_rank*world)}.
  * round_robin = 0: rank r owns experts [r*experts_per_rank, ...); 1: expert g
- * lives on rank g % world as local expert g / world.  top_k <= 32. */
+ * lives on rank g % world as local expert g / world; 2: as 1, but every second
+ * group of `world` experts is dealt in reverse rank order.  top_k <= 32. */
 int64_t xkb_ep_plan_workspace_bytes(int64_t M, int top_k, int world, int chunks);
 int xkb_ep_plan(const int32_t* topk_ids, const float* topk_w, int64_t M, int top_k,
                 int experts_per_rank, int world, int round_robin, int chunks,

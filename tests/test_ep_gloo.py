@@ -88,7 +88,8 @@ def _worker(rank: int, world: int, port: int, fail_rank: int, placement: str = "
 
 
 @pytest.mark.parametrize("world,placement,chunks", [(2, "contiguous", 1), (4, "contiguous", 1),
-                                                     (2, "round_robin", 3), (4, "round_robin", 2)])
+                                                     (2, "round_robin", 3), (4, "round_robin", 2),
+                                                     (4, "snake", 1)])
 def test_all_to_all_matches_dense_oracle(world, placement, chunks):
     mp.spawn(_worker, args=(world, _free_port(), -1, placement, chunks), nprocs=world, join=True)
 
@@ -112,6 +113,10 @@ def test_plan_dispatch_makes_one_pair_per_token_and_owner():
     assert plan.pair_dest.tolist() == [0, 1, 0, 1]
     assert plan.pair_ids.tolist() == [[-1, 0, -1], [2, -1, 1], [-1, -1, 1], [0, 3, -1]]
     assert ep.local_expert_ids(1, 4, 2, "round_robin") == [1, 3, 5, 7]
+    # snake: groups of W experts dealt forwards, backwards, forwards, ...
+    assert ep.local_expert_ids(0, 4, 2, "snake") == [0, 3, 4, 7] and ep.local_expert_ids(1, 4, 2, "snake") == [1, 2, 5, 6]
+    owner, local = ep.owner_and_local(torch.arange(8), 4, 2, "snake")
+    assert owner.tolist() == [0, 1, 1, 0, 0, 1, 1, 0] and local.tolist() == [0, 0, 1, 1, 2, 2, 3, 3]
     # a token whose experts all live on one rank crosses the wire once
     plan = ep.plan_dispatch(torch.tensor([[0, 1, 2]], dtype=torch.int32), 4, 2)
     assert plan.send_counts.tolist() == [[1, 0]] and plan.pair_ids.tolist() == [[0, 1, 2]]

@@ -68,6 +68,7 @@ def test_rows_with_absent_slots_and_per_row_sum(cuda_device):
 @pytest.mark.parametrize("M,E,top_k,world,placement,chunks", [
     (96, 16, 4, 2, "contiguous", 1), (96, 16, 4, 4, "round_robin", 3), (4096, 256, 8, 8, "round_robin", 1),
     (1, 8, 8, 8, "contiguous", 1), (333, 48, 6, 4, "contiguous", 2), (0, 8, 2, 2, "contiguous", 1),
+    (500, 64, 8, 8, "snake", 1), (96, 16, 4, 2, "snake", 2),
 ])
 def test_device_plan_equals_host_plan(M, E, top_k, world, placement, chunks, cuda_device):
     """xkb_ep_plan (three launches, no host read) against ep.plan_dispatch (torch ops on the CPU)."""
@@ -131,7 +132,7 @@ def _ep_worker(rank: int, world: int, port: int, placement: str, chunks: int):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("placement,chunks", [("contiguous", 1), ("round_robin", 3)])
+@pytest.mark.parametrize("placement,chunks", [("contiguous", 1), ("round_robin", 3), ("snake", 1)])
 def test_all_to_all_on_gpus(placement, chunks):
     n = torch.cuda.device_count()
     if n < 2:

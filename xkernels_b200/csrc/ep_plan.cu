@@ -17,8 +17,12 @@ constexpr int kMaxTopK = 32;
 
 __device__ __forceinline__ void owner_local(int id, int experts_per_rank, int world, int round_robin, int& owner,
                                             int& local) {
-  if (round_robin) { owner = id % world; local = id / world; }
-  else { owner = id / experts_per_rank; local = id - owner * experts_per_rank; }
+  if (round_robin == 1) { owner = id % world; local = id / world; }
+  else if (round_robin == 2) {   // snake: every second group of `world` experts in reverse rank order
+    local = id / world;
+    const int pos = id % world;
+    owner = (local & 1) ? world - 1 - pos : pos;
+  } else { owner = id / experts_per_rank; local = id - owner * experts_per_rank; }
 }
 
 // thread = token: key[slot] = chunk * world + rank for the first slot of the token that goes to that

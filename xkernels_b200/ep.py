@@ -26,7 +26,8 @@ the fp32 additions differs (experts of one rank first).
 Expert placement: ``"contiguous"`` (rank r owns experts ``[r*E/W, (r+1)*E/W)``, the layout of the
 reference's ``expert_map`` tests, tests/test_moe_int4_ep.py:84-93) or ``"round_robin"`` (expert g
 lives on rank ``g % W`` as local expert ``g // W``), which spreads a popularity-ranked expert set
-evenly over the ranks.
+evenly over the ranks, or ``"snake"`` (like round robin, but every second group of W experts is
+dealt in reverse rank order, so that no rank collects the most popular expert of every group).
 
 The exchange uses ``torch.distributed`` (NCCL on GPUs, gloo on CPU); data lands in local buffers
 before any kernel reads it.  The local compute is pluggable so the routing logic runs on CPU ranks
@@ -48,6 +49,10 @@ def owner_and_local(expert: torch.Tensor, experts_per_rank: int, world: int, pla
         return owner, expert - owner * experts_per_rank
     if placement == "round_robin":
         return expert % world, torch.div(expert, world, rounding_mode="floor")
+    if placement == "snake":
+        group = torch.div(expert, world, rounding_mode="floor")
+        pos = expert % world
+        return torch.where(group % 2 == 0, pos, world - 1 - pos), group
     raise ValueError(f"unknown expert placement {placement!r}")
 
 
@@ -57,6 +62,8 @@ def local_expert_ids(rank: int, experts_per_rank: int, world: int, placement: st
         return list(range(rank * experts_per_rank, (rank + 1) * experts_per_rank))
     if placement == "round_robin":
         return [rank + world * i for i in range(experts_per_rank)]
+    if placement == "snake":
+        return [world * i + (rank if i % 2 == 0 else world - 1 - rank) for i in range(experts_per_rank)]
     raise ValueError(f"unknown expert placement {placement!r}")
 
 

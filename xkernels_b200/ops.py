@@ -357,6 +357,9 @@ def moe_gather_sum_reduce(rows, row_index, w, out_dtype=torch.bfloat16):
     return out
 
 
+_PLACEMENT = {"contiguous": 0, "round_robin": 1, "snake": 2}
+
+
 def ep_plan(topk_ids, topk_w, experts_per_rank, world, placement="contiguous", chunks=1):
     """Device-side dispatch plan of the all-to-all expert-parallel mode (``xkb_ep_plan``): no host
     read.  Returns ``(pair_token, pair_dest, routing, pair_of, counts, info)`` with the per-pair
@@ -364,7 +367,7 @@ def ep_plan(topk_ids, topk_w, experts_per_rank, world, placement="contiguous", c
     ``xkernels_b200/ep.py:plan_dispatch`` for the meaning of each."""
     lib = _lib.load()
     dev = _require_cuda("ep_plan", topk_ids, topk_w)
-    if placement not in ("contiguous", "round_robin"):
+    if placement not in _PLACEMENT:
         raise ValueError(f"unknown expert placement {placement!r}")
     ids = topk_ids.to(torch.int32).contiguous()
     w = topk_w.to(torch.float32).contiguous()
@@ -381,7 +384,7 @@ def ep_plan(topk_ids, topk_w, experts_per_rank, world, placement="contiguous", c
         ws = get_workspace(dev, ws_bytes, tag=1)     # not the fused ops' buffer: that one starts with their status words
         _lib.check(
             lib.xkb_ep_plan(_ptr(ids), _ptr(w), M, top_k, int(experts_per_rank), int(world),
-                            1 if placement == "round_robin" else 0, int(chunks), _ptr(pair_token), _ptr(pair_dest),
+                            _PLACEMENT[placement], int(chunks), _ptr(pair_token), _ptr(pair_dest),
                             _ptr(routing), _ptr(pair_of), _ptr(counts), _ptr(info), _ptr(ws), ws.numel(),
                             _stream(dev)),
             "xkb_ep_plan")
