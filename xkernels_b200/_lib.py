@@ -11,10 +11,7 @@ import ctypes
 from ctypes import c_char_p, c_float, c_int, c_int64, c_void_p
 from pathlib import Path
 
-import os
-
-# XKB200_LIB points at an alternative build of the library (e.g. an instrumented one).
-LIB_PATH = Path(os.environ.get("XKB200_LIB") or Path(__file__).resolve().parent / "libxkb200.so")
+LIB_PATH = Path(__file__).resolve().parent / "libxkb200.so"
 
 XKB_BF16 = 0
 XKB_F32 = 1

@@ -80,12 +80,11 @@ int launch_align(const int32_t* topk_ids, int64_t numel, int num_experts, int bl
                  void* workspace, int64_t workspace_bytes, cudaStream_t stream);
 int64_t align_workspace_bytes(int64_t numel, int num_experts);
 
-// out[m,n] = sum_j scratch[m*top_k+j, n] over the slots that are local
-// (expert_map NULL or expert_map[topk_ids[slot]] >= 0), ascending j, fp32.
-// `parts` copies of the slot rows (part p at scratch + p*M*top_k*N) are added up, part-major inside a slot.
+// out[m,n] = sum_j scratch[m*top_k+j, n] over the slots whose (mapped) expert id lies in [0, E)
+// (the slots the align stage kept), ascending j, fp32.
 int launch_combine(const float* scratch, const int32_t* topk_ids, const int32_t* expert_map,
-                   int num_map, void* out, int out_dtype, int64_t M, int top_k, int64_t N,
-                   cudaStream_t stream, int parts = 1);
+                   int num_map, int E, void* out, int out_dtype, int64_t M, int top_k, int64_t N,
+                   cudaStream_t stream);
 
 // Records one event pair of the optional GEMM timer (xkb_gemm_timer_enable) around
 // the launches made while it is alive; does nothing when the timer is not armed.

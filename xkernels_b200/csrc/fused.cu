@@ -115,7 +115,7 @@ extern "C" int64_t xkb_fused_moe_int4_w4a16_workspace_bytes(int64_t M, int64_t N
   if (M < 0 || N < 0 || K < 0 || E < 0 || top_k < 0) return -1;
   const int64_t numel = M * top_k;
   int64_t total = routing_bytes(numel, E);
-  total += align_up(2 * numel * N * 4, 256);       // fp32 slot-indexed partial rows (two K parts at most)
+  total += align_up(numel * N * 4, 256);           // fp32 slot-indexed rows
   total += int4_tc_workspace_bytes(numel, N, K, E);  // gathered activations etc.
   return total + 256;
 }
@@ -147,7 +147,7 @@ static int int4_impl(const void* A, int a_dtype, const int32_t* packed, const vo
   const int64_t numel = M * top_k;
   Carver carve(workspace);
   RoutingBuffers rb = carve_routing(carve, numel, E);
-  float* scratch = carve.take<float>(2 * numel * N);
+  float* scratch = carve.take<float>(numel * N);
   if (rows_out != nullptr) scratch = rows_out;
   void* tc_ws = carve.take<char>(int4_tc_workspace_bytes(numel, N, K, E));
 
@@ -164,17 +164,15 @@ static int int4_impl(const void* A, int a_dtype, const int32_t* packed, const vo
   int rc = launch_align(topk_ids, numel, E, block, expert_map, num_map, rb.sorted_ids, rb.expert_ids,
                         rb.num_post, rb.expert_off, rb.align_ws, rb.align_ws_bytes, stream);
   if (rc != XKB_OK) return rc;
-  // K-split only when this call also runs the combine (caller-owned rows hold one part)
-  const int ksplit = (use_tc && rows_out == nullptr) ? int4_tc_ksplit(numel, N, K, E, block) : 1;
   if (use_tc)
-    rc = launch_int4_tc(A, packed, scale, r, topk_w, scratch, N, K, E, top_k, mul_routed_weight, ksplit,
+    rc = launch_int4_tc(A, packed, scale, r, topk_w, scratch, N, K, E, top_k, mul_routed_weight,
                         tc_ws, rb.status, stream);
   else
     rc = launch_int4_simt(A, a_dtype, packed, scale, r, topk_w, scratch, N, K, top_k, group_size,
                           mul_routed_weight, stream);
   if (rc != XKB_OK) return rc;
   if (rows_out != nullptr) return XKB_OK;
-  return launch_combine(scratch, topk_ids, expert_map, num_map, out, a_dtype, M, top_k, N, stream, ksplit);
+  return launch_combine(scratch, topk_ids, expert_map, num_map, E, out, a_dtype, M, top_k, N, stream);
 }
 
 extern "C" int xkb_fused_moe_int4_w4a16(const void* A, int a_dtype, const int32_t* packed,
@@ -267,7 +265,7 @@ extern "C" int xkb_fused_moe_mxfp4(const void* A, int a_dtype, const uint8_t* w1
     rc = launch_mxfp4_simt(A, a_dtype, w13, w13_scale, w2, w2_scale, b13, b2, r, topk_w, act, scratch,
                            hidden, ispp, top_k, swiglu_limit, mul_routed_weight, stream);
   if (rc != XKB_OK) return rc;
-  return launch_combine(scratch, topk_ids, expert_map, num_map, out, a_dtype, M, top_k, hidden, stream);
+  return launch_combine(scratch, topk_ids, expert_map, num_map, E, out, a_dtype, M, top_k, hidden, stream);
 }
 
 // ---------------------------------------------------------------------------

@@ -20,12 +20,9 @@ int launch_mxfp4_simt(const void* A, int a_dtype, const uint8_t* w13, const uint
 bool int4_tc_supported(int a_dtype, int64_t M, int64_t N, int64_t K, int E, int top_k, int group);
 int int4_tc_block(int64_t numel, int E);
 int64_t int4_tc_workspace_bytes(int64_t numel, int64_t N, int64_t K, int E);
-// ksplit: the kernel writes `ksplit` copies of the slot rows (part p at scratch + p*numel*N) that the
-// combine adds up; int4_tc_ksplit picks 1 or 2 from the expected tile count per CTA.
-int int4_tc_ksplit(int64_t numel, int64_t N, int64_t K, int E, int block);
 int launch_int4_tc(const void* A, const int32_t* packed, const void* scale, const Routing& r,
                    const float* topk_w, float* scratch, int64_t N, int64_t K, int E, int top_k,
-                   int mul_w, int ksplit, void* tc_ws, int* status, cudaStream_t stream);
+                   int mul_w, void* tc_ws, int* status, cudaStream_t stream);
 
 bool mxfp4_tc_supported(int a_dtype, int64_t M, int64_t hidden, int64_t ispp, int E, int top_k);
 int mxfp4_tc_block(int64_t numel, int E);

@@ -41,7 +41,6 @@
 // a status code, all roles leave their loops, and tensor memory is released.
 
 #include <atomic>
-#include <cstdlib>
 #include "moe_kernels.h"
 #include "tc_common.cuh"
 
@@ -58,21 +57,11 @@ constexpr int kSubs = kStageK / kSubK;  // 4
 constexpr int kSlotCols = kStageK / 2;                 // 128 columns of bf16 pairs per A slot
 constexpr int kSubCols = kSubK / 2;                    // 32 of them per warpgroup
 constexpr int kMaxIssuers = 3;
-#ifndef XKB_W_STAGES_NARROW
-#define XKB_W_STAGES_NARROW 6
-#endif
-#ifndef XKB_B_STAGES_16
-#define XKB_B_STAGES_16 9
-#endif
-#ifndef XKB_PROD_SLEEP
-#define XKB_PROD_SLEEP 400
-#endif
-#ifndef XKB_ISS_SLEEP
-#define XKB_ISS_SLEEP 32
-#endif
-#ifndef XKB_NARROW_WGS
-#define XKB_NARROW_WGS 4
-#endif
+constexpr int kWStagesNarrow = 6;      // weight ring depth for token tiles of 16
+constexpr int kBStages16 = 9;          // token ring depth for token tiles of 16
+constexpr uint32_t kProdSleepNs = 400; // back-off of the TMA producers, which run a whole ring ahead
+constexpr uint32_t kIssSleepNs = 32;   // back-off of the MMA issuers (on the critical path: short)
+constexpr int kNarrowWGs = 4;          // dequantiser warpgroups for token tiles <= 64
 constexpr int kTmemCols = 512;     // one CTA per SM owns all of tensor memory
 constexpr int kPackedStageBytes = kTileRows * (kStageK / 2);  // 16 KiB
 constexpr int kScaleStageBytes = kTileRows * (kStageK / 32) * 2;  // 2 KiB
@@ -91,7 +80,7 @@ template <int BT, int MATS = 1, bool INT4 = true> struct TcCfg {
   // the tensor pipe and have only two A slots; there all sixteen warps fill one slot together,
   // which halves the fill latency in the slot's round trip.
   // dequantiser warpgroups (the four warps of one cover the four tensor-memory lane quarters)
-  static constexpr int kWGs = (BT <= 64) ? XKB_NARROW_WGS : 4;
+  static constexpr int kWGs = (BT <= 64) ? kNarrowWGs : 4;
   static constexpr int kDequantWarps = 4 * kWGs;
   // Control warps: weight producer, the issuers, token producer.  Narrow INT4 tiles run three
   // issuers (five control warps; 21 warps get 80 registers each, enough for the INT4 dequantiser);
@@ -105,10 +94,10 @@ template <int BT, int MATS = 1, bool INT4 = true> struct TcCfg {
   // Token ring.  A token stage is released by the commit of the MMAs that read it and re-filled by
   // TMA from L2 about a microsecond later; narrow tiles are small, so their ring is made deep
   // enough that the issuers never wait for tokens.
-  static constexpr int kBStages = (BT <= 16) ? XKB_B_STAGES_16 : (BT <= 32) ? 6 : (BT <= 64) ? (kGroups == 3 ? 3 : 4) : 2;
+  static constexpr int kBStages = (BT <= 16) ? kBStages16 : (BT <= 32) ? 6 : (BT <= 64) ? (kGroups == 3 ? 3 : 4) : 2;
   static constexpr int kBSubBytes = BT * kSubK * 2;
   static constexpr int kBStageBytes = kSubs * kBSubBytes;   // [4][BT x 64] bf16
-  static constexpr int kWStages = (BT <= 16) ? XKB_W_STAGES_NARROW : (BT <= 32 || kGroups == 3) ? 6 : 4;
+  static constexpr int kWStages = (BT <= 16) ? kWStagesNarrow : (BT <= 32 || kGroups == 3) ? 6 : 4;
   static_assert(kWStages % kGroups == 0, "a weight stage must always be converted by the same group");
   // MMA issuers.  One thread sustains one tcgen05.mma per ~45 cycles (65-100 beside busy
   // dequantiser warps) whatever the shape, and that is an issue limit of the thread, not of the
@@ -147,25 +136,6 @@ template <int BT, int MATS = 1, bool INT4 = true> struct TcCfg {
   static_assert(kSmemBytes <= 227 * 1024, "shared memory overcommitted");
 };
 
-#ifdef XKB_TC_TRACE
-// Debug builds only: CTA 0 logs (clock, tag) pairs per role into a global buffer.
-constexpr int kTraceCap = 4096;
-}  // namespace
-__device__ long long g_trace[8][kTraceCap];
-__device__ int g_trace_n[8];
-namespace {
-#define TRACE(role, tag)                                                         \
-  do {                                                                           \
-    if (blockIdx.x == 0 && trace_i < kTraceCap) {                                \
-      g_trace[role][trace_i++] = (clock64() << 8) | (tag);                       \
-      g_trace_n[role] = trace_i;                                                 \
-    }                                                                            \
-  } while (0)
-#else
-#define TRACE(role, tag) do {} while (0)
-#endif
-#define TRACE_ISS(tag) do { if (me < 2) TRACE(me == 0 ? 2 : 7, tag); } while (0)
-
 // Kernel modes: which weights are streamed and what the epilogue does.
 constexpr int kModeInt4 = 0;      // INT4 W4A16: rows = N, bf16 group scales by TMA, fp32 slot rows out
 constexpr int kModeMxGateUp = 1;  // MXFP4 w13: a tile is 128 gate rows + the 128 matching up rows, the
@@ -186,8 +156,6 @@ struct TcParams {
   int64_t numel;
   int N, K;                     // tile rows are taken from N rows per expert; K = contraction length
   int mul_w;
-  int ksplit;                   // K is cut in `ksplit` equal parts, each its own tile writing its own
-                                // copy of the slot rows (part p at scratch + p * numel * N); 1 = no split
   // MXFP4 only
   const uint8_t* mx_scale;      // e8m0 scales of the streamed matrix, [E, rows_per_expert, K/32]
   const __nv_bfloat16* bias;    // b13 [E, 2*ispp] or b2 [E, hidden] or nullptr
@@ -271,9 +239,6 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
   // role branches then live in uniform registers)
   const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
   Guard guard{abort_word, p.status};
-#ifdef XKB_TC_TRACE
-  int trace_i = 0;
-#endif
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kWStages; ++i) { mbar_init(&w_full[i], 1); mbar_init(&w_empty[i], 1); }
@@ -295,13 +260,12 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
   tc_fence_after();
   const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_slot, 0);   // (marks it warp-uniform)
 
-  // tile index t -> (K part, token block, row tile); the row tile varies fastest so that CTAs that run
+  // tile index t -> (token block, row tile); the row tile varies fastest so that CTAs that run
   // together share the token block and walk through one expert's weights
-  const int n_row_tiles = p.N / (MODE == kModeInt4Pair ? 2 * kTileRows : kTileRows);
-  const int n_tiles = n_row_tiles * p.ksplit;
+  const int n_tiles = p.N / (MODE == kModeInt4Pair ? 2 * kTileRows : kTileRows);
   const int n_blocks = p.num_post[0] / BT;
   const int64_t total_tiles = (int64_t)n_blocks * n_tiles;
-  const int k_stages = p.K / kStageK / p.ksplit;   // 256-K stages per tile
+  const int k_stages = p.K / kStageK;   // 256-K stages per tile
   // "virtual" weight stages of a tile: two-matrix modes alternate the matrices stage by stage
   constexpr int kMats = mode_mats(MODE);
   const int v_stages = kMats * k_stages;
@@ -319,14 +283,11 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
     {
       uint32_t st = 0, ph = 0;
       for (int64_t t = blockIdx.x; t < total_tiles && !guard.aborted(); t += gridDim.x) {
-        const int rt = (int)(t % n_tiles), b = (int)(t / n_tiles);
-        const int nt = rt % n_row_tiles, ks0 = (rt / n_row_tiles) * k_stages;
+        const int nt = (int)(t % n_tiles), b = (int)(t / n_tiles);
         for (int vs = 0; vs < v_stages; ++vs) {
-          const int ks = ks0 + vs / kMats;
+          const int ks = vs / kMats;
           const int row0 = tile_row(b, nt, vs);
-          TRACE(0, 1);
-          if (!mbar_wait(&w_empty[st], ph ^ 1, guard, 1, XKB_PROD_SLEEP)) break;
-          TRACE(0, 2);
+          if (!mbar_wait(&w_empty[st], ph ^ 1, guard, 1, kProdSleepNs)) break;
           if (mode_is_int4(MODE)) {
             mbar_expect_tx(&w_full[st], kPackedStageBytes + kScaleStageBytes);
             tma_load_2d(s_packed + st * kPackedStageBytes, &tm_packed, &w_full[st], ks * (kStageK / 2), row0);
@@ -346,21 +307,18 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
       for (int64_t t = blockIdx.x; t < total_tiles && !guard.aborted(); t += gridDim.x) {
         const int b = (int)(t / n_tiles);
         const int pos0 = b * BT;
-        const int ks0 = ((int)(t % n_tiles) / n_row_tiles) * k_stages;  // first 256-K stage of this K part
         for (int ks = 0; ks < k_stages; ++ks) {
-          TRACE(1, 1);
           // the slot's previous user was token stage tb - kBStages: wait for its readers' commits
           if (tb >= (uint32_t)Cfg::kBStages) {
             const uint32_t tp = tb - Cfg::kBStages;
-            if (!mbar_wait(&b_empty[tp % Cfg::kBBars], (tp / Cfg::kBBars) & 1u, guard, 2, XKB_PROD_SLEEP)) break;
+            if (!mbar_wait(&b_empty[tp % Cfg::kBBars], (tp / Cfg::kBBars) & 1u, guard, 2, kProdSleepNs)) break;
           }
           const uint32_t bar = tb % Cfg::kBBars;
-          TRACE(1, 2);
           mbar_expect_tx(&b_full[bar], Cfg::kBStageBytes);
 #pragma unroll
           for (int j = 0; j < kSubs; ++j)
             tma_load_2d(s_tokens + st * Cfg::kBStageBytes + j * Cfg::kBSubBytes, &tm_tokens, &b_full[bar],
-                        ((ks0 + ks) * kSubs + j) * kSubK, pos0);
+                        (ks * kSubs + j) * kSubK, pos0);
           if (++st == Cfg::kBStages) st = 0;
           ++tb;
         }
@@ -388,16 +346,13 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
           const uint32_t aq = g % Cfg::kASlots, abar = g % Cfg::kABars, aph = (g / Cfg::kABars) & 1u;
           const uint32_t tb = g / kMats;                    // token stage read by stage g
           const uint32_t bst = tb % Cfg::kBStages, bbar = tb % Cfg::kBBars, bph = (tb / Cfg::kBBars) & 1u;
-          TRACE_ISS(1);
-          ok = mbar_wait(&a_full[abar], aph, guard, 3, XKB_ISS_SLEEP);
-          TRACE_ISS(2);
+          ok = mbar_wait(&a_full[abar], aph, guard, 3, kIssSleepNs);
           // every dequantiser warp of the stage's group has arrived, so all of them are done with the
           // weight stage in shared memory: hand it back to the producer on their behalf
           if (ok) mbar_arrive(&w_empty[g % kWStages]);
           if (ok) ok = mbar_wait(&b_full[bbar], bph, guard, 4);
           if (!ok) break;
           tc_fence_after();
-          TRACE_ISS(3);
           const int acc = Cfg::kLocked ? mat : (int)me * kMats + mat;
           const uint32_t d_tmem = tmem_base + (uint32_t)(((int)dbuf * Cfg::kAccs + acc) * BT);
           const uint32_t a_tmem = tmem_base + Cfg::kACol0 + aq * kSlotCols;
@@ -412,10 +367,8 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
                            b_desc + (uint64_t)((sub * Cfg::kBSubBytes) >> 4) + (uint64_t)(kk * 2), idesc,
                            (fresh && sub == 0 && kk == 0) ? 0u : 1u);
           }
-          TRACE_ISS(4);
           tc_commit(&a_empty[abar]);
           tc_commit(&b_empty[bbar]);   // kMats arrivals release the token stage
-          TRACE_ISS(5);
         }
         if (!ok) break;
         tc_commit(&d_full[dbuf]);
@@ -439,17 +392,16 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
     const uint32_t s_packed_u32 = smem_u32(s_packed), s_scale_u32 = smem_u32(s_scale);
     // MXFP4: the four e8m0 bytes of this row's half stage, fetched one stage ahead
     auto mx_scale_load = [&](int64_t t, int vs) -> uint32_t {
-      const int rt = (int)(t % n_tiles), b = (int)(t / n_tiles);
-      const int nt = rt % n_row_tiles, ks0 = (rt / n_row_tiles) * k_stages;
+      const int nt = (int)(t % n_tiles), b = (int)(t / n_tiles);
       const int64_t grow = (int64_t)tile_row(b, nt, vs) + row;
-      const uint8_t* sp = p.mx_scale + grow * (p.K / 32) + (ks0 + vs / kMats) * (kStageK / 32) + part * kChunks;
+      const uint8_t* sp = p.mx_scale + grow * (p.K / 32) + (vs / kMats) * (kStageK / 32) + part * kChunks;
       if (kChunks == 4) return __ldg(reinterpret_cast<const uint32_t*>(sp));
       return __ldg(reinterpret_cast<const uint16_t*>(sp));
     };
-    // Epilogue of tile (b, nt, kpart) whose accumulators sit in set `dbuf` (use number `duse` of that
+    // Epilogue of tile (b, nt) whose accumulators sit in set `dbuf` (use number `duse` of that
     // set).  It runs one weight stage into the NEXT tile (or after the last tile), so that the MMAs
     // it waits for have long finished and the pipeline never drains at a tile boundary.
-    auto run_epilogue = [&](int b, int nt, int kpart, uint32_t dbuf, uint32_t duse, uint32_t tile_g0) -> bool {
+    auto run_epilogue = [&](int b, int nt, uint32_t dbuf, uint32_t duse, uint32_t tile_g0) -> bool {
       const uint32_t d_base = tmem_base + lane_base + dbuf * (uint32_t)(Cfg::kAccs * BT);
       // which accumulators the tile's stages went to: stage vs -> (issuer (g0 + vs) % kIssuers, matrix vs % kMats)
       uint32_t valid = 0;
@@ -522,11 +474,11 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
             } else if (p.mul_w) {
               v = p.topk_w[slot] * v;
             }
-            p.scratch[((int64_t)kpart * p.numel + slot) * p.N + n_glob] = v;
+            p.scratch[(int64_t)slot * p.N + n_glob] = v;
             if (MODE == kModeInt4Pair) {  // the second weight tile: rows 128 further down
               float v2 = __uint_as_float(more[j]);
               if (p.mul_w) v2 = p.topk_w[slot] * v2;
-              p.scratch[((int64_t)kpart * p.numel + slot) * p.N + n_glob + kTileRows] = v2;
+              p.scratch[(int64_t)slot * p.N + n_glob + kTileRows] = v2;
             }
           }
         }
@@ -537,10 +489,8 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
       return true;
     };
     bool pend = false;
-    int pend_b = 0, pend_nt = 0, pend_kpart = 0;
+    int pend_b = 0, pend_nt = 0;
     uint32_t pend_it = 0, pend_g0 = 0, it = 0, g0 = 0;      // g0 = number of the tile's first stage
-    const bool tracer = (lane == 0 && quarter == 0);
-    (void)tracer;
     // the stage this group converts after (t, vs, g0): two further on, or the first own stage of a later tile
     auto next_own = [&](int64_t& t, int& vs, uint32_t& gbase) -> bool {
       vs += kGroups;
@@ -558,17 +508,14 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
       if (tn < total_tiles && next_own(tn, vn, gn)) mx_next = mx_scale_load(tn, vn);
     }
     for (int64_t t = blockIdx.x; t < total_tiles; t += gridDim.x, ++it, g0 += (uint32_t)v_stages) {
-      const int rt = (int)(t % n_tiles), b = (int)(t / n_tiles);
-      const int nt = rt % n_row_tiles, kpart = rt / n_row_tiles;
+      const int nt = (int)(t % n_tiles), b = (int)(t / n_tiles);
       bool ok = true;
       bool epi_due = pend;   // the previous tile's epilogue runs after this group's first stage of this tile
       for (int vs = (int)((grp + kGroups - g0 % kGroups) % kGroups); vs < v_stages && ok; vs += kGroups) {
         const uint32_t g = g0 + (uint32_t)vs;
         const uint32_t wst = g % kWStages, wph = (g / kWStages) & 1u;
         const uint32_t aq = g % Cfg::kASlots, abar = g % Cfg::kABars, aph = (g / Cfg::kABars) & 1u;
-        if (tracer) TRACE(3 + wg, 1);
         if (!mbar_wait(&w_full[wst], wph, guard, 5)) { ok = false; break; }
-        if (tracer) TRACE(3 + wg, 2);
         const uint32_t pk = s_packed_u32 + wst * kPackedStageBytes + row * 128;
         uint2 sw = make_uint2(0, 0);  // INT4: the kChunks bf16 group scales of this share; MXFP4: .x = its e8m0 bytes
         if (mode_is_int4(MODE)) {
@@ -585,14 +532,12 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
         for (int c = 0; c < kChunks; ++c) w4[c] = lds128(pk + (((part * kChunks + c) ^ (row & 7)) << 4));
         // (the stage is handed back to the producer by the MMA issuer once all warps of the group have
         // published the converted slices, which they do after these loads)
-        if (tracer) TRACE(3 + wg, 3);
         // the slot's previous user was stage g - kASlots: wait until its MMAs have completed
         if (g >= (uint32_t)Cfg::kASlots) {
           const uint32_t gp = g - Cfg::kASlots;
           if (!mbar_wait(&a_empty[gp % Cfg::kABars], (gp / Cfg::kABars) & 1u, guard, 6)) { ok = false; break; }
         }
         tc_fence_after();
-        if (tracer) TRACE(3 + wg, 4);
         const uint32_t dst = tmem_base + lane_base + Cfg::kACol0 + aq * kSlotCols + part * (kChunks * 16);
 #pragma unroll
         for (int c = 0; c < kChunks; ++c) {
@@ -621,25 +566,23 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
             }
           }
         }
-        if (tracer) TRACE(3 + wg, 5);
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&a_full[abar]);
-        if (tracer) TRACE(3 + wg, 6);
         if (epi_due) {
           epi_due = false;
-          if (!run_epilogue(pend_b, pend_nt, pend_kpart, pend_it % Cfg::kDBuf, pend_it / Cfg::kDBuf, pend_g0)) { ok = false; break; }
+          if (!run_epilogue(pend_b, pend_nt, pend_it % Cfg::kDBuf, pend_it / Cfg::kDBuf, pend_g0)) { ok = false; break; }
         }
       }
       if (!ok) break;
       if (epi_due) {  // this group had no stage in this tile
-        if (!run_epilogue(pend_b, pend_nt, pend_kpart, pend_it % Cfg::kDBuf, pend_it / Cfg::kDBuf, pend_g0)) break;
+        if (!run_epilogue(pend_b, pend_nt, pend_it % Cfg::kDBuf, pend_it / Cfg::kDBuf, pend_g0)) break;
       }
       // the epilogue is deferred: see run_epilogue
-      pend = true; pend_b = b; pend_nt = nt; pend_kpart = kpart; pend_it = it; pend_g0 = g0;
+      pend = true; pend_b = b; pend_nt = nt; pend_it = it; pend_g0 = g0;
     }
-    if (pend && !guard.aborted()) run_epilogue(pend_b, pend_nt, pend_kpart, pend_it % Cfg::kDBuf, pend_it / Cfg::kDBuf, pend_g0);
+    if (pend && !guard.aborted()) run_epilogue(pend_b, pend_nt, pend_it % Cfg::kDBuf, pend_it / Cfg::kDBuf, pend_g0);
   }
 
   tc_fence_before();
@@ -761,19 +704,9 @@ int64_t int4_tc_workspace_bytes(int64_t numel, int64_t N, int64_t K, int E) {
   return align_up((numel + (int64_t)(E + 1) * 255) * K * 2, 256);
 }
 
-int int4_tc_ksplit(int64_t numel, int64_t N, int64_t K, int E, int block) {
-  // Tiles are equal-sized, so a decode launch whose CTAs get five or six tiles each loses up to 14 %
-  // to the last round; cutting K in two (ksplit = 2) evens that out.  Measured on the decode
-  // configuration it costs more than it saves (260 us against 248 us: twice the pipeline fills and
-  // epilogues, a second copy of the slot rows), so the split stays off; the kernel and the combine
-  // keep the capability.
-  (void)numel; (void)N; (void)K; (void)E; (void)block;
-  return 1;
-}
-
 int launch_int4_tc(const void* A, const int32_t* packed, const void* scale, const Routing& r,
                    const float* topk_w, float* scratch, int64_t N, int64_t K, int E, int top_k, int mul_w,
-                   int ksplit, void* tc_ws, int* status, cudaStream_t stream) {
+                   void* tc_ws, int* status, cudaStream_t stream) {
   Carver carve(tc_ws);
   __nv_bfloat16* Ag = carve.take<__nv_bfloat16>(r.max_pad * K);
 
@@ -806,19 +739,18 @@ int launch_int4_tc(const void* A, const int32_t* packed, const void* scale, cons
   prm.N = (int)N;
   prm.K = (int)K;
   prm.mul_w = mul_w;
-  prm.ksplit = ksplit;
   prm.mx_scale = nullptr;
   prm.bias = nullptr;
   prm.act = nullptr;
   prm.rows_per_expert = (int)N;
   prm.limit = 0.f;
-  const int64_t max_tiles = r.max_blocks * (N / kTileRows) * ksplit;
+  const int64_t max_tiles = r.max_blocks * (N / kTileRows);
   switch (r.block) {
     case 16: return launch_bt<16, kModeInt4>(tm_packed, tm_scale, tm_tokens, prm, max_tiles, stream);
     case 32: return launch_bt<32, kModeInt4>(tm_packed, tm_scale, tm_tokens, prm, max_tiles, stream);
     case 64: return launch_bt<64, kModeInt4>(tm_packed, tm_scale, tm_tokens, prm, max_tiles, stream);
     case 128:
-      if (N % (2 * kTileRows) == 0 && getenv("XKB_NO_PAIR") == nullptr)
+      if (N % (2 * kTileRows) == 0)
         return launch_bt<128, kModeInt4Pair>(tm_packed, tm_scale, tm_tokens, prm, max_tiles / 2, stream);
       return launch_bt<128, kModeInt4>(tm_packed, tm_scale, tm_tokens, prm, max_tiles, stream);
     default: return fail(XKB_ERR_ARG, "int4 tcgen05 path: unsupported token tile %d", r.block);
@@ -885,7 +817,6 @@ int launch_mxfp4_tc(const void* A, const uint8_t* w13, const uint8_t* w13_scale,
   prm.numel = r.numel;
   prm.mul_w = mul_w;
   prm.limit = limit;
-  prm.ksplit = 1;
   // stage 0: gate_up + SwiGLU -> act
   prm.scratch = nullptr;
   prm.act = act;
@@ -912,17 +843,6 @@ int launch_mxfp4_tc(const void* A, const uint8_t* w13, const uint8_t* w13_scale,
 }
 
 }  // namespace xkb
-
-#ifdef XKB_TC_TRACE
-extern "C" int xkb_debug_trace(long long* host, int* counts_host) {
-  int zero[8] = {0};
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(counts_host, xkb::g_trace_n, sizeof(int) * 8);
-  cudaMemcpyFromSymbol(host, xkb::g_trace, sizeof(long long) * 8 * xkb::kTraceCap);
-  cudaMemcpyToSymbol(xkb::g_trace_n, zero, sizeof(zero));
-  return 0;
-}
-#endif
 
 extern "C" int xkb_set_sm_margin(int sms) {
   if (sms < 0 || sms > 128) return xkb::fail(XKB_ERR_ARG, "xkb_set_sm_margin: %d outside [0,128]", sms);

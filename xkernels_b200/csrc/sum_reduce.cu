@@ -51,22 +51,27 @@ __device__ __forceinline__ float to_f(__nv_bfloat16 x) { return __bfloat162float
 __device__ __forceinline__ void from_f(float& d, float x) { d = x; }
 __device__ __forceinline__ void from_f(__nv_bfloat16& d, float x) { d = __float2bfloat16_rn(x); }
 
-// Validity of slot (m,k) under expert parallelism: the slot contributes only if
-// its expert is local.  ids == nullptr means every slot contributes.
+// Validity of slot (m,k): the same predicate as the align stage (align.cu:map_expert), which
+// drops a slot whose (mapped) expert id falls outside [0, E) and therefore never has its fp32
+// row written.  The reference skips those slots too (src/xkernels/ops/moe/reference.py:59-63,
+// mxfp4_reference.py:82-83).  ids == nullptr means every slot contributes (moe_sum_reduce).
 __device__ __forceinline__ bool slot_valid(const int32_t* ids, const int32_t* emap, int num_map,
-                                           int64_t slot) {
-  if (ids == nullptr || emap == nullptr) return true;
-  const int g = ids[slot];
-  return g >= 0 && g < num_map && emap[g] >= 0;
+                                           int E, int64_t slot) {
+  if (ids == nullptr) return true;
+  int g = ids[slot];
+  if (emap != nullptr) {
+    if (g < 0 || g >= num_map) return false;
+    g = emap[g];
+  }
+  return g >= 0 && g < E;
 }
 
-template <typename TY, typename TW, typename TO, bool kParts>
+template <typename TY, typename TW, typename TO>
 __global__ void __launch_bounds__(256)
 sum_reduce_vec8_kernel(const TY* __restrict__ y, const TW* __restrict__ w, TO* __restrict__ out,
                        int64_t M, int top_k, int64_t H, float rsf, const int32_t* __restrict__ ids,
-                       const int32_t* __restrict__ emap, int num_map, int parts) {
+                       const int32_t* __restrict__ emap, int num_map, int E) {
   const int64_t hv = H >> 3;  // 8-wide columns per row
-  const int64_t part_stride = M * top_k * H;
   const int64_t total = M * hv;
   for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (int64_t)gridDim.x * blockDim.x) {
@@ -76,18 +81,16 @@ sum_reduce_vec8_kernel(const TY* __restrict__ y, const TW* __restrict__ w, TO* _
     const TY* row = y + (m * top_k) * H + h;
 #pragma unroll 4
     for (int k = 0; k < top_k; ++k) {
-      if (!slot_valid(ids, emap, num_map, m * top_k + k)) continue;
-      for (int part = 0; part < (kParts ? parts : 1); ++part) {
-        float v[8];
-        Vec8<TY>::load(row + (int64_t)k * H + part * part_stride, v);
-        if (w != nullptr) {
-          const float wk = to_f(w[m * top_k + k]);
+      if (!slot_valid(ids, emap, num_map, E, m * top_k + k)) continue;
+      float v[8];
+      Vec8<TY>::load(row + (int64_t)k * H, v);
+      if (w != nullptr) {
+        const float wk = to_f(w[m * top_k + k]);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) acc[i] += v[i] * wk;
-        } else {
+        for (int i = 0; i < 8; ++i) acc[i] += v[i] * wk;
+      } else {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) acc[i] += v[i];
-        }
+        for (int i = 0; i < 8; ++i) acc[i] += v[i];
       }
     }
 #pragma unroll
@@ -102,19 +105,16 @@ __global__ void __launch_bounds__(256)
 sum_reduce_scalar_kernel(const TY* __restrict__ y, const TW* __restrict__ w, TO* __restrict__ out,
                          int64_t M, int top_k, int64_t H, float rsf,
                          const int32_t* __restrict__ ids, const int32_t* __restrict__ emap,
-                         int num_map, int parts) {
+                         int num_map, int E) {
   const int64_t total = M * H;
-  const int64_t part_stride = M * top_k * H;
   for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (int64_t)gridDim.x * blockDim.x) {
     const int64_t m = idx / H, h = idx - m * H;
     float acc = 0.f;
     for (int k = 0; k < top_k; ++k) {
-      if (!slot_valid(ids, emap, num_map, m * top_k + k)) continue;
-      for (int part = 0; part < parts; ++part) {
-        const float v = to_f(y[(m * top_k + k) * H + h + part * part_stride]);
-        acc += (w != nullptr) ? v * to_f(w[m * top_k + k]) : v;
-      }
+      if (!slot_valid(ids, emap, num_map, E, m * top_k + k)) continue;
+      const float v = to_f(y[(m * top_k + k) * H + h]);
+      acc += (w != nullptr) ? v * to_f(w[m * top_k + k]) : v;
     }
     from_f(out[idx], acc * rsf);
   }
@@ -122,7 +122,7 @@ sum_reduce_scalar_kernel(const TY* __restrict__ y, const TW* __restrict__ w, TO*
 
 template <typename TY, typename TW, typename TO>
 int launch_typed(const void* y, const void* w, void* out, int64_t M, int top_k, int64_t H, float rsf,
-                 const int32_t* ids, const int32_t* emap, int num_map, cudaStream_t stream, int parts = 1) {
+                 const int32_t* ids, const int32_t* emap, int num_map, int E, cudaStream_t stream) {
   if (M == 0 || H == 0) return XKB_OK;
   const bool vec_ok = (H % 8 == 0) && (reinterpret_cast<uintptr_t>(y) % 16 == 0) &&
                       (reinterpret_cast<uintptr_t>(out) % 16 == 0);
@@ -132,19 +132,14 @@ int launch_typed(const void* y, const void* w, void* out, int64_t M, int top_k, 
   const int64_t cap = 148 * 8 * 4;
   if (blocks > cap) blocks = cap;
   if (vec_ok) {
-    if (parts > 1)
-      sum_reduce_vec8_kernel<TY, TW, TO, true><<<(unsigned)blocks, 256, 0, stream>>>(
-          static_cast<const TY*>(y), static_cast<const TW*>(w), static_cast<TO*>(out), M, top_k, H, rsf,
-          ids, emap, num_map, parts);
-    else
-      sum_reduce_vec8_kernel<TY, TW, TO, false><<<(unsigned)blocks, 256, 0, stream>>>(
-          static_cast<const TY*>(y), static_cast<const TW*>(w), static_cast<TO*>(out), M, top_k, H, rsf,
-          ids, emap, num_map, 1);
+    sum_reduce_vec8_kernel<TY, TW, TO><<<(unsigned)blocks, 256, 0, stream>>>(
+        static_cast<const TY*>(y), static_cast<const TW*>(w), static_cast<TO*>(out), M, top_k, H, rsf,
+        ids, emap, num_map, E);
     XKB_CHECK_LAUNCH("sum_reduce_vec8_kernel");
   } else {
     sum_reduce_scalar_kernel<TY, TW, TO><<<(unsigned)blocks, 256, 0, stream>>>(
         static_cast<const TY*>(y), static_cast<const TW*>(w), static_cast<TO*>(out), M, top_k, H, rsf,
-        ids, emap, num_map, parts);
+        ids, emap, num_map, E);
     XKB_CHECK_LAUNCH("sum_reduce_scalar_kernel");
   }
   return XKB_OK;
@@ -153,10 +148,10 @@ int launch_typed(const void* y, const void* w, void* out, int64_t M, int top_k, 
 template <typename TY, typename TW>
 int dispatch_out(int out_dtype, const void* y, const void* w, void* out, int64_t M, int top_k,
                  int64_t H, float rsf, const int32_t* ids, const int32_t* emap, int num_map,
-                 cudaStream_t s, int parts = 1) {
+                 int E, cudaStream_t s) {
   if (out_dtype == XKB_BF16)
-    return launch_typed<TY, TW, __nv_bfloat16>(y, w, out, M, top_k, H, rsf, ids, emap, num_map, s, parts);
-  return launch_typed<TY, TW, float>(y, w, out, M, top_k, H, rsf, ids, emap, num_map, s, parts);
+    return launch_typed<TY, TW, __nv_bfloat16>(y, w, out, M, top_k, H, rsf, ids, emap, num_map, E, s);
+  return launch_typed<TY, TW, float>(y, w, out, M, top_k, H, rsf, ids, emap, num_map, E, s);
 }
 
 // out[m, :] = sum_k w[m,k] * rows[row_index[m,k], :]   (fp32 rows, ascending k, fp32 sum).
@@ -187,10 +182,10 @@ gather_reduce_kernel(const float* __restrict__ rows, const int32_t* __restrict__
 }  // namespace
 
 int launch_combine(const float* scratch, const int32_t* topk_ids, const int32_t* expert_map,
-                   int num_map, void* out, int out_dtype, int64_t M, int top_k, int64_t N,
-                   cudaStream_t stream, int parts) {
+                   int num_map, int E, void* out, int out_dtype, int64_t M, int top_k, int64_t N,
+                   cudaStream_t stream) {
   return dispatch_out<float, float>(out_dtype, scratch, nullptr, out, M, top_k, N, 1.0f, topk_ids,
-                                    expert_map, num_map, stream, parts);
+                                    expert_map, num_map, E, stream);
 }
 
 }  // namespace xkb
@@ -210,12 +205,12 @@ extern "C" int xkb_moe_sum_reduce(const void* y, int y_dtype, const void* w, int
   const float rsf = routed_scaling_factor;
   if (y_dtype == XKB_BF16) {
     if (w != nullptr && w_dtype == XKB_BF16)
-      return dispatch_out<__nv_bfloat16, __nv_bfloat16>(out_dtype, y, w, out, M, top_k, H, rsf, nullptr, nullptr, 0, s);
-    return dispatch_out<__nv_bfloat16, float>(out_dtype, y, w, out, M, top_k, H, rsf, nullptr, nullptr, 0, s);
+      return dispatch_out<__nv_bfloat16, __nv_bfloat16>(out_dtype, y, w, out, M, top_k, H, rsf, nullptr, nullptr, 0, 0, s);
+    return dispatch_out<__nv_bfloat16, float>(out_dtype, y, w, out, M, top_k, H, rsf, nullptr, nullptr, 0, 0, s);
   }
   if (w != nullptr && w_dtype == XKB_BF16)
-    return dispatch_out<float, __nv_bfloat16>(out_dtype, y, w, out, M, top_k, H, rsf, nullptr, nullptr, 0, s);
-  return dispatch_out<float, float>(out_dtype, y, w, out, M, top_k, H, rsf, nullptr, nullptr, 0, s);
+    return dispatch_out<float, __nv_bfloat16>(out_dtype, y, w, out, M, top_k, H, rsf, nullptr, nullptr, 0, 0, s);
+  return dispatch_out<float, float>(out_dtype, y, w, out, M, top_k, H, rsf, nullptr, nullptr, 0, 0, s);
 }
 
 extern "C" int xkb_moe_gather_sum_reduce(const float* rows, const int32_t* row_index, const float* w,

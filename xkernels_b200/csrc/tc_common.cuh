@@ -67,10 +67,7 @@ struct Guard {
 // `sleep_ns` > 0 backs off between probes: roles that run ahead of the pipeline
 // (the TMA producers) and roles that wait on the slower side (the MMA issuers)
 // would otherwise spend issue slots on probes that the dequantiser warps need.
-#ifndef XKB_TRY_HINT_NS
-#define XKB_TRY_HINT_NS 1000
-#endif
-constexpr uint32_t kTryHintNs = XKB_TRY_HINT_NS;
+constexpr uint32_t kTryHintNs = 1000;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Guard& g, int where,
                                           uint32_t sleep_ns = 0) {
   if (mbar_try(bar, parity, kTryHintNs)) return true;   // the common case: already complete
@@ -135,19 +132,6 @@ __device__ __forceinline__ void tc_commit(uint64_t* bar) {
                : "memory");
 }
 
-// 32 lanes x 32 columns store: thread i of the warp writes its 32 registers to
-// lane (lane_base + i), columns [col, col+32).
-__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
-      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-      "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]),
-      "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]),
-      "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-      : "memory");
-}
 // 32 lanes x 8 columns store (registers r[0..7] of each thread).
 __device__ __forceinline__ void tmem_st_32x8(uint32_t taddr, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3,
                                              uint32_t r4, uint32_t r5, uint32_t r6, uint32_t r7) {
@@ -195,10 +179,6 @@ __device__ __forceinline__ void umma_ts_bf16(uint32_t d_tmem, uint32_t a_tmem, u
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
-}
-
-__device__ __forceinline__ void named_barrier(int id, int threads) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
 }  // namespace tc
