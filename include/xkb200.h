@@ -81,7 +81,7 @@ int xkb_moe_align_block_size(const int32_t* topk_ids, int64_t numel,
  * of the call - a plug-in living inside another runtime's memory pool, a
  * serving loop that has frozen its allocator, a plain C caller without one.
  * The scratch of the multi-launch path (the chunk x expert count matrix) is a
- * fixed array compiled into the library, about 258 KiB on every GPU that loads
+ * fixed array compiled into the library, 259 KiB on every GPU that loads
  * the library, kept until the process ends.  The call makes no cudaMalloc /
  * cudaFree and uses no allocating library routine; inputs and outputs are
  * still the caller's.
@@ -89,8 +89,9 @@ int xkb_moe_align_block_size(const int32_t* topk_ids, int64_t numel,
  * Limits: numel <= 262144 token-slots and num_experts <= 256; larger
  * arguments are refused with XKB_ERR_ARG and a message that names the limit.
  * The first call on a device looks up the array's device address
- * (cudaGetSymbolAddress, with that device current) and remembers it; make
- * that first call before starting any stream capture.  All calls on a device
+ * (cudaGetSymbolAddress, for the device that is current at the call, which
+ * must be the device `stream` belongs to) and remembers it; make that first
+ * call before starting any stream capture.  All calls on a device
  * share the one array, which keeps whatever the previous call left in it (no
  * part of it needs clearing: every entry that is read is first rewritten by
  * the same call).  Two calls that overlap on the GPU - different streams, or
@@ -234,6 +235,19 @@ int xkb_fused_moe_mxfp4(const void* A, int a_dtype, const uint8_t* w13,
  * launch (src/xkernels/_dispatch.py:204-240); this is the explicit query.
  * ---------------------------------------------------------------------- */
 int xkb_workspace_status(const void* workspace, void* stream);
+
+/* ------------------------------------------------------------------------
+ * xkb_selftest_bounded_wait: exercises the abort path of the tcgen05 kernels
+ * on purpose and harmlessly.  One small kernel allocates tensor memory and
+ * waits, with a 20 microsecond budget, on an mbarrier that nothing arrives on;
+ * the wait runs out, the kernel writes its status word into the workspace
+ * header, releases tensor memory and returns.  xkb_workspace_status on the
+ * same workspace then returns XKB_ERR_DEVICE, and the next fused call works.
+ * Nothing traps, faults or spins without a limit.  No reference counterpart
+ * (the reference's kernels have no device-side waits to bound).
+ * ---------------------------------------------------------------------- */
+int xkb_selftest_bounded_wait(void* workspace, int64_t workspace_bytes,
+                              void* stream);
 
 /* ------------------------------------------------------------------------
  * Measurement support: time the expert-GEMM kernel(s) of each fused call with

@@ -61,13 +61,15 @@ def _worker(rank: int, world: int, port: int, fail_rank: int, placement: str = "
                                       placement=placement, chunks=chunks,
                                       max_recv_rows=0 if rank == fail_rank else None)
         if fail_rank >= 0:
-            # capacity check: the overloaded rank raises on the host before any payload moves
-            raised = False
-            try:
+            # capacity check: EVERY rank raises the same refusal before any payload moves, so none
+            # is left waiting in the dispatch all-to-all
+            with pytest.raises(ep.ExchangeRefused, match=f"rank {fail_rank} would receive .* capacity 0"):
                 layer(A, ids, w)
-            except RuntimeError as exc:
-                raised = "capacity" in str(exc)
-            assert raised == (rank == fail_rank)
+            # the group is still usable: the next call with the limit lifted goes through
+            layer.max_recv_rows = None
+            out = layer(A, ids, w)
+            want = oracle.moe_w4a16(A, packed, scale, ids, w, 32)
+            assert oracle.count_violations(out, want, 2e-2, 1e-2) == 0
             return
         out = layer(A, ids, w)
         want = oracle.moe_w4a16(A, packed, scale, ids, w, 32)
@@ -122,10 +124,67 @@ def test_plan_dispatch_makes_one_pair_per_token_and_owner():
     assert plan.send_counts.tolist() == [[1, 0]] and plan.pair_ids.tolist() == [[0, 1, 2]]
 
 
-def test_receive_capacity_is_checked_on_the_host():
-    """Failure injected on the host: a rank whose receive capacity is exceeded raises a Python
-    exception; no kernel waits on anything."""
-    # every rank completes the count exchange, then only the overloaded one refuses; the others would
-    # block in the payload exchange, so the test stops after the count phase on all ranks
-    plan = ep.plan_dispatch(torch.zeros((4, 2), dtype=torch.int32), 4, 2)
-    assert plan.send_counts.tolist() == [[4, 0]]
+@pytest.mark.parametrize("world,fail_rank", [(2, 1), (4, 2)])
+def test_receive_capacity_refusal_is_raised_by_every_rank(world, fail_rank):
+    """Failure injected on the host: one rank's receive capacity is exceeded.  All ranks learn it
+    from the gathered count matrix and raise together; nothing waits on anything."""
+    mp.spawn(_worker, args=(world, _free_port(), fail_rank), nprocs=world, join=True)
+
+
+def _bad_input_worker(rank: int, world: int, port: int, case: str):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        packed, scale = synth.int4_weights(CFG.E, CFG.N, CFG.K, 32, seed=5)
+        e_local = CFG.E // world
+        sl = torch.tensor(ep.local_expert_ids(rank, e_local, world, "contiguous"))
+        layer = ep.ExpertParallelInt4(packed[sl], scale[sl], num_global_experts=CFG.E, group_size=32,
+                                      partial_fn=_oracle_partial(packed[sl], scale[sl]), reduce_fn=_cpu_reduce)
+        M = 0 if (case == "empty_rank" and rank == 1) else CFG.M
+        A = synth.activations(M, CFG.K, seed=100 + rank)
+        if M:
+            ids, w = synth.routing(M, CFG.E, CFG.top_k, seed=200 + rank)
+        else:
+            ids, w = torch.zeros((0, CFG.top_k), dtype=torch.int32), torch.zeros((0, CFG.top_k))
+        if case == "invalid_id":
+            if rank == 1:
+                ids = ids.clone()
+                ids[3, 1] = CFG.E          # one bad id on one rank only
+            with pytest.raises(ValueError, match=r"rank\(s\) \[1\]"):
+                layer(A, ids, w)
+        elif case == "negative_count":
+            counts = ep.plan_dispatch(ids, e_local, world, "contiguous", 1, host_checks=False).send_counts.clone()
+            if rank == 0:
+                counts[0, 1] = -5          # a corrupted count matrix on one rank
+            with pytest.raises(ep.ExchangeRefused, match="rank 0 reported a negative count"):
+                ep.exchange_counts(counts, dist.group.WORLD)
+        elif case == "too_many_pairs":
+            counts = ep.plan_dispatch(ids, e_local, world, "contiguous", 1, host_checks=False).send_counts.clone()
+            if rank == 1:
+                counts[0, 0] += 1000       # more pairs than the rank has slots
+            with pytest.raises(ep.ExchangeRefused, match="rank 1 reported"):
+                ep.exchange_counts(counts, dist.group.WORLD, n_slots=M * CFG.top_k)
+        else:                               # empty_rank: a rank without tokens still serves its experts
+            out = layer(A, ids, w)
+            assert out.shape == (M, CFG.N)
+            if M:
+                want = oracle.moe_w4a16(A, packed, scale, ids, w, 32)
+                assert oracle.count_violations(out, want, 2e-2, 1e-2) == 0
+            # what the ranks received is what the ranks sent
+            t = torch.tensor([layer.last_recv_rows, sum(layer.last_send_counts)])
+            dist.all_reduce(t)
+            assert int(t[0]) == int(t[1])
+        if case != "empty_rank":
+            # the refusal was collective: the group still works afterwards
+            ids_ok, w_ok = synth.routing(CFG.M, CFG.E, CFG.top_k, seed=300 + rank)
+            A_ok = synth.activations(CFG.M, CFG.K, seed=400 + rank)
+            out = layer(A_ok, ids_ok, w_ok)
+            want = oracle.moe_w4a16(A_ok, packed, scale, ids_ok, w_ok, 32)
+            assert oracle.count_violations(out, want, 2e-2, 1e-2) == 0
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("case", ["invalid_id", "negative_count", "too_many_pairs", "empty_rank"])
+def test_bad_inputs_on_one_rank_stop_every_rank(case):
+    mp.spawn(_bad_input_worker, args=(2, _free_port(), case), nprocs=2, join=True)

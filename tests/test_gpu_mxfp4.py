@@ -83,6 +83,37 @@ def test_expert_parallel_partials_sum_to_dense(cuda_device):
     assert bool(((total - dense).abs() <= slack).all()), "sum of partials differs from the dense result"
 
 
+@pytest.mark.parametrize("path", ["simt", "tc"])
+@pytest.mark.parametrize("with_map", [False, True])
+def test_slots_without_a_local_expert_are_dropped(path, with_map, cuda_device):
+    """Ids of -1 and ids >= E contribute nothing (ops/moe/mxfp4_reference.py:82-83); the combine
+    must not add the never-written rows of those slots (workspace poisoned beforehand)."""
+    from xkernels_b200 import ops
+
+    cfg = synth.Mxfp4Config("drop", M=24, hidden=256, ispp=256, E=6, top_k=3, scale_lo=119, scale_hi=124)
+    c = synth.make_mxfp4(cfg, seed=5)
+    g = torch.Generator().manual_seed(4)
+    ids = c["topk_ids"].clone()
+    kill = torch.rand(cfg.M, cfg.top_k, generator=g)
+    ids[kill < 0.2] = -1
+    ids[(kill >= 0.2) & (kill < 0.4)] = cfg.E + 1
+    ids[0] = -1
+    emap = None
+    if with_map:
+        emap = torch.arange(cfg.E + 4, dtype=torch.int32)
+        emap[cfg.E:] = -1
+        emap[1] = -1
+    want = oracle.moe_mxfp4(c["A"], c["w13"], c["w13_scale"], c["w2"], c["w2_scale"], ids.clamp(min=-1), c["topk_w"],
+                            expert_map=None if emap is None else torch.cat([emap, torch.tensor([-1], dtype=torch.int32)]))
+    d = to_dev({k: c.get(k) for k in KEYS}, cuda_device)
+    ops.get_workspace(cuda_device, 1 << 24).view(torch.float32)[64:].fill_(1.0e4)
+    got = xkb.fused_moe_mxfp4(d["A"], d["w13"], d["w13_scale"], d["w2"], d["w2_scale"], ids.to(cuda_device),
+                              d["topk_w"], expert_map=None if emap is None else emap.to(cuda_device), path=path)
+    ops.check_status(cuda_device)
+    assert_within(got, want, RTOL, ATOL, what=f"dropped slots/{path}/map={with_map}", allowed=max(1, want.numel() // 2000))
+    assert bool((got[0] == 0).all())
+
+
 def test_decode_config_full(cuda_device):
     """E=256, hidden=4096, ispp=512, top_k=6, M=48, scales in [118,130]: |out| ~ 4e3 with heavy
     cancellation.  The whole output is compared with the oracle (8 s of CPU); the measured

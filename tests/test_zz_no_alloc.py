@@ -18,7 +18,7 @@ from xkernels_b200 import _lib
 pytestmark = pytest.mark.gpu
 
 
-def _align(lib, fn_name, ids, E, block, dev, with_workspace):
+def _align(lib, fn_name, ids, E, block, dev, with_workspace, expert_map=None):
     numel = ids.numel()
     max_pad = numel + (E + 1) * (block - 1)
     max_blocks = -(-max_pad // block)
@@ -27,7 +27,9 @@ def _align(lib, fn_name, ids, E, block, dev, with_workspace):
     num_post = torch.full((1,), -7, dtype=torch.int32, device=dev)
     offs = torch.full((E + 1,), -7, dtype=torch.int32, device=dev)
     stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
-    common = [ctypes.c_void_p(ids.data_ptr()), ctypes.c_int64(numel), E, block, None, 0,
+    emap_p = None if expert_map is None else ctypes.c_void_p(expert_map.data_ptr())
+    common = [ctypes.c_void_p(ids.data_ptr()), ctypes.c_int64(numel), E, block, emap_p,
+              0 if expert_map is None else expert_map.numel(),
               ctypes.c_void_p(sorted_ids.data_ptr()), ctypes.c_void_p(expert_ids.data_ptr()),
               ctypes.c_void_p(num_post.data_ptr()), ctypes.c_void_p(offs.data_ptr())]
     if with_workspace:
@@ -62,6 +64,28 @@ def test_static_scratch_entry_point_matches_the_workspace_one(cuda_device):
     a = _align(lib, "xkb_moe_align_block_size_static", small, 8, 16, dev, with_workspace=False)
     b = _align(lib, "xkb_moe_align_block_size", small, 8, 16, dev, with_workspace=True)
     assert all(torch.equal(x, y) for x, y in zip(a, b))
+
+
+def test_static_scratch_entry_point_at_its_size_limit_and_with_an_expert_map(cuda_device):
+    """The largest problem the built-in array accepts (262 144 slots, 256 experts: 264 448 of its
+    265 220 bytes are used) and the expert-parallel form with an expert_map, both bit for bit
+    equal to the workspace entry point."""
+    lib = _lib.load()
+    dev = cuda_device
+    g = torch.Generator().manual_seed(5)
+    ids = torch.randint(0, 256, (32768, 8), generator=g, dtype=torch.int32).to(dev)
+    want = _align(lib, "xkb_moe_align_block_size", ids, 256, 16, dev, with_workspace=True)
+    got = _align(lib, "xkb_moe_align_block_size_static", ids, 256, 16, dev, with_workspace=False)
+    assert all(torch.equal(a, b) for a, b in zip(got, want))
+    # expert-parallel form: 64 global experts, this rank holds 16..31 as local 0..15
+    emap = torch.full((64,), -1, dtype=torch.int32)
+    emap[16:32] = torch.arange(16, dtype=torch.int32)
+    emap = emap.to(dev)
+    gids = torch.randint(0, 64, (4096, 4), generator=g, dtype=torch.int32).to(dev)
+    want = _align(lib, "xkb_moe_align_block_size", gids, 16, 32, dev, with_workspace=True, expert_map=emap)
+    got = _align(lib, "xkb_moe_align_block_size_static", gids, 16, 32, dev, with_workspace=False, expert_map=emap)
+    assert all(torch.equal(a, b) for a, b in zip(got, want))
+    assert int(got[2]) < gids.numel()      # most slots were not local and were dropped
 
 
 def test_static_scratch_entry_point_refuses_oversized_problems(cuda_device):

@@ -67,6 +67,7 @@ SIGNATURES = {
          c_int, c_int, c_void_p, c_int64, c_void_p],
     ),
     "xkb_workspace_status": (c_int, [c_void_p, c_void_p]),
+    "xkb_selftest_bounded_wait": (c_int, [c_void_p, c_int64, c_void_p]),
     "xkb_gemm_timer_enable": (c_int, [c_int]),
     "xkb_gemm_timer_read": (c_int, [c_void_p, c_int, c_void_p]),
 }

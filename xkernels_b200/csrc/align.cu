@@ -343,25 +343,27 @@ constexpr int kStaticMaxExperts = 256;        // num_experts limit
 constexpr int64_t kStaticChunks = kStaticMaxSlots / kChunk;
 constexpr int64_t kStaticInts = kStaticChunks * (kStaticMaxExperts + 1) + (kStaticMaxExperts + 1) + 256;
 
-// ~258 KiB per GPU that loads the library, held until the process exits.
+// 265 220 bytes (259 KiB) per GPU that loads the library, held until the process exits.
 static __device__ __align__(256) int32_t g_align_static_scratch[kStaticInts];
 
 constexpr int kMaxDevices = 64;
-void* g_static_ptr[kMaxDevices] = {nullptr};   // device address of the array, per device
+std::atomic<void*> g_static_ptr[kMaxDevices];   // device address of the array, per device (zero-initialised)
 
 // The array's name is only a host-side handle; the device address has to be asked for, once per
-// device, with that device current.
+// device, with that device current.  The address is looked up for the device that is CURRENT at
+// the call, so the stream passed in must belong to the current device (as for any launch).
+// Threads that race on a device's first call all store the same value.
 int static_scratch_address(void** out) {
   int dev = -1;
   XKB_CHECK_CUDA(cudaGetDevice(&dev));
   XKB_REQUIRE(dev >= 0 && dev < kMaxDevices, "moe_align (static): device index %d not supported", dev);
-  if (g_static_ptr[dev] == nullptr) {
-    void* p = nullptr;
+  void* p = g_static_ptr[dev].load(std::memory_order_acquire);
+  if (p == nullptr) {
     XKB_CHECK_CUDA(cudaGetSymbolAddress(&p, g_align_static_scratch));
     XKB_REQUIRE(p != nullptr, "moe_align (static): cudaGetSymbolAddress returned a null address");
-    g_static_ptr[dev] = p;
+    g_static_ptr[dev].store(p, std::memory_order_release);
   }
-  *out = g_static_ptr[dev];
+  *out = p;
   return XKB_OK;
 }
 

@@ -62,15 +62,32 @@ constexpr int kBStages16 = 9;          // token ring depth for token tiles of 16
 constexpr uint32_t kProdSleepNs = 400; // back-off of the TMA producers, which run a whole ring ahead
 constexpr uint32_t kIssSleepNs = 32;   // back-off of the MMA issuers (on the critical path: short)
 constexpr int kNarrowWGs = 4;          // dequantiser warpgroups for token tiles <= 64
+// Hand-off units per 256-K stage (1 = the whole stage, or one unit per warpgroup that shares the
+// stage): every unit has its own tensor-memory slot and its own full/empty barriers, so its MMAs
+// start as soon as its warpgroup has published it and its slot is free again as soon as they end.
+constexpr int kUnitsNarrow = 2;        // token tiles <= 64: two warpgroups share a stage
+constexpr int kUnitsWide = 4;          // token tiles of 128: four warpgroups share a stage
+// The dequantiser warps hand a weight stage back to the TMA producer as soon as they have read it
+// from shared memory into registers, before they convert it (one arrival per warp of the group):
+// the turn-round of a ring slot (TMA latency + wait for the readers + their wake-up) then does not
+// contain the conversion time.
+// MMA issuer warps run their loop with all 32 lanes (waits included) and only the tcgen05.mma /
+// commit / arrive instructions themselves are predicated on lane 0: the loop is then warp-uniform
+// and descriptors and tensor-memory addresses are computed in uniform registers, instead of being
+// moved there one by one for every MMA as in a loop that only lane 0 executes.
+constexpr bool kUniformIssuer = false;
 constexpr int kTmemCols = 512;     // one CTA per SM owns all of tensor memory
 constexpr int kPackedStageBytes = kTileRows * (kStageK / 2);  // 16 KiB
 constexpr int kScaleStageBytes = kTileRows * (kStageK / 32) * 2;  // 2 KiB
 
 // MATS = weight matrices that alternate 256-K stages inside one tile (MXFP4 gate/up, INT4 row-tile pairs)
 //
-// The hand-off between the dequantisers and the MMA issuers is one whole 256-K stage.  A finer
-// hand-off (64 K) was measured to be bound by the issuing thread's own loop (about 1000 cycles
-// per 64-K slice under the dequantisers' issue pressure) and not by the tensor pipe.
+// Why the hand-off unit matters: a tensor-memory slot is busy from the first converted column until
+// the commit of the MMAs that read it comes back, i.e. for (fill time + MMA issue time + barrier
+// round trips), and only 384-416 columns are left for slots beside the accumulators.  With whole
+// 256-K stages as units that is three slots, and the slot cycle, not any pipe, bounds the kernel.
+// Units of half a stage (one warpgroup's share) halve the MMA part of the cycle and let the other
+// half be converted meanwhile.
 constexpr int gcd_c(int a, int b) { return b == 0 ? a : gcd_c(b, a % b); }
 constexpr int lcm_c(int a, int b) { return a / gcd_c(a, b) * b; }
 
@@ -91,6 +108,11 @@ template <int BT, int MATS = 1, bool INT4 = true> struct TcCfg {
   static constexpr int kGroupWarps = kDequantWarps / kGroups;
   static constexpr int kPartsPerStage = kWGs / kGroups;      // warpgroups that share one stage
   static constexpr int kChunks = 8 / kPartsPerStage;         // 16-byte chunks (32 weights, one scale group) per thread and stage
+  static constexpr int kUnits = (BT <= 64) ? kUnitsNarrow : kUnitsWide;   // hand-off units per stage
+  static_assert(kUnits == 1 || kUnits == kPartsPerStage, "a unit is a whole stage or one warpgroup's share of it");
+  static constexpr int kUnitCols = kSlotCols / kUnits;       // tensor-memory columns of one unit
+  static constexpr int kUnitSubs = kSubs / kUnits;           // 64-K token sub-tiles one unit spans
+  static_assert(kSubs % kUnits == 0, "a unit must span whole 64-K sub-tiles");
   // Token ring.  A token stage is released by the commit of the MMAs that read it and re-filled by
   // TMA from L2 about a microsecond later; narrow tiles are small, so their ring is made deep
   // enough that the issuers never wait for tokens.
@@ -119,20 +141,29 @@ template <int BT, int MATS = 1, bool INT4 = true> struct TcCfg {
   static constexpr int kDBuf = (2 * kAccs * BT + 3 * kSlotCols <= kTmemCols) ? 2 : 1;
   static constexpr int kDCols = kDBuf * kAccs * BT;         // accumulator a of set d at (d * kAccs + a) * BT
   static constexpr int kACol0 = kDCols;                     // the A slots follow the accumulators
-  static constexpr int kASlotsFit = (kTmemCols - kDCols) / kSlotCols;
-  static constexpr int kASlots = kASlotsFit > 3 ? 3 : kASlotsFit;
-  static_assert(kASlots >= 2, "need two A slots so that conversion and MMA overlap");
+  // A slots, counted in units (three stages' worth at most)
+  static constexpr int kASlotsFit = (kTmemCols - kDCols) / kUnitCols;
+  static constexpr int kASlots = kASlotsFit > 3 * kUnits ? 3 * kUnits : kASlotsFit;
+  static_assert(kASlots >= 2 * kUnits, "need two stages of A slots so that conversion and MMA overlap");
   // mbarrier parity waits only tell "the phase with this parity is over", so a waiter must see every
-  // phase of a barrier it waits on.  Stage g is filled by group g % kGroups and consumed by issuer
-  // g % kIssuers; its barriers are therefore number g % kABars with kABars a common multiple of the
-  // slot count, kGroups and kIssuers (the slot itself is g % kASlots): every barrier then always
-  // has the same producer group and the same consumer, and both pass through all of its phases.
-  // The token ring does the same with kBBars (the producer thread visits every token stage).
-  static constexpr int kABars = lcm_c(lcm_c(kASlots, kGroups), kIssuers);
+  // phase of a barrier it waits on.  Unit u = g * kUnits + h (stage g, numbered across the tiles of
+  // the CTA; h = the warpgroup's share) is filled by one fixed warpgroup of group g % kGroups and
+  // consumed by issuer g % kIssuers; its barriers are number u % kABars with kABars a common
+  // multiple of the slot count and of the unit periods of the groups and of the issuers (the slot
+  // itself is u % kASlots): every barrier then always has the same producers and the same consumer,
+  // and both pass through all of its phases.  The token ring does the same with kBBars (the
+  // producer thread visits every token stage).
+  static constexpr int kABars = lcm_c(lcm_c(kASlots, kGroups * kUnits), kIssuers * kUnits);
   static constexpr int kBBars = lcm_c(kBStages, kIssuers);
+  // the running ring positions of the roles advance by one own stage at a time with a single
+  // conditional wrap, and the units of one stage never straddle a wrap
+  static_assert(kGroups * kUnits <= kASlots && kASlots % kUnits == 0 && kABars % kUnits == 0, "unit ring arithmetic");
+  static_assert(kIssuers % MATS == 0 && kIssuers / MATS <= kBStages, "token ring arithmetic");
+  static constexpr int kNumBars = 2 * kWStages + 2 * kBBars + 2 * kABars + 2 * kDBuf;
+  static constexpr size_t kBarBytes = ((size_t)kNumBars * 8 + 64 + 127) / 128 * 128;   // + allocation slot, abort word
   static constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + (size_t)kWStages * kPackedStageBytes +
                                        (size_t)kBStages * kBStageBytes + (size_t)kWStages * kScaleStageBytes +
-                                       1024 /*barriers*/;
+                                       kBarBytes;
   static_assert(kSmemBytes <= 227 * 1024, "shared memory overcommitted");
 };
 
@@ -176,6 +207,35 @@ __device__ __forceinline__ uint32_t dequant_pair(uint32_t biased, uint32_t scale
   const __nv_bfloat162 q = __hsub2(v, *reinterpret_cast<const __nv_bfloat162*>(&k136));
   const __nv_bfloat162 w = __hmul2(q, *reinterpret_cast<const __nv_bfloat162*>(&scale2));
   return *reinterpret_cast<const uint32_t*>(&w);
+}
+
+// ---- INT4 -> bf16 without a subtraction and with one shift per word --------------------------
+// A bf16 bit pattern whose sign and upper seven exponent bits are zero reads as  m * 2^-133  for
+// the 8-bit integer m in bits 7..0: the subnormals (exponent field 0) and the first binade
+// (exponent field 1, implicit one worth 2^-126 = 128 * 2^-133) continue each other.  So the two
+// low nibbles of each 16-bit half of a packed word are exact bf16 numbers in place, with no magic
+// number to subtract again:  x & 0x000F000F = (nib * 2^-133),  x & 0x00F000F0 = (nib * 2^-129),
+// and one shift by 8 brings the other two nibbles of each half down.  One fused multiply-add then
+// gives  nib * s - 8 * s = (nib - 8) * s  with the single rounding of the reference
+// (src/xkernels/ops/moe/w4a16.py:48-50): the product is exact inside the FMA and -8 * s is exact
+// as a bf16 number.  Everything is kept 2^-30 smaller than the true weights so that the
+// per-position multipliers s * 2^133 and s * 2^129 stay finite: multipliers s * 2^103 and
+// s * 2^99, addend -s * 2^-27, and the epilogue multiplies the fp32 accumulators by 2^30, which
+// is exact.  Exact for scales with 2^-96 <= |s| < 2^24 (and for s = 0); the host side refuses
+// scale tensors outside that range.
+constexpr bool kInt4NoSubtract = true;
+constexpr uint32_t kMulLo = 0x73007300u;    // 2^103, twice: multiplier for nibbles at bits 3..0
+constexpr uint32_t kMulHi = 0x71007100u;    // 2^99: nibbles at bits 7..4
+constexpr uint32_t kMulAdd = 0xB200B200u;   // -2^-27 = -8 * 2^-30
+constexpr float kInt4Unscale = 1073741824.f;  // 2^30
+__device__ __forceinline__ uint32_t bf2_mul(uint32_t a, uint32_t b) {
+  const __nv_bfloat162 r = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+__device__ __forceinline__ uint32_t bf2_fma(uint32_t a, uint32_t b, uint32_t c) {
+  const __nv_bfloat162 r = __hfma2(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b),
+                                   *reinterpret_cast<const __nv_bfloat162*>(&c));
+  return *reinterpret_cast<const uint32_t*>(&r);
 }
 
 // ---- MXFP4: E2M1 code -> bf16 -------------------------------------------------------------
@@ -241,9 +301,9 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
   Guard guard{abort_word, p.status};
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < kWStages; ++i) { mbar_init(&w_full[i], 1); mbar_init(&w_empty[i], 1); }
+    for (int i = 0; i < kWStages; ++i) { mbar_init(&w_full[i], 1); mbar_init(&w_empty[i], Cfg::kGroupWarps); }
     for (int i = 0; i < Cfg::kBBars; ++i) { mbar_init(&b_full[i], 1); mbar_init(&b_empty[i], kMatsC); }
-    for (int i = 0; i < Cfg::kABars; ++i) { mbar_init(&a_full[i], Cfg::kGroupWarps); mbar_init(&a_empty[i], 1); }
+    for (int i = 0; i < Cfg::kABars; ++i) { mbar_init(&a_full[i], Cfg::kGroupWarps / Cfg::kUnits); mbar_init(&a_empty[i], 1); }
     for (int i = 0; i < Cfg::kDBuf; ++i) { mbar_init(&d_full[i], Cfg::kIssuers); mbar_init(&d_empty[i], Cfg::kDequantWarps); }
     *abort_word = 0;
     mbar_fence_init();
@@ -331,47 +391,69 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
     // sixteen M=128 N=BT K=16 MMAs into its own accumulator of the stage's matrix and commits.
     constexpr int kIssuers = Cfg::kIssuers;
     const uint32_t me = warp - 1;
-    if (lane == 0 && me < (uint32_t)kIssuers) {
+    if ((kUniformIssuer || lane == 0) && me < (uint32_t)kIssuers) {
+      const uint32_t leader = (lane == 0) ? 1u : 0u;
+      // in the warp-uniform form every wait result is made uniform with a vote
+      auto uni = [&](bool v) -> bool { return kUniformIssuer ? (__all_sync(0xffffffffu, v) != 0) : v; };
       constexpr uint32_t idesc = umma_idesc_bf16(kTileRows, BT);
-      uint32_t it = 0, g0 = 0;                            // g0 = number of the tile's first stage
-      for (int64_t t = blockIdx.x; t < total_tiles && !guard.aborted(); t += gridDim.x, ++it, g0 += (uint32_t)v_stages) {
+      // This issuer's stages are g = me, me + kIssuers, ...; its ring positions advance with them
+      // (no division in the loop: the issuing thread is on the critical path of every hand-off).
+      constexpr uint32_t kDU = (uint32_t)(kIssuers * Cfg::kUnits);       // units per own-stage step
+      constexpr uint32_t kDTB = (uint32_t)(kIssuers / kMats);            // token stages per own-stage step
+      uint32_t aq0 = (me * Cfg::kUnits) % Cfg::kASlots;                  // A slot of the stage's first unit
+      uint32_t ab0 = (me * Cfg::kUnits) % Cfg::kABars, acyc = 0;         // its barrier and the barrier ring's lap parity
+      uint32_t bst = (me / kMats) % Cfg::kBStages;                       // token slot
+      uint32_t bbar = (me / kMats) % Cfg::kBBars, bcyc = 0;              // token barrier and lap parity
+      uint32_t it = 0, g0mod = 0;                                        // g0mod = (first stage of the tile) % kIssuers
+      const uint32_t vsmod = (uint32_t)v_stages % kIssuers;
+      for (int64_t t = blockIdx.x; t < total_tiles && uni(!guard.aborted()); t += gridDim.x, ++it) {
         // accumulator set of this tile; its previous user must have been read out by every epilogue warp
         const uint32_t dbuf = it % Cfg::kDBuf, duse = it / Cfg::kDBuf;
-        bool ok = mbar_wait(&d_empty[dbuf], (duse & 1u) ^ 1u, guard, 8, 100);
+        bool ok = uni(mbar_wait(&d_empty[dbuf], (duse & 1u) ^ 1u, guard, 8, 100));
         if (ok) tc_fence_after();
         uint32_t started = 0;   // bit m: this issuer has already written its accumulator of matrix m in this tile
-        for (int vs = (int)((me + kIssuers - g0 % kIssuers) % kIssuers); vs < v_stages && ok; vs += kIssuers) {
-          const uint32_t g = g0 + (uint32_t)vs;
+        for (int vs = (int)(me >= g0mod ? me - g0mod : me + kIssuers - g0mod); vs < v_stages && ok; vs += kIssuers) {
           const int mat = vs % kMats;                       // which matrix this stage belongs to
-          const uint32_t aq = g % Cfg::kASlots, abar = g % Cfg::kABars, aph = (g / Cfg::kABars) & 1u;
-          const uint32_t tb = g / kMats;                    // token stage read by stage g
-          const uint32_t bst = tb % Cfg::kBStages, bbar = tb % Cfg::kBBars, bph = (tb / Cfg::kBBars) & 1u;
-          ok = mbar_wait(&a_full[abar], aph, guard, 3, kIssSleepNs);
-          // every dequantiser warp of the stage's group has arrived, so all of them are done with the
-          // weight stage in shared memory: hand it back to the producer on their behalf
-          if (ok) mbar_arrive(&w_empty[g % kWStages]);
-          if (ok) ok = mbar_wait(&b_full[bbar], bph, guard, 4);
-          if (!ok) break;
-          tc_fence_after();
           const int acc = Cfg::kLocked ? mat : (int)me * kMats + mat;
           const uint32_t d_tmem = tmem_base + (uint32_t)(((int)dbuf * Cfg::kAccs + acc) * BT);
-          const uint32_t a_tmem = tmem_base + Cfg::kACol0 + aq * kSlotCols;
           const uint64_t b_desc = umma_desc_k_sw128(smem_u32(s_tokens + bst * Cfg::kBStageBytes));
           const bool fresh = ((started >> mat) & 1u) == 0;
           started |= 1u << mat;
 #pragma unroll
-          for (int sub = 0; sub < kSubs; ++sub) {
+          for (int h = 0; h < Cfg::kUnits; ++h) {
+            ok = uni(mbar_wait(&a_full[ab0 + h], acyc, guard, 3, kIssSleepNs));
+            if (!ok) break;
+            if (h == 0) {
+              ok = uni(mbar_wait(&b_full[bbar], bcyc, guard, 4));
+              if (!ok) break;
+            }
+            tc_fence_after();
+            const uint32_t a_tmem = tmem_base + Cfg::kACol0 + (aq0 + h) * Cfg::kUnitCols;
 #pragma unroll
-            for (int kk = 0; kk < kSubK / 16; ++kk)
-              umma_ts_bf16(d_tmem, a_tmem + sub * kSubCols + kk * 8,
-                           b_desc + (uint64_t)((sub * Cfg::kBSubBytes) >> 4) + (uint64_t)(kk * 2), idesc,
-                           (fresh && sub == 0 && kk == 0) ? 0u : 1u);
+            for (int us = 0; us < Cfg::kUnitSubs; ++us) {
+              const int sub = h * Cfg::kUnitSubs + us;
+#pragma unroll
+              for (int kk = 0; kk < kSubK / 16; ++kk)
+                umma_ts_bf16_if(d_tmem, a_tmem + us * kSubCols + kk * 8,
+                                b_desc + (uint64_t)((sub * Cfg::kBSubBytes) >> 4) + (uint64_t)(kk * 2), idesc,
+                                (fresh && sub == 0 && kk == 0) ? 0u : 1u, leader);
+            }
+            tc_commit_if(&a_empty[ab0 + h], leader);
           }
-          tc_commit(&a_empty[abar]);
-          tc_commit(&b_empty[bbar]);   // kMats arrivals release the token stage
+          if (!ok) break;
+          tc_commit_if(&b_empty[bbar], leader);   // kMats arrivals release the token stage
+          // on to this issuer's next stage
+          aq0 += kDU; if (aq0 >= (uint32_t)Cfg::kASlots) aq0 -= Cfg::kASlots;
+          if (kDU >= (uint32_t)Cfg::kASlots && aq0 >= (uint32_t)Cfg::kASlots) aq0 -= Cfg::kASlots;
+          ab0 += kDU; if (ab0 >= (uint32_t)Cfg::kABars) { ab0 -= Cfg::kABars; acyc ^= 1u; }
+          // a two-matrix tile shares a token stage between the matrices: with kIssuers == kMats every
+          // own stage is a new token stage; otherwise the step is kIssuers / kMats token stages
+          bst += kDTB; if (bst >= (uint32_t)Cfg::kBStages) bst -= Cfg::kBStages;
+          bbar += kDTB; if (bbar >= (uint32_t)Cfg::kBBars) { bbar -= Cfg::kBBars; bcyc ^= 1u; }
         }
         if (!ok) break;
-        tc_commit(&d_full[dbuf]);
+        tc_commit_if(&d_full[dbuf], leader);
+        g0mod += vsmod; if (g0mod >= (uint32_t)kIssuers) g0mod -= kIssuers;
       }
     }
   } else if (warp >= kCtrlWarps) {
@@ -467,6 +549,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
             const int32_t slot = __ldg(slots + c0 + j);  // same address for the whole warp
             if (slot < 0 || slot >= p.numel) continue;
             float v = __uint_as_float(acc[j]);
+            if (mode_is_int4(MODE) && kInt4NoSubtract) v *= kInt4Unscale;   // exact: a power of two
             if (MODE == kModeMxDown) {  // reference rounds `down` to bf16, adds the bf16 bias, then x w
               v = round_to_bf16(v);
               if (p.bias != nullptr) v = round_to_bf16(v + bias0);
@@ -477,6 +560,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
             p.scratch[(int64_t)slot * p.N + n_glob] = v;
             if (MODE == kModeInt4Pair) {  // the second weight tile: rows 128 further down
               float v2 = __uint_as_float(more[j]);
+              if (kInt4NoSubtract) v2 *= kInt4Unscale;
               if (p.mul_w) v2 = p.topk_w[slot] * v2;
               p.scratch[(int64_t)slot * p.N + n_glob + kTileRows] = v2;
             }
@@ -485,13 +569,13 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&d_empty[dbuf]);
+      mbar_arrive_if(&d_empty[dbuf], (lane == 0) ? 1u : 0u);
       return true;
     };
     bool pend = false;
     int pend_b = 0, pend_nt = 0;
     uint32_t pend_it = 0, pend_g0 = 0, it = 0, g0 = 0;      // g0 = number of the tile's first stage
-    // the stage this group converts after (t, vs, g0): two further on, or the first own stage of a later tile
+    // the stage this group converts after (t, vs, g0): kGroups further on, or the first own stage of a later tile
     auto next_own = [&](int64_t& t, int& vs, uint32_t& gbase) -> bool {
       vs += kGroups;
       while (vs >= v_stages) {
@@ -507,14 +591,22 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
       int64_t tn = blockIdx.x; int vn = (int)grp - kGroups; uint32_t gn = 0;
       if (tn < total_tiles && next_own(tn, vn, gn)) mx_next = mx_scale_load(tn, vn);
     }
+    // This group's stages are g = grp, grp + kGroups, ... whatever the tile boundaries, so its ring
+    // positions advance by a fixed step per converted stage (no division in the loop).
+    constexpr uint32_t kDU = (uint32_t)(kGroups * Cfg::kUnits);           // units per own-stage step
+    const uint32_t u_first = grp * Cfg::kUnits + (Cfg::kUnits > 1 ? (uint32_t)part : 0u);
+    uint32_t wst = grp % kWStages, wph = 0;                               // weight slot and its lap parity
+    uint32_t aq = u_first % Cfg::kASlots;                                 // A slot of this warpgroup's unit
+    uint32_t abar = u_first % Cfg::kABars, acyc = 0;                      // its barrier and the barrier ring's lap parity
+    uint32_t n_own = 0;                                                   // own stages converted so far
+    const uint32_t lead = (lane == 0) ? 1u : 0u;
+    uint32_t g0mod = 0;                                                   // g0 % kGroups
+    const uint32_t vsmod = (uint32_t)v_stages % kGroups;
     for (int64_t t = blockIdx.x; t < total_tiles; t += gridDim.x, ++it, g0 += (uint32_t)v_stages) {
       const int nt = (int)(t % n_tiles), b = (int)(t / n_tiles);
       bool ok = true;
       bool epi_due = pend;   // the previous tile's epilogue runs after this group's first stage of this tile
-      for (int vs = (int)((grp + kGroups - g0 % kGroups) % kGroups); vs < v_stages && ok; vs += kGroups) {
-        const uint32_t g = g0 + (uint32_t)vs;
-        const uint32_t wst = g % kWStages, wph = (g / kWStages) & 1u;
-        const uint32_t aq = g % Cfg::kASlots, abar = g % Cfg::kABars, aph = (g / Cfg::kABars) & 1u;
+      for (int vs = (int)(grp >= g0mod ? grp - g0mod : grp + kGroups - g0mod); vs < v_stages && ok; vs += kGroups) {
         if (!mbar_wait(&w_full[wst], wph, guard, 5)) { ok = false; break; }
         const uint32_t pk = s_packed_u32 + wst * kPackedStageBytes + row * 128;
         uint2 sw = make_uint2(0, 0);  // INT4: the kChunks bf16 group scales of this share; MXFP4: .x = its e8m0 bytes
@@ -530,29 +622,48 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
         uint4 w4[kChunks];
 #pragma unroll
         for (int c = 0; c < kChunks; ++c) w4[c] = lds128(pk + (((part * kChunks + c) ^ (row & 7)) << 4));
-        // (the stage is handed back to the producer by the MMA issuer once all warps of the group have
-        // published the converted slices, which they do after these loads)
-        // the slot's previous user was stage g - kASlots: wait until its MMAs have completed
-        if (g >= (uint32_t)Cfg::kASlots) {
-          const uint32_t gp = g - Cfg::kASlots;
-          if (!mbar_wait(&a_empty[gp % Cfg::kABars], (gp / Cfg::kABars) & 1u, guard, 6)) { ok = false; break; }
+        // This warp's share of the stage is in registers (the shared-memory unit executes a warp's
+        // loads and the arrive in order, and the arrive has release semantics): one arrival per warp
+        // of the group hands the stage back to the producer.
+        __syncwarp();
+        mbar_arrive_if(&w_empty[wst], lead);
+        // the slot's previous user was the unit kASlots before this one: wait until its MMAs have completed
+        if (n_own * kDU + u_first >= (uint32_t)Cfg::kASlots) {
+          const bool same_lap = abar >= (uint32_t)Cfg::kASlots;
+          const uint32_t eb = same_lap ? abar - Cfg::kASlots : abar + Cfg::kABars - Cfg::kASlots;
+          if (!mbar_wait(&a_empty[eb], same_lap ? acyc : (acyc ^ 1u), guard, 6)) { ok = false; break; }
         }
         tc_fence_after();
-        const uint32_t dst = tmem_base + lane_base + Cfg::kACol0 + aq * kSlotCols + part * (kChunks * 16);
+        const uint32_t dst = tmem_base + lane_base + Cfg::kACol0 + aq * Cfg::kUnitCols +
+                             (Cfg::kUnits > 1 ? 0 : part * (kChunks * 16));
 #pragma unroll
         for (int c = 0; c < kChunks; ++c) {
           const uint32_t words[4] = {w4[c].x, w4[c].y, w4[c].z, w4[c].w};
           if (mode_is_int4(MODE)) {
             const uint32_t s01 = (c < 2) ? sw.x : sw.y;
             const uint32_t s2 = (c & 1) ? __byte_perm(s01, s01, 0x3232) : __byte_perm(s01, s01, 0x1010);
+            if (kInt4NoSubtract) {
+              const uint32_t m_lo = bf2_mul(s2, kMulLo), m_hi = bf2_mul(s2, kMulHi), add = bf2_mul(s2, kMulAdd);
 #pragma unroll
-            for (int wp = 0; wp < 2; ++wp) {  // two words = 16 weights = 8 columns
-              const uint32_t x0 = words[2 * wp], x1 = words[2 * wp + 1];
-              tmem_st_32x8(dst + c * 16 + wp * 8,
-                           dequant_pair(nib_pair(x0), s2), dequant_pair(nib_pair(x0 >> 4), s2),
-                           dequant_pair(nib_pair(x0 >> 8), s2), dequant_pair(nib_pair(x0 >> 12), s2),
-                           dequant_pair(nib_pair(x1), s2), dequant_pair(nib_pair(x1 >> 4), s2),
-                           dequant_pair(nib_pair(x1 >> 8), s2), dequant_pair(nib_pair(x1 >> 12), s2));
+              for (int wp = 0; wp < 2; ++wp) {  // two words = 16 weights = 8 columns
+                const uint32_t x0 = words[2 * wp], x1 = words[2 * wp + 1];
+                const uint32_t y0 = x0 >> 8, y1 = x1 >> 8;
+                tmem_st_32x8(dst + c * 16 + wp * 8,
+                             bf2_fma(x0 & 0x000F000Fu, m_lo, add), bf2_fma(x0 & 0x00F000F0u, m_hi, add),
+                             bf2_fma(y0 & 0x000F000Fu, m_lo, add), bf2_fma(y0 & 0x00F000F0u, m_hi, add),
+                             bf2_fma(x1 & 0x000F000Fu, m_lo, add), bf2_fma(x1 & 0x00F000F0u, m_hi, add),
+                             bf2_fma(y1 & 0x000F000Fu, m_lo, add), bf2_fma(y1 & 0x00F000F0u, m_hi, add));
+              }
+            } else {
+#pragma unroll
+              for (int wp = 0; wp < 2; ++wp) {  // two words = 16 weights = 8 columns
+                const uint32_t x0 = words[2 * wp], x1 = words[2 * wp + 1];
+                tmem_st_32x8(dst + c * 16 + wp * 8,
+                             dequant_pair(nib_pair(x0), s2), dequant_pair(nib_pair(x0 >> 4), s2),
+                             dequant_pair(nib_pair(x0 >> 8), s2), dequant_pair(nib_pair(x0 >> 12), s2),
+                             dequant_pair(nib_pair(x1), s2), dequant_pair(nib_pair(x1 >> 4), s2),
+                             dequant_pair(nib_pair(x1 >> 8), s2), dequant_pair(nib_pair(x1 >> 12), s2));
+              }
             }
           } else {
             uint32_t c1, c2;
@@ -566,10 +677,14 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
             }
           }
         }
-        tmem_wait_st();
+        tmem_wait_st();          // warp-wide: every lane's stores have landed
         tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&a_full[abar]);
+        mbar_arrive_if(&a_full[abar], lead);
+        // on to this group's next stage
+        ++n_own;
+        wst += kGroups; if (wst >= (uint32_t)kWStages) { wst -= kWStages; wph ^= 1u; }
+        aq += kDU; if (aq >= (uint32_t)Cfg::kASlots) aq -= Cfg::kASlots;
+        abar += kDU; if (abar >= (uint32_t)Cfg::kABars) { abar -= Cfg::kABars; acyc ^= 1u; }
         if (epi_due) {
           epi_due = false;
           if (!run_epilogue(pend_b, pend_nt, pend_it % Cfg::kDBuf, pend_it / Cfg::kDBuf, pend_g0)) { ok = false; break; }
@@ -581,6 +696,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
       }
       // the epilogue is deferred: see run_epilogue
       pend = true; pend_b = b; pend_nt = nt; pend_it = it; pend_g0 = g0;
+      g0mod += vsmod; if (g0mod >= (uint32_t)kGroups) g0mod -= kGroups;
     }
     if (pend && !guard.aborted()) run_epilogue(pend_b, pend_nt, pend_it % Cfg::kDBuf, pend_it / Cfg::kDBuf, pend_g0);
   }

@@ -14,9 +14,15 @@ namespace tc {
 // Error codes a kernel writes to its status word when a bounded wait runs out.
 constexpr int kErrWaitTimeout = 1;
 
-// Poll budget of one wait.  A probe parks the thread for up to its time hint (2 us by default),
-// so this bounds a wait to about a second; a healthy pipeline needs a handful of probes.
-constexpr uint32_t kMaxPolls = 1u << 19;
+// Time budget of one wait.  A healthy pipeline completes every wait within microseconds; a wait
+// that lasts this long means a lost arrival, and the kernel gives up instead of hanging the GPU.
+constexpr uint64_t kWaitBudgetNs = 1000000000ull;   // one second
+
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -36,17 +42,18 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                : "memory");
 }
-// One probe of the barrier phase.  `hint_ns` lets the hardware park the thread for up to that
-// long while the phase is incomplete (it is woken when the phase completes), so that waiting
-// roles do not burn the issue slots the dequantiser warps need.
-__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+// One probe of the barrier phase.  try_wait may park the thread for a hardware-defined time while
+// the phase is incomplete (it is woken when the phase completes), so waiting roles burn fewer of
+// the issue slots the dequantiser warps need than with test_wait.  (An explicit suspend-time hint
+// measured 1 % slower than none.)
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+      : "r"(smem_u32(bar)), "r"(parity)
       : "memory");
   return ok != 0;
 }
@@ -62,22 +69,34 @@ struct Guard {
   }
 };
 
-// Bounded wait: returns false (after recording the failure) if the barrier has
-// not completed the phase within the poll budget or another role aborted.
-// `sleep_ns` > 0 backs off between probes: roles that run ahead of the pipeline
-// (the TMA producers) and roles that wait on the slower side (the MMA issuers)
-// would otherwise spend issue slots on probes that the dequantiser warps need.
-constexpr uint32_t kTryHintNs = 1000;
+// Bounded wait: returns false (after recording the failure) if the barrier has not completed the
+// phase within `budget_ns` of wall-clock time (read from %globaltimer every 64 probes) or another
+// role aborted.  `sleep_ns` > 0 backs off between probes: roles that run ahead of the pipeline
+// (the TMA producers) and roles that wait on the slower side (the MMA issuers) would otherwise
+// spend issue slots on probes that the dequantiser warps need.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Guard& g, int where,
-                                          uint32_t sleep_ns = 0) {
-  if (mbar_try(bar, parity, kTryHintNs)) return true;   // the common case: already complete
-  for (uint32_t i = 0; i < kMaxPolls; ++i) {
+                                          uint32_t sleep_ns = 0, uint64_t budget_ns = kWaitBudgetNs) {
+  if (mbar_try(bar, parity)) return true;   // the common case: already complete
+  uint64_t t0 = 0;
+  for (uint32_t i = 1;; ++i) {
     if (sleep_ns) __nanosleep(sleep_ns);
-    if (mbar_try(bar, parity, kTryHintNs)) return true;
-    if ((i & 63u) == 63u && g.aborted()) return false;
+    if (mbar_try(bar, parity)) return true;
+    if ((i & 63u) == 0u) {
+      if (g.aborted()) return false;
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > budget_ns) break;
+    }
   }
   g.raise(kErrWaitTimeout + (where << 8));
   return false;
+}
+
+// Variants for warp-uniform code: every lane of the warp executes the call with the same operands
+// and `leader` (non-zero in exactly one lane) selects the lane whose instruction takes effect.
+__device__ __forceinline__ void mbar_arrive_if(uint64_t* bar, uint32_t leader) {
+  asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %1, 0;\n\t@q mbarrier.arrive.shared::cta.b64 _, [%0];\n\t}"
+               ::"r"(smem_u32(bar)), "r"(leader) : "memory");
 }
 
 // ---- shared-memory loads by 32-bit shared address (keeps the loads in the shared state space) ----
@@ -132,6 +151,13 @@ __device__ __forceinline__ void tc_commit(uint64_t* bar) {
                : "memory");
 }
 
+__device__ __forceinline__ void tc_commit_if(uint64_t* bar, uint32_t leader) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %1, 0;\n\t"
+      "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+      ::"r"(smem_u32(bar)), "r"(leader) : "memory");
+}
+
 // 32 lanes x 8 columns store (registers r[0..7] of each thread).
 __device__ __forceinline__ void tmem_st_32x8(uint32_t taddr, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3,
                                              uint32_t r4, uint32_t r5, uint32_t r6, uint32_t r7) {
@@ -178,6 +204,18 @@ __device__ __forceinline__ void umma_ts_bf16(uint32_t d_tmem, uint32_t a_tmem, u
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// The same, executed by a whole warp with identical operands; only the lane with `leader` != 0 issues.
+__device__ __forceinline__ void umma_ts_bf16_if(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                                uint32_t accumulate, uint32_t leader) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.ne.b32 q, %5, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(leader)
       : "memory");
 }
 

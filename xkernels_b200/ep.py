@@ -5,8 +5,9 @@ One process per GPU; every rank owns ``E/W`` experts and its own batch of tokens
   1. plan: one (token, destination rank) PAIR for every rank that owns at least one of the token's
      top-k experts, grouped by (token chunk, destination), stable inside a group.  A token whose
      experts share a rank crosses the wire once, not once per expert;
-  2. exchange the pair-count matrix (one small all-to-all, one host read; counts are validated
-     on the host before any payload moves);
+  2. all-gather the pair-count matrices (one small collective, one host read); every rank checks
+     the whole matrix, so a refusal (invalid expert id, receive capacity exceeded, inconsistent
+     counts) is raised by all ranks together before any payload moves;
   3. per chunk: dispatch all-to-all of the pairs' activation rows and of their routing (local expert
      ids padded with -1, routing weights), local grouped GEMM over the received rows and a weighted
      fp32 sum over each pair's experts, all-to-all of ONE fp32 partial row per pair back to the
@@ -130,27 +131,56 @@ def plan_dispatch(topk_ids: torch.Tensor, experts_per_rank: int, world: int, pla
     return plan.trim() if host_checks else plan
 
 
-def exchange_counts(send_counts: torch.Tensor, group, extra: torch.Tensor | None = None):
-    """All-to-all of the [chunks, W] pair-count matrix.  Returns (send, recv) as nested Python lists
-    indexed [chunk][peer] and validates them.  ``extra`` (a 0-d device tensor) rides along on the
-    one host read and is returned as a third value."""
+class ExchangeRefused(RuntimeError):
+    """The count exchange found a reason not to move any payload.  Raised by EVERY rank of the
+    group with the same message, so that no rank is left waiting in a collective the others skip."""
+
+
+def exchange_counts(send_counts: torch.Tensor, group, n_bad: torch.Tensor | None = None,
+                    capacity: int | None = None, n_slots: int | None = None):
+    """All-gather of every rank's [chunks, W] pair-count matrix, its count of invalid expert ids and
+    its receive capacity: one collective, one host read.  Returns ``(send, recv)`` as nested Python
+    lists indexed [chunk][peer].
+
+    Every rank sees the whole W x W matrix, so every rank reaches the SAME verdict before any
+    payload moves: an invalid expert id anywhere raises ``ValueError`` everywhere; a negative
+    count, a rank that claims more pairs than it has slots, or a rank whose receive capacity would
+    be exceeded raises :class:`ExchangeRefused` everywhere.  (What a rank receives is by
+    construction what the others send it: both are read from the one gathered matrix.)"""
     world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
     chunks = send_counts.shape[0]
-    send_t = send_counts.t().contiguous()            # [W, chunks]: row p goes to peer p
-    recv_t = torch.empty_like(send_t)
-    dist.all_to_all_single(recv_t, send_t, group=group)
-    parts = [send_t.reshape(-1), recv_t.reshape(-1)]
-    if extra is not None:
-        parts.append(extra.reshape(1).to(send_t.dtype))
-    flat_host = torch.cat(parts).cpu().tolist()
-    n = world * chunks
-    send_l = [[flat_host[p * chunks + c] for p in range(world)] for c in range(chunks)]
-    recv_l = [[flat_host[n + p * chunks + c] for p in range(world)] for c in range(chunks)]
-    flat = [v for row in send_l + recv_l for v in row]
-    if flat and min(flat) < 0:
-        raise RuntimeError(f"expert-parallel count exchange returned invalid counts: {send_l} / {recv_l}")
-    if extra is not None:
-        return send_l, recv_l, flat_host[2 * n]
+    dev = send_counts.device
+    tail = torch.stack([
+        (torch.zeros((), dtype=torch.int64, device=dev) if n_bad is None else n_bad.reshape(()).to(torch.int64)),
+        torch.tensor(-1 if capacity is None else int(capacity), dtype=torch.int64, device=dev),
+        torch.tensor(-1 if n_slots is None else int(n_slots), dtype=torch.int64, device=dev)])
+    mine = torch.cat([send_counts.to(torch.int64).reshape(-1), tail])          # [chunks * W + 3]
+    everyone = torch.empty((world * mine.numel(),), dtype=torch.int64, device=dev)
+    dist.all_gather_into_tensor(everyone, mine.contiguous(), group=group)
+    host = everyone.view(world, mine.numel()).cpu().tolist()                    # the one host read
+    n = chunks * world
+    # matrix[src][chunk][dst]
+    matrix = [[row[c * world:(c + 1) * world] for c in range(chunks)] for row in host]
+    bad_ids = [int(row[n]) for row in host]
+    caps = [int(row[n + 1]) for row in host]
+    slots = [int(row[n + 2]) for row in host]
+    if any(bad_ids):
+        who = [r for r, b in enumerate(bad_ids) if b]
+        raise ValueError(f"expert id outside [0, num_global_experts) on rank(s) {who}")
+    for src in range(world):
+        flat = [v for c in range(chunks) for v in matrix[src][c]]
+        if min(flat, default=0) < 0:
+            raise ExchangeRefused(f"expert-parallel count exchange: rank {src} reported a negative count {matrix[src]}")
+        if slots[src] >= 0 and sum(flat) > slots[src]:
+            raise ExchangeRefused(f"expert-parallel count exchange: rank {src} reported {sum(flat)} pairs "
+                                  f"for {slots[src]} slots")
+    for dst in range(world):
+        n_in = sum(matrix[src][c][dst] for src in range(world) for c in range(chunks))
+        if caps[dst] >= 0 and n_in > caps[dst]:
+            raise ExchangeRefused(f"rank {dst} would receive {n_in} rows, capacity {caps[dst]}")
+    send_l = matrix[rank]
+    recv_l = [[matrix[src][c][rank] for src in range(world)] for c in range(chunks)]
     return send_l, recv_l
 
 
@@ -222,12 +252,14 @@ class ExpertParallelInt4:
 
             pair_token, _dest, routing, pair_of, counts, info = ops.ep_plan(
                 topk_ids, topk_w, self.e_local, self.world, self.placement, chunks)
-            send_l, recv_l, n_bad = exchange_counts(counts, self.group, extra=info[1])
+            send_l, recv_l = exchange_counts(counts, self.group, n_bad=info[1], capacity=self.max_recv_rows,
+                                             n_slots=M * top_k)
             P = sum(sum(r) for r in send_l)
             pair_token, send_R = pair_token[:P], routing[:P]
         else:
             plan = plan_dispatch(topk_ids, self.e_local, self.world, self.placement, chunks, host_checks=False)
-            send_l, recv_l, n_bad = exchange_counts(plan.send_counts, self.group, extra=plan.n_bad)
+            send_l, recv_l = exchange_counts(plan.send_counts, self.group, n_bad=plan.n_bad,
+                                             capacity=self.max_recv_rows, n_slots=M * top_k)
             P = sum(sum(r) for r in send_l)
             plan.trim(P)
             pair_token, pair_of = plan.pair_token, plan.pair_of
@@ -235,11 +267,7 @@ class ExpertParallelInt4:
             w_pairs = torch.where(plan.pair_ids >= 0, topk_w.to(torch.float32)[pair_token],
                                   torch.zeros((), dtype=torch.float32, device=A.device))
             send_R = torch.cat([plan.pair_ids, w_pairs.view(torch.int32)], dim=1).contiguous()
-        if n_bad:
-            raise ValueError("expert id outside [0, num_global_experts)")
         n_recv = sum(sum(r) for r in recv_l)
-        if self.max_recv_rows is not None and n_recv > self.max_recv_rows:
-            raise RuntimeError(f"rank {self.rank} would receive {n_recv} rows, capacity {self.max_recv_rows}")
         self.last_recv_rows = n_recv
         self.last_send_counts = [sum(send_l[c][p] for c in range(chunks)) for p in range(self.world)]
 
