@@ -150,6 +150,20 @@ def gen_mxfp4():
     save_case("mxfp4_scales", {**kw, "swiglu_limit": 0.0, "out": out})
 
 
+def gen_mxfp4_tensor_core_shape():
+    """A case whose dimensions are multiples of 512 (what the tcgen05 path of this repo takes: a row's
+    e8m0 scales must be whole 16-byte TMA rows), with bias, the clamp, and the edge scale codes."""
+    cfg = synth.Mxfp4Config("x", M=20, hidden=512, ispp=512, E=4, top_k=2, scale_lo=118, scale_hi=131)
+    kw = synth.make_mxfp4(cfg, seed=SEED + 40, with_bias=True)
+    kw["w13_scale"][0, 0, 0] = 0xFF
+    kw["w13_scale"][1, 700, 9] = 0xFF
+    kw["w2_scale"][1, 3, 1] = 0xFF
+    kw["w13_scale"][2, 5, 2] = 0
+    kw["w2_scale"][3, 130, 15] = 0
+    out = moe_mxfp4_ref(**kw, swiglu_limit=10.0)
+    save_case("mxfp4_tc_scales", {**kw, "swiglu_limit": 10.0, "out": out})
+
+
 # ---- moe_sum_reduce ---------------------------------------------------------------
 def gen_sum_reduce():
     for i, pt in enumerate(sweep_points("moe_sum_reduce")):
@@ -197,9 +211,14 @@ if __name__ == "__main__":
         gen_topk_softmax()
         print("wrote the topk_softmax cases")
         sys.exit(0)
+    if "--only-mxfp4-tc" in sys.argv:          # add the 512-multiple MXFP4 case without touching the others
+        gen_mxfp4_tensor_core_shape()
+        print("wrote mxfp4_tc_scales")
+        sys.exit(0)
     gen_align()
     gen_int4()
     gen_mxfp4()
+    gen_mxfp4_tensor_core_shape()
     gen_sum_reduce()
     gen_topk_softmax()
     (GOLDEN_DIR / "manifest.json").write_text(json.dumps(manifest, indent=1, sort_keys=True))

@@ -43,7 +43,7 @@ def test_int4_call_replays_on_new_inputs(cuda_device):
 
 
 def test_router_plus_mxfp4_call_replays(cuda_device):
-    cfg = synth.Mxfp4Config("g", M=24, hidden=512, ispp=256, E=8, top_k=2, scale_lo=119, scale_hi=124)
+    cfg = synth.Mxfp4Config("g", M=24, hidden=512, ispp=512, E=8, top_k=2, scale_lo=119, scale_hi=124)
     d = synth.make_mxfp4(cfg, seed=3, device=cuda_device)
     logits = torch.randn(cfg.M, cfg.E, device=cuda_device).to(torch.bfloat16)
     A = d["A"].clone()

@@ -26,7 +26,7 @@ def call(c, dev, **kw):
 
 
 @pytest.mark.parametrize("name", ["mxfp4_small", "mxfp4_small_bias", "mxfp4_mid", "mxfp4_fp32_act",
-                                  "mxfp4_scales"])
+                                  "mxfp4_scales", "mxfp4_tc_scales"])
 @pytest.mark.parametrize("path", ["auto", "simt"])
 def test_golden(name, path, cuda_device):
     c = load_case(name)
@@ -37,8 +37,10 @@ def test_golden(name, path, cuda_device):
 @pytest.mark.parametrize("M,hidden,ispp,E,top_k,bias", [
     (1, 64, 32, 4, 2, False), (37, 96, 64, 8, 3, True), (16, 256, 128, 5, 4, False),
     (48, 512, 256, 16, 6, True),
-    (640, 512, 256, 4, 2, True),      # more than 48 slots per expert: the 128-token tiles
-    (300, 256, 512, 3, 2, False),     # ragged last blocks in the wide mode
+    (48, 512, 512, 16, 6, True),      # multiples of 512: the tcgen05 kernels, 16-token tiles
+    (40, 1024, 512, 8, 4, False),     # four 256-K stages in gate_up, two in down
+    (640, 512, 512, 4, 2, True),      # more than 48 slots per expert: the 128-token tiles
+    (300, 512, 1024, 3, 2, False),    # ragged last blocks in the wide mode
 ])
 def test_against_oracle_with_repeated_ids(M, hidden, ispp, E, top_k, bias, cuda_device):
     g = torch.Generator().manual_seed(M + hidden)
@@ -90,7 +92,7 @@ def test_slots_without_a_local_expert_are_dropped(path, with_map, cuda_device):
     must not add the never-written rows of those slots (workspace poisoned beforehand)."""
     from xkernels_b200 import ops
 
-    cfg = synth.Mxfp4Config("drop", M=24, hidden=256, ispp=256, E=6, top_k=3, scale_lo=119, scale_hi=124)
+    cfg = synth.Mxfp4Config("drop", M=24, hidden=512, ispp=512, E=6, top_k=3, scale_lo=119, scale_hi=124)
     c = synth.make_mxfp4(cfg, seed=5)
     g = torch.Generator().manual_seed(4)
     ids = c["topk_ids"].clone()

@@ -113,7 +113,7 @@ def test_int4_no_routed_weight_and_ep_partials():
     assert oracle.count_violations(total, c["out"].float(), 2e-2, 2e-2) == 0
 
 
-MXFP4_CASES = ["mxfp4_small", "mxfp4_small_bias", "mxfp4_mid", "mxfp4_fp32_act", "mxfp4_scales"]
+MXFP4_CASES = ["mxfp4_small", "mxfp4_small_bias", "mxfp4_mid", "mxfp4_fp32_act", "mxfp4_scales", "mxfp4_tc_scales"]
 
 
 @pytest.mark.parametrize("name", MXFP4_CASES)

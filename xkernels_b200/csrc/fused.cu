@@ -249,7 +249,7 @@ extern "C" int xkb_fused_moe_mxfp4(const void* A, int a_dtype, const uint8_t* w1
   if (path == XKB_PATH_TC && !tc_fit)
     return fail(XKB_ERR_ARG,
                 "fused_moe_mxfp4: shape not supported by the tcgen05 path (needs bf16 A, "
-                "hidden %% 256 == 0, ispp %% 256 == 0)");
+                "hidden %% 512 == 0, ispp %% 512 == 0)");
   const bool use_tc = (path == XKB_PATH_TC) || (path == XKB_PATH_AUTO && tc_fit);
   const int block = use_tc ? mxfp4_tc_block(numel, E) : kSimtBlock;
 
@@ -275,6 +275,9 @@ extern "C" int xkb_workspace_status(const void* workspace, void* stream_) {
   int host = 0;
   XKB_CHECK_CUDA(cudaMemcpyAsync(&host, workspace, sizeof(int), cudaMemcpyDeviceToHost, stream));
   XKB_CHECK_CUDA(cudaStreamSynchronize(stream));
+  if (host == 2)
+    return fail(XKB_ERR_DEVICE, "an MXFP4 scale byte in 191..254 (weights of 2^64 and more) is outside the range "
+                                "the tcgen05 dequantiser converts: status 0x2");
   if (host != 0)
     return fail(XKB_ERR_DEVICE, "a kernel gave up a bounded wait: status 0x%x (wait site %d)", host, host >> 8);
   return XKB_OK;

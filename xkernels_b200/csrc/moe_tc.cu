@@ -8,8 +8,9 @@
 // twenty or twenty-one warps, everything handed over in whole 256-K stages:
 //
 //   warp 0   TMA producer, weights: packed tile [128 rows x 128 B] (128B swizzle, so that one
-//            row per thread reads conflict-free) + bf16 scale tile [128 x 8] per stage (MXFP4
-//            scales are read from global memory by the dequantisers).
+//            row per thread reads conflict-free) + scale tile per stage: bf16 [128 x 8] for INT4,
+//            e8m0 bytes [128 x 16] for MXFP4 (sixteen bytes are the smallest TMA row, so a tile
+//            carries the scales of two stages and each stage uses its half).
 //   then     two or three MMA issuer warps (lane 0 each; warp 1 also allocates and frees tensor
 //            memory): tcgen05.mma kind::f16, A from tensor memory, B from shared
 //            memory, fp32 accumulators in tensor memory.  They take whole stages in
@@ -67,6 +68,10 @@ constexpr int kNarrowWGs = 4;          // dequantiser warpgroups for token tiles
 // start as soon as its warpgroup has published it and its slot is free again as soon as they end.
 constexpr int kUnitsNarrow = 2;        // token tiles <= 64: two warpgroups share a stage
 constexpr int kUnitsWide = 4;          // token tiles of 128: four warpgroups share a stage
+// A tile's accumulators are read out by the dequantiser warps after they have converted this many
+// further stages of their own: the last MMAs of the tile (about one conversion time of issue and
+// commit latency behind the conversion) have then long completed and the read-out never waits.
+constexpr int kEpiDelay = 2;
 // The dequantiser warps hand a weight stage back to the TMA producer as soon as they have read it
 // from shared memory into registers, before they convert it (one arrival per warp of the group):
 // the turn-round of a ring slot (TMA latency + wait for the readers + their wake-up) then does not
@@ -99,6 +104,12 @@ template <int BT, int MATS = 1, bool INT4 = true> struct TcCfg {
   // dequantiser warpgroups (the four warps of one cover the four tensor-memory lane quarters)
   static constexpr int kWGs = (BT <= 64) ? kNarrowWGs : 4;
   static constexpr int kDequantWarps = 4 * kWGs;
+  // Read-out of a tile's accumulators: one task per 16 token columns.  A tile with fewer tasks than
+  // warpgroups (token tiles of 16 and 32) is read out by kEpiWGs warpgroups only, and the duty
+  // rotates from tile to tile, so that no warpgroup carries the read-out of every tile on top of
+  // its share of the conversion.
+  static constexpr int kColGroups = BT / 16;
+  static constexpr int kEpiWGs = kColGroups < kWGs ? kColGroups : kWGs;
   // Control warps: weight producer, the issuers, token producer.  Narrow INT4 tiles run three
   // issuers (five control warps; 21 warps get 80 registers each, enough for the INT4 dequantiser);
   // the others two issuers (four control warps, 96 registers, which the E2M1 dequantiser needs).
@@ -136,9 +147,11 @@ template <int BT, int MATS = 1, bool INT4 = true> struct TcCfg {
   // of MATS stages), so one accumulator per matrix is enough.
   static constexpr bool kLocked = (kIssuers == MATS);
   static constexpr int kAccs = kLocked ? MATS : kIssuers * MATS;   // accumulator (issuer j, matrix m) = j * MATS + m
-  // Two accumulator sets when tensor memory has room: the MMAs of the next tile start while the
-  // previous tile's accumulators are still being read out.
-  static constexpr int kDBuf = (2 * kAccs * BT + 3 * kSlotCols <= kTmemCols) ? 2 : 1;
+  // Two or three accumulator sets when tensor memory has room beside three stages of A slots: the
+  // MMAs of the next tiles start while an earlier tile's accumulators still wait to be read out.
+  // (Three sets let the read-out trail two tiles behind, which short tiles need: see kEpiDelay.)
+  static constexpr int kDBuf = (3 * kAccs * BT + 3 * kSlotCols <= kTmemCols) ? 3
+                               : (2 * kAccs * BT + 3 * kSlotCols <= kTmemCols) ? 2 : 1;
   static constexpr int kDCols = kDBuf * kAccs * BT;         // accumulator a of set d at (d * kAccs + a) * BT
   static constexpr int kACol0 = kDCols;                     // the A slots follow the accumulators
   // A slots, counted in units (three stages' worth at most)
@@ -188,7 +201,6 @@ struct TcParams {
   int N, K;                     // tile rows are taken from N rows per expert; K = contraction length
   int mul_w;
   // MXFP4 only
-  const uint8_t* mx_scale;      // e8m0 scales of the streamed matrix, [E, rows_per_expert, K/32]
   const __nv_bfloat16* bias;    // b13 [E, 2*ispp] or b2 [E, hidden] or nullptr
   __nv_bfloat16* act;           // gate_up mode output: [positions, N] bf16 in the K-permuted order
   int rows_per_expert;          // 2*ispp (gate_up) or hidden (down)
@@ -240,34 +252,37 @@ __device__ __forceinline__ uint32_t bf2_fma(uint32_t a, uint32_t b, uint32_t c) 
 
 // ---- MXFP4: E2M1 code -> bf16 -------------------------------------------------------------
 // The three magnitude bits (e1 e0 m) placed at bf16 bits 8..6 read as  e2m1 * 2^-126  (the code
-// 0b001 = 0.5 lands on the bf16 subnormal 2^-127), the sign bit goes to bit 15.  Multiplying by
-// 2^(s-1) = 2^126 * 2^(s-127) then gives e2m1 * 2^(s-127) exactly; the power of two is split in
-// two bf16 factors so that every e8m0 byte, 0 and 254 included, stays in range (0xFF -> 0).
-__device__ __forceinline__ void mx_scale_factors(uint32_t s, uint32_t& c1, uint32_t& c2) {
-  const int e = (int)s - 1;
-  const int e1 = e >> 1, e2 = e - e1;
-  uint32_t b1 = (uint32_t)(e1 + 127) << 7;
-  const uint32_t b2 = (uint32_t)(e2 + 127) << 7;
-  if (s == 0xFFu) b1 = 0;
-  c1 = b1 | (b1 << 16);
-  c2 = b2 | (b2 << 16);
+// 0b001 = 0.5 lands on the bf16 subnormal 2^-127), the sign bit goes to bit 15.  One bf16 multiply
+// by a power of two then gives the weight exactly.  The true factor 2^126 * 2^(s-127) does not fit
+// bf16 for s > 128, so all weights are kept 2^-62 smaller than they are: the factor is 2^(s-63),
+// a bf16 number for every e8m0 byte up to 190, and the epilogue multiplies the fp32 accumulators
+// by 2^62, which is exact.  s = 0xFF decodes to 0 like in the reference
+// (src/xkernels/ops/gather/mxfp4.py:60-66).  Exact for 57 <= s <= 190 (weights of magnitude
+// 2^-70 ... 2^63 and above 2^-134 after scaling); smaller scales land on bf16 subnormals and lose
+// bits far below anything an output can show; a scale byte in 191..254 (weights of 2^64 and
+// more) is reported through the status word instead of being converted.
+constexpr int kMxShift = 62;
+constexpr float kMxUnscale = 4611686018427387904.f;   // 2^62
+constexpr uint32_t kMxMaxScale = 190;
+constexpr int kErrMxScaleRange = 2;                  // status code: an e8m0 scale byte in 191..254
+__device__ __forceinline__ uint32_t mx_scale_factor(uint32_t s) {
+  // exponent field of 2^(s - 1 - kMxShift), twice; 0 for the NaN code
+  const uint32_t f = (s + (uint32_t)(126 - kMxShift)) * 0x00800080u;
+  return s == 0xFFu ? 0u : f;
 }
-__device__ __forceinline__ uint32_t mx_pair(uint32_t mag_shifted, uint32_t sign_shifted, uint32_t c1, uint32_t c2) {
+__device__ __forceinline__ uint32_t mx_pair(uint32_t mag_shifted, uint32_t sign_shifted, uint32_t c) {
   uint32_t t;
   asm("lop3.b32 %0, %1, 0x01C001C0, 0, 0xC0;" : "=r"(t) : "r"(mag_shifted));            // a & b
   asm("lop3.b32 %0, %0, %1, 0x80008000, 0xF8;" : "+r"(t) : "r"(sign_shifted));           // a | (b & c)
-  const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(&t);
-  const __nv_bfloat162 w = __hmul2(__hmul2(v, *reinterpret_cast<const __nv_bfloat162*>(&c1)),
-                                   *reinterpret_cast<const __nv_bfloat162*>(&c2));
-  return *reinterpret_cast<const uint32_t*>(&w);
+  return bf2_mul(t, c);
 }
 // One packed word (8 codes) -> 4 registers in the nibble order (0,4),(1,5),(2,6),(3,7).
-__device__ __forceinline__ void mx_word(uint32_t x, uint32_t c1, uint32_t c2, uint32_t& r0, uint32_t& r1,
-                                        uint32_t& r2, uint32_t& r3) {
-  r0 = mx_pair(x << 6, x << 12, c1, c2);
-  r1 = mx_pair(x << 2, x << 8, c1, c2);
-  r2 = mx_pair(x >> 2, x << 4, c1, c2);
-  r3 = mx_pair(x >> 6, x, c1, c2);
+__device__ __forceinline__ void mx_word(uint32_t x, uint32_t c, uint32_t& r0, uint32_t& r1, uint32_t& r2,
+                                        uint32_t& r3) {
+  r0 = mx_pair(x << 6, x << 12, c);
+  r1 = mx_pair(x << 2, x << 8, c);
+  r2 = mx_pair(x >> 2, x << 4, c);
+  r3 = mx_pair(x >> 6, x, c);
 }
 
 template <int BT, int MODE>
@@ -304,7 +319,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
     for (int i = 0; i < kWStages; ++i) { mbar_init(&w_full[i], 1); mbar_init(&w_empty[i], Cfg::kGroupWarps); }
     for (int i = 0; i < Cfg::kBBars; ++i) { mbar_init(&b_full[i], 1); mbar_init(&b_empty[i], kMatsC); }
     for (int i = 0; i < Cfg::kABars; ++i) { mbar_init(&a_full[i], Cfg::kGroupWarps / Cfg::kUnits); mbar_init(&a_empty[i], 1); }
-    for (int i = 0; i < Cfg::kDBuf; ++i) { mbar_init(&d_full[i], Cfg::kIssuers); mbar_init(&d_empty[i], Cfg::kDequantWarps); }
+    for (int i = 0; i < Cfg::kDBuf; ++i) { mbar_init(&d_full[i], Cfg::kIssuers); mbar_init(&d_empty[i], 4 * Cfg::kEpiWGs); }
     *abort_word = 0;
     mbar_fence_init();
   }
@@ -313,7 +328,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
   constexpr int kCtrlWarps = Cfg::kCtrlWarps;
   constexpr int kTokWarp = kCtrlWarps - 1, kTokLane = 0;   // a warp of its own: two polling threads in one warp slow each other down
   if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
-  if (warp == 0 && lane == 0) { prefetch_tensormap(&tm_packed); if (mode_is_int4(MODE)) prefetch_tensormap(&tm_scale); }
+  if (warp == 0 && lane == 0) { prefetch_tensormap(&tm_packed); prefetch_tensormap(&tm_scale); }
   if (warp == kTokWarp && lane == kTokLane) prefetch_tensormap(&tm_tokens);
   tc_fence_before();
   __syncthreads();
@@ -324,7 +339,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
   // together share the token block and walk through one expert's weights
   const int n_tiles = p.N / (MODE == kModeInt4Pair ? 2 * kTileRows : kTileRows);
   const int n_blocks = p.num_post[0] / BT;
-  const int64_t total_tiles = (int64_t)n_blocks * n_tiles;
+  const int total_tiles = n_blocks * n_tiles;   // the host checks that the worst case fits 31 bits
   const int k_stages = p.K / kStageK;   // 256-K stages per tile
   // "virtual" weight stages of a tile: two-matrix modes alternate the matrices stage by stage
   constexpr int kMats = mode_mats(MODE);
@@ -342,8 +357,8 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
     // ---------------- weight producer ----------------
     {
       uint32_t st = 0, ph = 0;
-      for (int64_t t = blockIdx.x; t < total_tiles && !guard.aborted(); t += gridDim.x) {
-        const int nt = (int)(t % n_tiles), b = (int)(t / n_tiles);
+      for (int t = (int)blockIdx.x; t < total_tiles && !guard.aborted(); t += (int)gridDim.x) {
+        const int b = t / n_tiles, nt = t - b * n_tiles;
         for (int vs = 0; vs < v_stages; ++vs) {
           const int ks = vs / kMats;
           const int row0 = tile_row(b, nt, vs);
@@ -352,9 +367,10 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
             mbar_expect_tx(&w_full[st], kPackedStageBytes + kScaleStageBytes);
             tma_load_2d(s_packed + st * kPackedStageBytes, &tm_packed, &w_full[st], ks * (kStageK / 2), row0);
             tma_load_2d(s_scale + st * kScaleStageBytes, &tm_scale, &w_full[st], ks * (kStageK / 32), row0);
-          } else {  // MXFP4 scales are read straight from global memory by the dequantisers
-            mbar_expect_tx(&w_full[st], kPackedStageBytes);
+          } else {  // e8m0 scales: 16 bytes per row = the scales of stages ks & ~1 and ks | 1
+            mbar_expect_tx(&w_full[st], kPackedStageBytes + kScaleStageBytes);
             tma_load_2d(s_packed + st * kPackedStageBytes, &tm_packed, &w_full[st], ks * (kStageK / 2), row0);
+            tma_load_2d(s_scale + st * kScaleStageBytes, &tm_scale, &w_full[st], (ks >> 1) * 16, row0);
           }
           if (++st == kWStages) { st = 0; ph ^= 1; }
         }
@@ -364,8 +380,8 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
     // ---------------- token producer (diverged from lane 0; both make progress independently) ----------------
     {
       uint32_t st = 0, tb = 0;   // token stage slot and running number of the token stage
-      for (int64_t t = blockIdx.x; t < total_tiles && !guard.aborted(); t += gridDim.x) {
-        const int b = (int)(t / n_tiles);
+      for (int t = (int)blockIdx.x; t < total_tiles && !guard.aborted(); t += (int)gridDim.x) {
+        const int b = t / n_tiles;
         const int pos0 = b * BT;
         for (int ks = 0; ks < k_stages; ++ks) {
           // the slot's previous user was token stage tb - kBStages: wait for its readers' commits
@@ -406,7 +422,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
       uint32_t bbar = (me / kMats) % Cfg::kBBars, bcyc = 0;              // token barrier and lap parity
       uint32_t it = 0, g0mod = 0;                                        // g0mod = (first stage of the tile) % kIssuers
       const uint32_t vsmod = (uint32_t)v_stages % kIssuers;
-      for (int64_t t = blockIdx.x; t < total_tiles && uni(!guard.aborted()); t += gridDim.x, ++it) {
+      for (int t = (int)blockIdx.x; t < total_tiles && uni(!guard.aborted()); t += (int)gridDim.x, ++it) {
         // accumulator set of this tile; its previous user must have been read out by every epilogue warp
         const uint32_t dbuf = it % Cfg::kDBuf, duse = it / Cfg::kDBuf;
         bool ok = uni(mbar_wait(&d_empty[dbuf], (duse & 1u) ^ 1u, guard, 8, 100));
@@ -472,18 +488,10 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
     const int row = quarter * 32 + lane;       // weight row inside the tile
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     const uint32_t s_packed_u32 = smem_u32(s_packed), s_scale_u32 = smem_u32(s_scale);
-    // MXFP4: the four e8m0 bytes of this row's half stage, fetched one stage ahead
-    auto mx_scale_load = [&](int64_t t, int vs) -> uint32_t {
-      const int nt = (int)(t % n_tiles), b = (int)(t / n_tiles);
-      const int64_t grow = (int64_t)tile_row(b, nt, vs) + row;
-      const uint8_t* sp = p.mx_scale + grow * (p.K / 32) + (vs / kMats) * (kStageK / 32) + part * kChunks;
-      if (kChunks == 4) return __ldg(reinterpret_cast<const uint32_t*>(sp));
-      return __ldg(reinterpret_cast<const uint16_t*>(sp));
-    };
     // Epilogue of tile (b, nt) whose accumulators sit in set `dbuf` (use number `duse` of that
     // set).  It runs one weight stage into the NEXT tile (or after the last tile), so that the MMAs
     // it waits for have long finished and the pipeline never drains at a tile boundary.
-    auto run_epilogue = [&](int b, int nt, uint32_t dbuf, uint32_t duse, uint32_t tile_g0) -> bool {
+    auto run_epilogue = [&](int b, int nt, uint32_t dbuf, uint32_t duse, uint32_t tile_g0, int cg) -> bool {
       const uint32_t d_base = tmem_base + lane_base + dbuf * (uint32_t)(Cfg::kAccs * BT);
       // which accumulators the tile's stages went to: stage vs -> (issuer (g0 + vs) % kIssuers, matrix vs % kMats)
       uint32_t valid = 0;
@@ -503,9 +511,15 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
         bias0 = __bfloat162float(p.bias[e_row + n_glob]);
         if (MODE == kModeMxGateUp) bias1 = __bfloat162float(p.bias[e_row + p.N + n_glob]);
       }
-      // the warpgroups take the 16-column groups round robin
+      // this warpgroup's 16-column groups: cg, cg + kWGs, ...
 #pragma unroll 1
-      for (int c0 = wg * 16; c0 < BT; c0 += 16 * Cfg::kWGs) {
+      for (int c0 = cg * 16; c0 < BT; c0 += 16 * Cfg::kWGs) {
+        // slot ids of the 16 token positions (lane j holds position c0 + j); padding positions carry
+        // the value numel.  Decode-sized blocks hold one or two real tokens, so everything below is
+        // skipped for the others, and a block of padding only costs this one load.
+        const int32_t my_slot = (lane < 16) ? __ldg(slots + c0 + lane) : -1;
+        const uint32_t live = __ballot_sync(0xffffffffu, my_slot >= 0 && my_slot < p.numel) & 0xFFFFu;
+        if (live == 0u) continue;
         // acc = matrix 0 (INT4 / down: the only one; gate_up: gate; pair: first row tile), more = matrix 1,
         // each the sum of the accumulators that were written in this tile
         uint32_t acc[16], more[16];
@@ -534,10 +548,9 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
           const int64_t col = (n_glob & ~int64_t(7)) | (((n_glob & 3) << 1) | ((n_glob >> 2) & 1));
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            const int32_t slot = __ldg(slots + c0 + j);
-            if (slot < 0 || slot >= p.numel) continue;
-            float g = round_to_bf16(__uint_as_float(acc[j]));
-            float u = round_to_bf16(__uint_as_float(more[j]));
+            if (!((live >> j) & 1u)) continue;          // warp-uniform
+            float g = round_to_bf16(__uint_as_float(acc[j]) * kMxUnscale);   // exact: a power of two
+            float u = round_to_bf16(__uint_as_float(more[j]) * kMxUnscale);
             if (p.bias != nullptr) { g = round_to_bf16(g + bias0); u = round_to_bf16(u + bias1); }
             if (p.limit > 0.f) { g = fminf(g, p.limit); u = fminf(fmaxf(u, -p.limit), p.limit); }
             const float silu = g / (1.f + expf(-g));
@@ -546,12 +559,12 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
         } else {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            const int32_t slot = __ldg(slots + c0 + j);  // same address for the whole warp
-            if (slot < 0 || slot >= p.numel) continue;
+            if (!((live >> j) & 1u)) continue;          // warp-uniform
+            const int32_t slot = __shfl_sync(0xffffffffu, my_slot, j);
             float v = __uint_as_float(acc[j]);
             if (mode_is_int4(MODE) && kInt4NoSubtract) v *= kInt4Unscale;   // exact: a power of two
             if (MODE == kModeMxDown) {  // reference rounds `down` to bf16, adds the bf16 bias, then x w
-              v = round_to_bf16(v);
+              v = round_to_bf16(v * kMxUnscale);
               if (p.bias != nullptr) v = round_to_bf16(v + bias0);
               if (p.mul_w) v = v * p.topk_w[slot];
             } else if (p.mul_w) {
@@ -572,25 +585,18 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
       mbar_arrive_if(&d_empty[dbuf], (lane == 0) ? 1u : 0u);
       return true;
     };
-    bool pend = false;
-    int pend_b = 0, pend_nt = 0;
-    uint32_t pend_it = 0, pend_g0 = 0, it = 0, g0 = 0;      // g0 = number of the tile's first stage
-    // the stage this group converts after (t, vs, g0): kGroups further on, or the first own stage of a later tile
-    auto next_own = [&](int64_t& t, int& vs, uint32_t& gbase) -> bool {
-      vs += kGroups;
-      while (vs >= v_stages) {
-        t += gridDim.x;
-        if (t >= total_tiles) return false;
-        gbase += (uint32_t)v_stages;
-        vs = (int)((grp + kGroups - gbase % kGroups) % kGroups);
-      }
-      return true;
+    // Read-outs that are still due, oldest first (at most two wait at any time: a tile is read out
+    // before its accumulator set is needed again, see below).
+    struct Pending { int b, nt; uint32_t it, g0; int wait, cg; };
+    Pending pq0{0, 0, 0, 0, 0, 0}, pq1{0, 0, 0, 0, 0, 0};
+    int n_pend = 0;
+    auto run_oldest = [&]() -> bool {
+      const Pending e = pq0;
+      pq0 = pq1;
+      --n_pend;
+      return run_epilogue(e.b, e.nt, e.it % Cfg::kDBuf, e.it / Cfg::kDBuf, e.g0, e.cg);
     };
-    uint32_t mx_next = 0;
-    if (!mode_is_int4(MODE)) {
-      int64_t tn = blockIdx.x; int vn = (int)grp - kGroups; uint32_t gn = 0;
-      if (tn < total_tiles && next_own(tn, vn, gn)) mx_next = mx_scale_load(tn, vn);
-    }
+    uint32_t it = 0, g0 = 0;      // g0 = number of the tile's first stage
     // This group's stages are g = grp, grp + kGroups, ... whatever the tile boundaries, so its ring
     // positions advance by a fixed step per converted stage (no division in the loop).
     constexpr uint32_t kDU = (uint32_t)(kGroups * Cfg::kUnits);           // units per own-stage step
@@ -602,10 +608,12 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
     const uint32_t lead = (lane == 0) ? 1u : 0u;
     uint32_t g0mod = 0;                                                   // g0 % kGroups
     const uint32_t vsmod = (uint32_t)v_stages % kGroups;
-    for (int64_t t = blockIdx.x; t < total_tiles; t += gridDim.x, ++it, g0 += (uint32_t)v_stages) {
-      const int nt = (int)(t % n_tiles), b = (int)(t / n_tiles);
+    // (b, nt) of the tile advance with it: no division in the loop
+    const int step_b = (int)gridDim.x / n_tiles, step_nt = (int)gridDim.x - step_b * n_tiles;
+    int b = (int)blockIdx.x / n_tiles, nt = (int)blockIdx.x - b * n_tiles;
+    for (int t = (int)blockIdx.x; t < total_tiles; t += (int)gridDim.x, ++it, g0 += (uint32_t)v_stages,
+             b += step_b, nt += step_nt, b += (nt >= n_tiles ? 1 : 0), nt -= (nt >= n_tiles ? n_tiles : 0)) {
       bool ok = true;
-      bool epi_due = pend;   // the previous tile's epilogue runs after this group's first stage of this tile
       for (int vs = (int)(grp >= g0mod ? grp - g0mod : grp + kGroups - g0mod); vs < v_stages && ok; vs += kGroups) {
         if (!mbar_wait(&w_full[wst], wph, guard, 5)) { ok = false; break; }
         const uint32_t pk = s_packed_u32 + wst * kPackedStageBytes + row * 128;
@@ -613,10 +621,10 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
         if (mode_is_int4(MODE)) {
           if (kChunks == 4) sw = lds64(s_scale_u32 + wst * kScaleStageBytes + row * 16 + part * 8);
           else sw.x = lds32(s_scale_u32 + wst * kScaleStageBytes + row * 16 + part * 4);
-        } else {
-          sw.x = mx_next;
-          int64_t tn = t; int vn = vs; uint32_t gn = g0;
-          if (next_own(tn, vn, gn)) mx_next = mx_scale_load(tn, vn);
+        } else {  // the kChunks e8m0 bytes of this share: this stage's half of the row's sixteen
+          const uint32_t sa = s_scale_u32 + wst * kScaleStageBytes + row * 16 + (((vs / kMats) & 1) << 3) + part * kChunks;
+          if (kChunks == 4) sw.x = lds32(sa);
+          else sw.x = lds16(sa);
         }
         // 16-byte chunk = 32 weights = one scale group; this share is chunks kChunks * part ...
         uint4 w4[kChunks];
@@ -666,13 +674,14 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
               }
             }
           } else {
-            uint32_t c1, c2;
-            mx_scale_factors((sw.x >> (8 * c)) & 0xFFu, c1, c2);
+            const uint32_t sb = (sw.x >> (8 * c)) & 0xFFu;
+            if (sb > kMxMaxScale && sb != 0xFFu) atomicCAS(p.status, 0, kErrMxScaleRange);   // never taken for sane weights
+            const uint32_t cf = mx_scale_factor(sb);
 #pragma unroll
             for (int wp = 0; wp < 2; ++wp) {
               uint32_t r[8];
-              mx_word(words[2 * wp], c1, c2, r[0], r[1], r[2], r[3]);
-              mx_word(words[2 * wp + 1], c1, c2, r[4], r[5], r[6], r[7]);
+              mx_word(words[2 * wp], cf, r[0], r[1], r[2], r[3]);
+              mx_word(words[2 * wp + 1], cf, r[4], r[5], r[6], r[7]);
               tmem_st_32x8(dst + c * 16 + wp * 8, r[0], r[1], r[2], r[3], r[4], r[5], r[6], r[7]);
             }
           }
@@ -685,20 +694,30 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
         wst += kGroups; if (wst >= (uint32_t)kWStages) { wst -= kWStages; wph ^= 1u; }
         aq += kDU; if (aq >= (uint32_t)Cfg::kASlots) aq -= Cfg::kASlots;
         abar += kDU; if (abar >= (uint32_t)Cfg::kABars) { abar -= Cfg::kABars; acyc ^= 1u; }
-        if (epi_due) {
-          epi_due = false;
-          if (!run_epilogue(pend_b, pend_nt, pend_it % Cfg::kDBuf, pend_it / Cfg::kDBuf, pend_g0)) { ok = false; break; }
-        }
+        // read-outs whose delay has run out
+        --pq0.wait; --pq1.wait;
+        while (n_pend > 0 && pq0.wait <= 0 && ok) ok = run_oldest();
       }
       if (!ok) break;
-      if (epi_due) {  // this group had no stage in this tile
-        if (!run_epilogue(pend_b, pend_nt, pend_it % Cfg::kDBuf, pend_it / Cfg::kDBuf, pend_g0)) break;
+      // Before this tile joins the queue: a tile must have been read out before the MMAs of the tile
+      // kDBuf further on, which re-use its accumulator set, can start.  Reading it out no later than
+      // here (before any stage of tile it + 1 is converted) keeps every converted stage consumable,
+      // so the A slots can never fill up with stages that wait for a read-out.
+      while (n_pend > 0 && (pq0.it + (uint32_t)Cfg::kDBuf <= it + 1u || n_pend == 2) && ok) ok = run_oldest();
+      if (!ok) break;
+      // is this warpgroup on read-out duty for this tile, and for which column group?
+      const int cg = (Cfg::kEpiWGs == Cfg::kWGs) ? wg
+                                                 : (int)(((uint32_t)wg + (uint32_t)Cfg::kWGs - (it * (uint32_t)Cfg::kColGroups) % (uint32_t)Cfg::kWGs) % (uint32_t)Cfg::kWGs);
+      if (cg < Cfg::kColGroups || Cfg::kEpiWGs == Cfg::kWGs) {
+        const Pending e{b, nt, it, g0, Cfg::kDBuf >= 2 ? kEpiDelay : 1, cg};   // one set: the next tile's MMAs wait for it
+        if (n_pend == 0) pq0 = e; else pq1 = e;
+        ++n_pend;
       }
-      // the epilogue is deferred: see run_epilogue
-      pend = true; pend_b = b; pend_nt = nt; pend_it = it; pend_g0 = g0;
       g0mod += vsmod; if (g0mod >= (uint32_t)kGroups) g0mod -= kGroups;
     }
-    if (pend && !guard.aborted()) run_epilogue(pend_b, pend_nt, pend_it % Cfg::kDBuf, pend_it / Cfg::kDBuf, pend_g0);
+    while (n_pend > 0 && !guard.aborted()) {
+      if (!run_oldest()) break;
+    }
   }
 
   tc_fence_before();
@@ -787,6 +806,7 @@ int launch_bt(const CUtensorMap& tmp, const CUtensorMap& tms, const CUtensorMap&
   XKB_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   // one persistent CTA per SM (it owns all 512 tensor-memory columns), minus the SMs the caller
   // asked to keep free for kernels that should run beside this one (xkb_set_sm_margin)
+  XKB_REQUIRE(max_tiles < (1ll << 31), "moe_tc_kernel: %lld tiles do not fit the kernel's 31-bit tile index", (long long)max_tiles);
   int64_t grid = (int64_t)sms - g_sm_margin.load(std::memory_order_relaxed);
   if (grid < 8) grid = 8;
   if (grid > max_tiles) grid = max_tiles;
@@ -855,7 +875,6 @@ int launch_int4_tc(const void* A, const int32_t* packed, const void* scale, cons
   prm.N = (int)N;
   prm.K = (int)K;
   prm.mul_w = mul_w;
-  prm.mx_scale = nullptr;
   prm.bias = nullptr;
   prm.act = nullptr;
   prm.rows_per_expert = (int)N;
@@ -878,7 +897,8 @@ int launch_int4_tc(const void* A, const int32_t* packed, const void* scale, cons
 // ---------------------------------------------------------------------------
 bool mxfp4_tc_supported(int a_dtype, int64_t M, int64_t hidden, int64_t ispp, int E, int top_k) {
   return a_dtype == XKB_BF16 && M > 0 && E > 0 && top_k > 0 && hidden > 0 && ispp > 0 &&
-         hidden % kStageK == 0 && ispp % kStageK == 0 &&   // both are contraction lengths and tile-row counts
+         hidden % (2 * kStageK) == 0 && ispp % (2 * kStageK) == 0 &&   // contraction lengths and tile-row counts; a row's
+                                                                        // e8m0 scales must be whole 16-byte TMA rows
          (int64_t)E * 2 * ispp < (1ll << 31) && (int64_t)E * hidden < (1ll << 31);
 }
 
@@ -899,8 +919,8 @@ int launch_mxfp4_tc(const void* A, const uint8_t* w13, const uint8_t* w13_scale,
                     const float* topk_w, __nv_bfloat16* act, float* scratch, int64_t hidden, int64_t ispp,
                     int E, int top_k, float limit, int mul_w, void* tc_ws, int* status, cudaStream_t stream) {
   XKB_REQUIRE(r.block == 16 || r.block == 128, "mxfp4 tcgen05 path: unsupported token tile %d", r.block);
-  XKB_REQUIRE(reinterpret_cast<uintptr_t>(w13_scale) % 8 == 0 && reinterpret_cast<uintptr_t>(w2_scale) % 8 == 0,
-              "mxfp4 tcgen05 path: scale tensors must be 8-byte aligned");
+  XKB_REQUIRE(reinterpret_cast<uintptr_t>(w13_scale) % 16 == 0 && reinterpret_cast<uintptr_t>(w2_scale) % 16 == 0,
+              "mxfp4 tcgen05 path: scale tensors must be 16-byte aligned");
   Carver carve(tc_ws);
   __nv_bfloat16* Ag = carve.take<__nv_bfloat16>(r.max_pad * hidden);
   int64_t gblocks = r.max_pad < 148 * 16 ? r.max_pad : 148 * 16;
@@ -910,12 +930,18 @@ int launch_mxfp4_tc(const void* A, const uint8_t* w13, const uint8_t* w13_scale,
                                                                (int)hidden, top_k);
   XKB_CHECK_LAUNCH("gather_permute_kernel");
 
-  CUtensorMap tm_w13, tm_w2, tm_tok0, tm_tok1;
+  CUtensorMap tm_w13, tm_w2, tm_tok0, tm_tok1, tm_s13, tm_s2;
   int rc = make_map_2d(&tm_w13, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w13, (uint64_t)E * 2 * ispp, (uint64_t)hidden / 2,
                        kTileRows, kStageK / 2, CU_TENSOR_MAP_SWIZZLE_128B, "w13");
   if (rc != XKB_OK) return rc;
   rc = make_map_2d(&tm_w2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w2, (uint64_t)E * hidden, (uint64_t)ispp / 2,
                    kTileRows, kStageK / 2, CU_TENSOR_MAP_SWIZZLE_128B, "w2");
+  if (rc != XKB_OK) return rc;
+  rc = make_map_2d(&tm_s13, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w13_scale, (uint64_t)E * 2 * ispp, (uint64_t)hidden / 32,
+                   kTileRows, 16, CU_TENSOR_MAP_SWIZZLE_NONE, "w13 scales");
+  if (rc != XKB_OK) return rc;
+  rc = make_map_2d(&tm_s2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w2_scale, (uint64_t)E * hidden, (uint64_t)ispp / 32,
+                   kTileRows, 16, CU_TENSOR_MAP_SWIZZLE_NONE, "w2 scales");
   if (rc != XKB_OK) return rc;
   rc = make_map_2d(&tm_tok0, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, Ag, (uint64_t)r.max_pad, (uint64_t)hidden,
                    (uint32_t)r.block, kSubK, CU_TENSOR_MAP_SWIZZLE_128B, "gathered activations");
@@ -939,11 +965,10 @@ int launch_mxfp4_tc(const void* A, const uint8_t* w13, const uint8_t* w13_scale,
   prm.N = (int)ispp;
   prm.K = (int)hidden;
   prm.rows_per_expert = (int)(2 * ispp);
-  prm.mx_scale = w13_scale;
   prm.bias = static_cast<const __nv_bfloat16*>(b13);
   int64_t max_tiles = r.max_blocks * (ispp / kTileRows);
-  rc = r.block == 16 ? launch_bt<16, kModeMxGateUp>(tm_w13, tm_w13, tm_tok0, prm, max_tiles, stream)
-                     : launch_bt<128, kModeMxGateUp>(tm_w13, tm_w13, tm_tok0, prm, max_tiles, stream);
+  rc = r.block == 16 ? launch_bt<16, kModeMxGateUp>(tm_w13, tm_s13, tm_tok0, prm, max_tiles, stream)
+                     : launch_bt<128, kModeMxGateUp>(tm_w13, tm_s13, tm_tok0, prm, max_tiles, stream);
   if (rc != XKB_OK) return rc;
   // stage 1: down -> fp32 slot rows
   prm.scratch = scratch;
@@ -951,11 +976,10 @@ int launch_mxfp4_tc(const void* A, const uint8_t* w13, const uint8_t* w13_scale,
   prm.N = (int)hidden;
   prm.K = (int)ispp;
   prm.rows_per_expert = (int)hidden;
-  prm.mx_scale = w2_scale;
   prm.bias = static_cast<const __nv_bfloat16*>(b2);
   max_tiles = r.max_blocks * (hidden / kTileRows);
-  return r.block == 16 ? launch_bt<16, kModeMxDown>(tm_w2, tm_w2, tm_tok1, prm, max_tiles, stream)
-                       : launch_bt<128, kModeMxDown>(tm_w2, tm_w2, tm_tok1, prm, max_tiles, stream);
+  return r.block == 16 ? launch_bt<16, kModeMxDown>(tm_w2, tm_s2, tm_tok1, prm, max_tiles, stream)
+                       : launch_bt<128, kModeMxDown>(tm_w2, tm_s2, tm_tok1, prm, max_tiles, stream);
 }
 
 }  // namespace xkb

@@ -193,6 +193,26 @@ def moe_sum_reduce(y, w=None, routed_scaling_factor=1.0):
 
 
 # ---------------------------------------------------------------------------
+_checked_scales: dict[tuple[int, int], int] = {}
+_INT4_SCALE_LIMIT = float(2 ** 24)
+
+
+def _check_int4_scales(scale: torch.Tensor) -> None:
+    """The tcgen05 INT4 dequantiser is exact for group scales below 2^24 in magnitude (it multiplies
+    by s * 2^103 in bf16); a larger or non-finite scale would come out as inf/NaN, so such a tensor
+    is refused.  Checked once per tensor (keyed by storage address, size and version counter): one
+    reduction and one host read on the first call with it, so make that call before a stream capture."""
+    key = (scale.data_ptr(), scale.numel())
+    if _checked_scales.get(key) == scale._version:
+        return
+    top = float(scale.abs().max()) if scale.numel() else 0.0
+    if not (top < _INT4_SCALE_LIMIT):        # also catches NaN
+        raise ValueError(f"fused_moe_int4_w4a16: group scales must be finite and below 2^24 in magnitude (max |scale| = {top})")
+    if len(_checked_scales) > 256:
+        _checked_scales.clear()
+    _checked_scales[key] = scale._version
+
+
 def _routing_args(name, topk_ids, topk_w, expert_map, dev, M):
     if topk_ids.dim() != 2 or topk_ids.shape[0] != M:
         raise ValueError(f"{name}: topk_ids must be [M, top_k]")
@@ -240,6 +260,8 @@ def fused_moe_int4_w4a16(A, packed, scale, topk_ids, topk_w, group_size=32, mul_
     ids, tw, emap = _routing_args("fused_moe_int4_w4a16", topk_ids, topk_w, expert_map, dev, M)
     top_k = ids.shape[1]
     pcode = {"auto": _lib.PATH_AUTO, "simt": _lib.PATH_SIMT, "tc": _lib.PATH_TC}[path]
+    if path != "simt":
+        _check_int4_scales(scale)
     with torch.cuda.device(dev):
         out = torch.empty((M, N), dtype=A.dtype, device=dev)
         ws_bytes = int(lib.xkb_fused_moe_int4_w4a16_workspace_bytes(M, N, K, E, top_k, _DT[A.dtype]))
@@ -323,6 +345,8 @@ def moe_int4_w4a16_rows(A, packed, scale, topk_ids, topk_w=None, group_size=32, 
     top_k = ids.shape[1]
     tw = None if topk_w is None else topk_w.to(torch.float32).contiguous()
     pcode = {"auto": _lib.PATH_AUTO, "simt": _lib.PATH_SIMT, "tc": _lib.PATH_TC}[path]
+    if path != "simt":
+        _check_int4_scales(scale)
     with torch.cuda.device(dev):
         rows = torch.empty((M * top_k, N), dtype=torch.float32, device=dev)
         if M == 0:
