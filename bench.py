@@ -404,7 +404,57 @@ def run_single_gpu(args):
         line["other_configs"] = extras(dev, peaks)
     if not args.no_cpu:
         line["cpu_baseline"] = cpu_baseline_block(cfg, 512, verbatim=not args.no_verbatim)
+    if args.write_cards:
+        line["cards_written"] = write_cards(args, line)
     print(json.dumps(line), flush=True)
+
+
+def write_cards(args, line):
+    """--write-cards DIR: append this run's numbers to the cards' ``perf.measured`` through the
+    reference's own record_measurement (needs the reference package under baseline/_ref)."""
+    if reference_cpu_callable() is None:
+        return {"error": "the reference package is not installed under baseline/_ref"}
+    from xkernels_b200 import plugin
+
+    gpu = torch.cuda.get_device_name(0)
+    src = (f"python bench.py --gpus 1 --steps {args.steps} --warmup {args.warmup} on {gpu}, CUDA events, "
+           f"SM clock {line['clocks'].get('sm_mhz')} MHz, throttle reasons {line['clocks'].get('reasons')}, "
+           f"{time.strftime('%Y-%m-%dT%H:%M:%SZ', time.gmtime())}")
+    done = []
+    r = line["roofline"]
+    plugin.write_back("moe_int4_w4a16.cuda@1.0.0", shape={"M": 64, "K": 7168, "N": 4096, "E": 48, "top_k": 8}, dtype="bf16",
+                      source=src, ms=round(line["ms_per_step"], 5), achieved_bw_pct=round(100 * r["whole_call_frac"], 2),
+                      cards_dir=args.write_cards)
+    done.append("moe_int4_w4a16.cuda@1.0.0 decode")
+    oc = line.get("other_configs", {})
+    if "ms_per_call" in oc.get("int4_prefill", {}):
+        p = oc["int4_prefill"]
+        plugin.write_back("moe_int4_w4a16.cuda@1.0.0", shape={"M": 16384, "K": 7168, "N": 4096, "E": 48, "top_k": 8},
+                          dtype="bf16", source=src, ms=round(p["ms_per_call"], 4),
+                          tflops=round(2.0 * 16384 * 8 * 4096 * 7168 / (p["ms_per_call"] * 1e-3) / 1e12, 1),
+                          cards_dir=args.write_cards)
+        plugin.write_back("moe_align_block_size.cuda@1.0.0", shape={"M": 16384, "top_k": 8, "num_experts": 48, "block_size": 16},
+                          dtype="i32", source=src, ms=round(p["align_block16_us"] * 1e-3, 5), cards_dir=args.write_cards)
+        done += ["moe_int4_w4a16.cuda@1.0.0 prefill", "moe_align_block_size.cuda@1.0.0"]
+    if "us_per_call" in oc.get("mxfp4_decode", {}):
+        m = oc["mxfp4_decode"]
+        plugin.write_back("moe_mxfp4.cuda@1.0.0", shape={"M": 48, "hidden": 4096, "ispp": 512, "E": 256, "top_k": 6},
+                          dtype="bf16", source=src, ms=round(m["us_per_call"] * 1e-3, 5),
+                          achieved_bw_pct=round(100 * m["algorithmic_bytes"] / (m["us_per_call"] * 1e-6) / 1e9 / load_peaks()["hbm_gbs"], 2),
+                          cards_dir=args.write_cards)
+        done.append("moe_mxfp4.cuda@1.0.0")
+    if "us_per_call" in oc.get("moe_sum_reduce_8192x8x7168_bf16", {}):
+        m = oc["moe_sum_reduce_8192x8x7168_bf16"]
+        plugin.write_back("moe_sum_reduce.cuda@1.1.0", shape={"M": 8192, "top_k": 8, "H": 7168}, dtype="bf16", source=src,
+                          ms=round(m["us_per_call"] * 1e-3, 5), achieved_bw_pct=round(100 * m["frac_of_hbm_peak"], 2),
+                          cards_dir=args.write_cards)
+        done.append("moe_sum_reduce.cuda@1.1.0")
+    if "us_per_call" in oc.get("topk_softmax_16384x256_top8_bf16", {}):
+        m = oc["topk_softmax_16384x256_top8_bf16"]
+        plugin.write_back("topk_softmax.cuda@1.0.0", shape={"M": 16384, "E": 256, "topk": 8}, dtype="bf16", source=src,
+                          ms=round(m["us_per_call"] * 1e-3, 5), cards_dir=args.write_cards)
+        done.append("topk_softmax.cuda@1.0.0")
+    return done
 
 
 def time_call(fn, warmup: int, steps: int):
@@ -537,6 +587,9 @@ def run_multi_gpu(args, world: int, rank: int, local_rank: int):
     layer = ep.ExpertParallelInt4(packed, scale, num_global_experts=cfg.E, group=dist.group.WORLD,
                                   group_size=cfg.group_size, placement=args.ep_placement, chunks=args.ep_chunks,
                                   sm_margin=args.ep_sm_margin)
+    # model set-up, outside the timed region: the most popular experts (measured on this batch's
+    # routing) are copied to every rank; their slots are then served where the token lives
+    hot = layer.rebalance(ids, args.ep_replicas) if args.ep_replicas > 0 else []
 
     # reference point for scaling: the SAME configuration on one GPU (all 256 experts local, 4096
     # tokens, no exchange), timed on rank 0 before the group run
@@ -647,6 +700,7 @@ def run_multi_gpu(args, world: int, rank: int, local_rank: int):
             "slots_received_per_rank": slots,
             "rows_received_per_rank": rows_in,   # one activation row per (token, rank) pair crosses the wire
             "ep": {"placement": args.ep_placement, "chunks": args.ep_chunks, "sm_margin": args.ep_sm_margin,
+                   "replicated_experts": hot,
                    "same_config_on_one_gpu": single,
                    # weak scaling against the SAME configuration on one GPU (the N=1 line of this
                    # benchmark is the decode workload, a different one)
@@ -699,9 +753,14 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--no-verbatim", action="store_true",
                     help="skip the one full-size run of the reference's CPU function (about 15 s, 24 GB of host memory)")
+    ap.add_argument("--write-cards", default=None, metavar="DIR",
+                    help="append this run's numbers to the cards' perf.measured (through the reference's "
+                         "record_measurement) and write the updated card files to DIR")
     ap.add_argument("--ep-placement", default="round_robin", choices=["contiguous", "round_robin", "snake"],
                     help="expert -> rank assignment of the expert-parallel run")
     ap.add_argument("--ep-chunks", type=int, default=1, help="token chunks pipelined through the exchanges")
+    ap.add_argument("--ep-replicas", type=int, default=4,
+                    help="most popular experts copied to every rank (their slots stay on the token's rank)")
     ap.add_argument("--ep-sm-margin", type=int, default=16,
                     help="SMs the GEMM kernels leave to the exchange kernels when chunks > 1")
     ap.add_argument("--case", default=None, choices=sorted(PROFILE_CASES),

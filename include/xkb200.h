@@ -173,6 +173,22 @@ int xkb_moe_int4_w4a16_rows(const void* A, int a_dtype, const int32_t* packed,
                             int group_size, int mul_routed_weight, int path,
                             void* workspace, int64_t workspace_bytes,
                             void* stream);
+ /* xkb_moe_int4_w4a16_partial: the expert side of the all-to-all mode in one
+ *   call.  A [M,K] are the received rows, routing [M, 2*top_k] int32 what
+ *   travelled with them (top_k local expert ids, -1 = slot served on another
+ *   rank, then the top_k routing weights' fp32 bit patterns; the layout
+ *   xkb_ep_plan writes).  out [M,N] fp32 = per received row the weighted sum
+ *   over its local experts in ascending slot order, i.e. the rank's partial
+ *   of ops/moe/reference.py:59-69 before the final cast. */
+int64_t xkb_moe_int4_w4a16_partial_workspace_bytes(int64_t M, int64_t N,
+                                                   int64_t K, int E, int top_k,
+                                                   int a_dtype);
+int xkb_moe_int4_w4a16_partial(const void* A, int a_dtype,
+                               const int32_t* packed, const void* scale,
+                               const int32_t* routing, float* out, int64_t M,
+                               int64_t N, int64_t K, int E, int top_k,
+                               int group_size, int path, void* workspace,
+                               int64_t workspace_bytes, void* stream);
 int xkb_moe_gather_sum_reduce(const float* rows, const int32_t* row_index,
                               const float* w, void* out, int out_dtype,
                               int64_t M, int top_k, int64_t H, void* stream);
@@ -198,13 +214,27 @@ int xkb_set_sm_margin(int sms);
  * {number of pairs, number of expert ids outside [0, experts_per_rank*world)}.
  * round_robin = 0: rank r owns experts [r*experts_per_rank, ...); 1: expert g
  * lives on rank g % world as local expert g / world; 2: as 1, but every second
- * group of `world` experts is dealt in reverse rank order.  top_k <= 32. */
+ * group of `world` experts is dealt in reverse rank order.  expert_table, if not
+ * NULL, overrides all three: [experts_per_rank*world, 2] int32 on the device,
+ * (destination rank, expert index on that rank) per global expert as THIS rank
+ * sees it - a rank that holds a replica of a popular expert names itself there,
+ * so those slots never leave the GPU.  top_k <= 32. */
 int64_t xkb_ep_plan_workspace_bytes(int64_t M, int top_k, int world, int chunks);
 int xkb_ep_plan(const int32_t* topk_ids, const float* topk_w, int64_t M, int top_k,
-                int experts_per_rank, int world, int round_robin, int chunks,
+                int experts_per_rank, int world, int round_robin,
+                const int32_t* expert_table, int chunks,
                 int32_t* pair_token, int32_t* pair_dest, int32_t* routing,
                 int32_t* pair_of, int32_t* counts, int32_t* info, void* workspace,
                 int64_t workspace_bytes, void* stream);
+
+/* xkb_gather_rows: dst[p,:] = src[index[p],:] for p < *count_dev (count_dev NULL:
+ * for all max_rows positions); rows of row_bytes bytes, a multiple of 16.  Fills
+ * the dispatch send buffer of the all-to-all mode from the plan's pair_token
+ * list while the host still waits for the pair counts: the row count is read on
+ * the device (the plan's info[0]).  No reference counterpart. */
+int xkb_gather_rows(const void* src, int64_t src_rows, int64_t row_bytes,
+                    const int32_t* index, const int32_t* count_dev,
+                    int64_t max_rows, void* dst, void* stream);
 
 /* ------------------------------------------------------------------------
  * fused_moe_mxfp4: gate_up GEMM -> clamped SwiGLU -> down GEMM -> combine

@@ -47,7 +47,8 @@ def _cpu_reduce(rows, row_index, M, dtype):
     return out.to(dtype)
 
 
-def _worker(rank: int, world: int, port: int, fail_rank: int, placement: str = "contiguous", chunks: int = 1):
+def _worker(rank: int, world: int, port: int, fail_rank: int, placement: str = "contiguous", chunks: int = 1,
+            n_replicas: int = 0):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
@@ -71,9 +72,27 @@ def _worker(rank: int, world: int, port: int, fail_rank: int, placement: str = "
             want = oracle.moe_w4a16(A, packed, scale, ids, w, 32)
             assert oracle.count_violations(out, want, 2e-2, 1e-2) == 0
             return
+        sent_before = None
+        if n_replicas:
+            layer(A, ids, w)
+            sent_before = sum(c for p, c in enumerate(layer.last_send_counts) if p != rank)
+            hot = layer.rebalance(ids, n_replicas)
+            # every rank picked the same experts and now holds them behind its own
+            assert len(hot) == n_replicas and layer.packed.shape[0] == e_local + n_replicas
+            for i, g in enumerate(hot):
+                assert torch.equal(layer.packed[e_local + i], packed[g]) and torch.equal(layer.scale[e_local + i], scale[g])
+            layer.partial_fn = _oracle_partial(layer.packed, layer.scale)
         out = layer(A, ids, w)
         want = oracle.moe_w4a16(A, packed, scale, ids, w, 32)
         assert oracle.count_violations(out, want, 2e-2, 1e-2) == 0, f"rank {rank} differs from the dense oracle"
+        if n_replicas:
+            # the popular experts' slots stay at home: fewer rows leave this rank than before
+            sent_after = sum(c for p, c in enumerate(layer.last_send_counts) if p != rank)
+            assert sent_after <= sent_before
+            total = torch.tensor([layer.count_recv_slots(), sent_before - sent_after])
+            dist.all_reduce(total)
+            assert int(total[0]) == world * CFG.M * CFG.top_k and int(total[1]) > 0
+            return
         # every token went once to each rank that owns one of its experts, every slot is computed
         # exactly once, and the receive counts add up over the ranks
         plan = ep.plan_dispatch(ids, e_local, world, placement, chunks)
@@ -94,6 +113,20 @@ def _worker(rank: int, world: int, port: int, fail_rank: int, placement: str = "
                                                      (4, "snake", 1)])
 def test_all_to_all_matches_dense_oracle(world, placement, chunks):
     mp.spawn(_worker, args=(world, _free_port(), -1, placement, chunks), nprocs=world, join=True)
+
+
+@pytest.mark.parametrize("world,placement,chunks,n_replicas", [(2, "contiguous", 1, 2), (4, "round_robin", 2, 3)])
+def test_replicated_popular_experts_keep_the_result_and_cut_the_traffic(world, placement, chunks, n_replicas):
+    mp.spawn(_worker, args=(world, _free_port(), -1, placement, chunks, n_replicas), nprocs=world, join=True)
+
+
+def test_expert_table_sends_replicated_experts_home():
+    t = ep.expert_table(4, 2, "contiguous", rank=1, replicas=[5, 0])
+    assert t.tolist() == [[1, 5], [0, 1], [0, 2], [0, 3], [1, 0], [1, 4], [1, 2], [1, 3]]
+    ids = torch.tensor([[0, 5, 2]], dtype=torch.int32)
+    plan = ep.plan_dispatch(ids, 4, 2, table=t)                     # as rank 1: experts 0 and 5 are served at home
+    assert plan.send_counts.tolist() == [[1, 1]]
+    assert plan.pair_dest.tolist() == [0, 1] and plan.pair_ids.tolist() == [[-1, -1, 2], [5, 4, -1]]
 
 
 def test_plan_dispatch_makes_one_pair_per_token_and_owner():

@@ -96,13 +96,42 @@ def test_device_plan_equals_host_plan(M, E, top_k, world, placement, chunks, cud
         assert int(info2[1]) == 2
 
 
+def test_device_plan_with_replicas_equals_host_plan(cuda_device):
+    """The explicit expert table (popular experts served on the token's own rank) through xkb_ep_plan
+    against ep.plan_dispatch."""
+    from xkernels_b200 import ep
+
+    M, E, top_k, world = 300, 32, 6, 4
+    ids, w = synth.routing(M, E, top_k, seed=9, zipf_scale=2.0)
+    table = ep.expert_table(E // world, world, "round_robin", rank=2, replicas=[0, 1, 7])
+    want = ep.plan_dispatch(ids, E // world, world, "round_robin", 2, table=table)
+    pt, pd, routing, pair_of, counts, info = ops.ep_plan(ids.to(cuda_device), w.to(cuda_device), E // world, world,
+                                                          "round_robin", 2, table=table.to(cuda_device))
+    P = want.pair_token.numel()
+    assert info.tolist() == [P, 0] and counts.cpu().tolist() == want.send_counts.tolist()
+    assert torch.equal(pt[:P].cpu().long(), want.pair_token) and torch.equal(pd[:P].cpu().long(), want.pair_dest)
+    assert torch.equal(routing[:P, :top_k].cpu(), want.pair_ids) and torch.equal(pair_of.cpu(), want.pair_of)
+    assert int(want.pair_ids.max()) >= E // world          # replica slots use the indices behind the own experts
+
+
+def test_gather_rows_with_the_count_on_the_device(cuda_device):
+    g = torch.Generator().manual_seed(2)
+    src = torch.randn(50, 64, generator=g).to(torch.bfloat16).to(cuda_device)
+    idx = torch.randint(0, 50, (40,), generator=g, dtype=torch.int32).to(cuda_device)
+    n = torch.tensor([25], dtype=torch.int32, device=cuda_device)
+    out = torch.full((40, 64), -7.0, dtype=torch.bfloat16, device=cuda_device)
+    ops.gather_rows(src, idx, n, out=out)
+    assert torch.equal(out[:25], src[idx[:25].long()]) and bool((out[25:] == -7.0).all())
+    assert torch.equal(ops.gather_rows(src, idx), src[idx.long()])
+
+
 def _free_port() -> int:
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         return s.getsockname()[1]
 
 
-def _ep_worker(rank: int, world: int, port: int, placement: str, chunks: int):
+def _ep_worker(rank: int, world: int, port: int, placement: str, chunks: int, n_replicas: int = 0):
     import torch.distributed as dist
 
     from xkernels_b200 import ep
@@ -120,6 +149,9 @@ def _ep_worker(rank: int, world: int, port: int, placement: str, chunks: int):
         ids, w = synth.routing(cfg.M, cfg.E, cfg.top_k, seed=200 + rank, zipf_scale=cfg.zipf_scale)
         layer = ep.ExpertParallelInt4(packed[sl].to(dev), scale[sl].to(dev), num_global_experts=cfg.E,
                                       placement=placement, chunks=chunks)
+        if n_replicas:
+            hot = layer.rebalance(ids.to(dev), n_replicas)
+            assert len(hot) == n_replicas and layer.packed.shape[0] == e_local + n_replicas
         out = layer(A.to(dev), ids.to(dev), w.to(dev))
         ops.check_status(dev)
         want = oracle.moe_w4a16(A, packed, scale, ids, w, 32)
@@ -132,12 +164,13 @@ def _ep_worker(rank: int, world: int, port: int, placement: str, chunks: int):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("placement,chunks", [("contiguous", 1), ("round_robin", 3), ("snake", 1)])
-def test_all_to_all_on_gpus(placement, chunks):
+@pytest.mark.parametrize("placement,chunks,n_replicas", [("contiguous", 1, 0), ("round_robin", 3, 0), ("snake", 1, 0),
+                                                         ("round_robin", 1, 3)])
+def test_all_to_all_on_gpus(placement, chunks, n_replicas):
     n = torch.cuda.device_count()
     if n < 2:
         pytest.skip("needs at least 2 GPUs")
     import torch.multiprocessing as mp
 
     world = 4 if n >= 4 else 2
-    mp.spawn(_ep_worker, args=(world, _free_port(), placement, chunks), nprocs=world, join=True)
+    mp.spawn(_ep_worker, args=(world, _free_port(), placement, chunks, n_replicas), nprocs=world, join=True)

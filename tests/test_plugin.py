@@ -75,3 +75,39 @@ def test_reference_cards_verify_and_cuda_is_not_runnable_on_cpu(tmp_path):
     assert par["inconclusive"] is True and par["n_runnable"] == 1
     par = verify_parity("moe_mxfp4@1.0.0")
     assert par["n_runnable"] == 1
+
+
+@needs_ref
+def test_cards_validate_against_the_reference_schema_and_write_back_goes_through_its_function(tmp_path):
+    """Every card of this package passes the reference's impl_card schema (the optional `persistent`
+    block included, registry/schema/impl_card.schema.json:169-222), and plugin.write_back records a
+    measurement with the reference's own record_measurement: sourced, replacing the same point."""
+    import jsonschema
+    import xkernels
+
+    from xkernels_b200 import plugin
+
+    plugin.install(tmp_path / "overlay")
+    from xkernels.registry import schemas
+
+    schema = json.loads((Path(schemas._SCHEMA_DIR) / "impl_card.schema.json").read_text())
+    cards = sorted((ROOT / "xkernels_b200" / "registry" / "impls").glob("*.card.json"))
+    for c in cards:
+        jsonschema.validate(json.loads(c.read_text()), schema)
+    tc = json.loads((ROOT / "xkernels_b200" / "registry" / "impls" / "moe_int4_w4a16.cuda.card.json").read_text())
+    assert tc["persistent"]["tensor_memory_columns"] == 512 and tc["arch"]["scratch"]["bytes"] > 100000
+    assert any("dequantiser" in r for r in tc["persistent"]["warp_roles"])
+
+    out = tmp_path / "cards"
+    shape = {"M": 64, "K": 7168, "N": 4096, "E": 48, "top_k": 8}
+    plugin.write_back("moe_int4_w4a16.cuda@1.0.0", shape=shape, dtype="bf16", source="run:test#1", ms=0.25,
+                      achieved_bw_pct=50.0, cards_dir=out)
+    plugin.write_back("moe_int4_w4a16.cuda@1.0.0", shape=shape, dtype="bf16", source="run:test#2", ms=0.2,
+                      achieved_bw_pct=62.0, cards_dir=out)
+    doc = json.loads((out / "moe_int4_w4a16.cuda.card.json").read_text())
+    jsonschema.validate(doc, schema)
+    same = [m for m in doc["perf"]["measured"] if m["shape"] == shape]
+    assert len(same) == 1 and same[0]["source"] == "run:test#2" and same[0]["ms"] == 0.2
+    with pytest.raises(ValueError):
+        plugin.write_back("moe_int4_w4a16.cuda@1.0.0", shape=shape, dtype="bf16", source="", ms=0.2, cards_dir=out)
+    assert xkernels is not None

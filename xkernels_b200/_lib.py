@@ -50,13 +50,20 @@ SIGNATURES = {
         [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
          c_int, c_int, c_int, c_int, c_int, c_void_p, c_int64, c_void_p],
     ),
+    "xkb_moe_int4_w4a16_partial_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64, c_int, c_int, c_int]),
+    "xkb_moe_int4_w4a16_partial": (
+        c_int,
+        [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_int,
+         c_int, c_void_p, c_int64, c_void_p],
+    ),
     "xkb_set_sm_margin": (c_int, [c_int]),
     "xkb_ep_plan_workspace_bytes": (c_int64, [c_int64, c_int, c_int, c_int]),
     "xkb_ep_plan": (
         c_int,
-        [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-         c_void_p, c_void_p, c_void_p, c_int64, c_void_p],
+        [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+         c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p],
     ),
+    "xkb_gather_rows": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
     "xkb_moe_gather_sum_reduce": (
         c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_int64, c_void_p]),
     "xkb_fused_moe_mxfp4_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64, c_int, c_int]),

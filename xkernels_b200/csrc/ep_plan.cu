@@ -15,9 +15,10 @@ namespace {
 
 constexpr int kMaxTopK = 32;
 
-__device__ __forceinline__ void owner_local(int id, int experts_per_rank, int world, int round_robin, int& owner,
-                                            int& local) {
-  if (round_robin == 1) { owner = id % world; local = id / world; }
+__device__ __forceinline__ void owner_local(int id, int experts_per_rank, int world, int round_robin,
+                                            const int32_t* __restrict__ table, int& owner, int& local) {
+  if (table != nullptr) { owner = table[2 * id]; local = table[2 * id + 1]; }   // explicit placement (replicas)
+  else if (round_robin == 1) { owner = id % world; local = id / world; }
   else if (round_robin == 2) {   // snake: every second group of `world` experts in reverse rank order
     local = id / world;
     const int pos = id % world;
@@ -29,7 +30,7 @@ __device__ __forceinline__ void owner_local(int id, int experts_per_rank, int wo
 // rank, -1 (dropped by the sort) for the others; dest/local per slot for the later stages
 __global__ void __launch_bounds__(256)
 ep_key_kernel(const int32_t* __restrict__ topk_ids, int64_t M, int top_k, int experts_per_rank, int world,
-              int round_robin, int64_t tokens_per_chunk, int32_t* __restrict__ key, int32_t* __restrict__ dest,
+              int round_robin, const int32_t* __restrict__ table, int64_t tokens_per_chunk, int32_t* __restrict__ key, int32_t* __restrict__ dest,
               int32_t* __restrict__ local, int32_t* __restrict__ info) {
   const int64_t m = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (m >= M) return;
@@ -41,7 +42,7 @@ ep_key_kernel(const int32_t* __restrict__ topk_ids, int64_t M, int top_k, int ex
     int id = topk_ids[m * top_k + j];
     if (id < 0 || id >= E) { ++bad; id = id < 0 ? 0 : E - 1; }     // clamped; the host raises on info[1]
     int o, l;
-    owner_local(id, experts_per_rank, world, round_robin, o, l);
+    owner_local(id, experts_per_rank, world, round_robin, table, o, l);
     d[j] = o;
     bool first = true;
     for (int i = 0; i < j; ++i) first = first && (d[i] != o);
@@ -95,7 +96,8 @@ extern "C" int64_t xkb_ep_plan_workspace_bytes(int64_t M, int top_k, int world, 
 }
 
 extern "C" int xkb_ep_plan(const int32_t* topk_ids, const float* topk_w, int64_t M, int top_k,
-                           int experts_per_rank, int world, int round_robin, int chunks, int32_t* pair_token,
+                           int experts_per_rank, int world, int round_robin, const int32_t* expert_table,
+                           int chunks, int32_t* pair_token,
                            int32_t* pair_dest, int32_t* routing, int32_t* pair_of, int32_t* counts,
                            int32_t* info, void* workspace, int64_t workspace_bytes, void* stream) {
   using namespace xkb;
@@ -125,7 +127,7 @@ extern "C" int xkb_ep_plan(const int32_t* topk_ids, const float* topk_w, int64_t
   void* align_ws = carve.take<char>(align_workspace_bytes(numel, groups));
   const int64_t tokens_per_chunk = (M + chunks - 1) / chunks;
   ep_key_kernel<<<(unsigned)ceil_div(M, 256), 256, 0, s>>>(topk_ids, M, top_k, experts_per_rank, world, round_robin,
-                                                           tokens_per_chunk, key, dest, local, info);
+                                                           expert_table, tokens_per_chunk, key, dest, local, info);
   XKB_CHECK_LAUNCH("ep_key_kernel");
   // stable counting sort of the slots by key, one position per block: no padding, dropped keys (-1) leave
   int rc = launch_align(key, numel, groups, 1, nullptr, 0, sorted, group_of, num_pairs, group_off, align_ws,
@@ -135,5 +137,44 @@ extern "C" int xkb_ep_plan(const int32_t* topk_ids, const float* topk_w, int64_t
       sorted, num_pairs, group_off, groups, dest, local, topk_w, top_k, world, pair_token, pair_dest, routing,
       pair_of, counts, info);
   XKB_CHECK_LAUNCH("ep_pairs_kernel");
+  return XKB_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Row gather with the row count on the device: dst[p, :] = src[index[p], :] for p < *count.
+// Used to fill the dispatch send buffer while the host still waits for the pair counts (the
+// count lives in the plan's info word), so that the copy is off the host's critical path.
+// ---------------------------------------------------------------------------
+namespace xkb {
+namespace {
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const uint4* __restrict__ src, int64_t row_vecs, const int32_t* __restrict__ index,
+                   const int32_t* __restrict__ count, int64_t max_rows, int64_t src_rows, uint4* __restrict__ dst) {
+  int64_t n = count != nullptr ? (int64_t)count[0] : max_rows;
+  if (n > max_rows) n = max_rows;
+  for (int64_t p = blockIdx.x; p < n; p += gridDim.x) {
+    const int64_t r = index[p];
+    if (r < 0 || r >= src_rows) continue;
+    const uint4* s = src + r * row_vecs;
+    uint4* d = dst + p * row_vecs;
+    for (int64_t i = threadIdx.x; i < row_vecs; i += blockDim.x) d[i] = __ldg(s + i);
+  }
+}
+}  // namespace
+}  // namespace xkb
+
+extern "C" int xkb_gather_rows(const void* src, int64_t src_rows, int64_t row_bytes, const int32_t* index,
+                               const int32_t* count_dev, int64_t max_rows, void* dst, void* stream) {
+  using namespace xkb;
+  XKB_REQUIRE(src_rows >= 0 && max_rows >= 0 && row_bytes > 0 && row_bytes % 16 == 0,
+              "gather_rows: rows must be a positive multiple of 16 bytes long (got %lld)", (long long)row_bytes);
+  if (max_rows == 0 || src_rows == 0) return XKB_OK;
+  XKB_REQUIRE(src && index && dst, "gather_rows: null pointer");
+  XKB_REQUIRE(reinterpret_cast<uintptr_t>(src) % 16 == 0 && reinterpret_cast<uintptr_t>(dst) % 16 == 0,
+              "gather_rows: src and dst must be 16-byte aligned");
+  int64_t blocks = max_rows < 148 * 16 ? max_rows : 148 * 16;
+  gather_rows_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(src), row_bytes / 16, index, count_dev, max_rows, src_rows, static_cast<uint4*>(dst));
+  XKB_CHECK_LAUNCH("gather_rows_kernel");
   return XKB_OK;
 }

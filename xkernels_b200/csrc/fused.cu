@@ -126,7 +126,8 @@ static int int4_impl(const void* A, int a_dtype, const int32_t* packed, const vo
                      const int32_t* topk_ids, const float* topk_w, const int32_t* expert_map,
                      int num_map, void* out, float* rows_out, int64_t M, int64_t N, int64_t K, int E,
                      int top_k, int group_size, int mul_routed_weight, int path, void* workspace,
-                     int64_t workspace_bytes, cudaStream_t stream) {
+                     int64_t workspace_bytes, cudaStream_t stream, int out_dtype = -1) {
+  if (out_dtype < 0) out_dtype = a_dtype;
   XKB_REQUIRE(a_dtype == XKB_BF16 || a_dtype == XKB_F32, "fused_moe_int4_w4a16: bad a_dtype %d", a_dtype);
   XKB_REQUIRE(M >= 0 && N >= 0 && K >= 0 && E >= 0 && top_k >= 0, "fused_moe_int4_w4a16: negative dim");
   XKB_REQUIRE(group_size > 0 && group_size % 8 == 0 && K % group_size == 0 && K % 8 == 0,
@@ -172,7 +173,7 @@ static int int4_impl(const void* A, int a_dtype, const int32_t* packed, const vo
                           mul_routed_weight, stream);
   if (rc != XKB_OK) return rc;
   if (rows_out != nullptr) return XKB_OK;
-  return launch_combine(scratch, topk_ids, expert_map, num_map, E, out, a_dtype, M, top_k, N, stream);
+  return launch_combine(scratch, topk_ids, expert_map, num_map, E, out, out_dtype, M, top_k, N, stream);
 }
 
 extern "C" int xkb_fused_moe_int4_w4a16(const void* A, int a_dtype, const int32_t* packed,
@@ -196,6 +197,59 @@ extern "C" int xkb_moe_int4_w4a16_rows(const void* A, int a_dtype, const int32_t
   return int4_impl(A, a_dtype, packed, scale, topk_ids, topk_w, nullptr, 0, nullptr, rows_out, M, N, K,
                    E, top_k, group_size, mul_routed_weight, path, workspace, workspace_bytes,
                    static_cast<cudaStream_t>(stream));
+}
+
+// ---------------------------------------------------------------------------
+// Expert side of the all-to-all mode in one call: received rows whose routing travels with them as
+// [M, 2*top_k] int32 (top_k local expert ids, -1 = slot served elsewhere, then the top_k routing
+// weights' bit patterns) -> one fp32 partial row per received row (the weighted sum over its local
+// experts, ascending slot order).  The routing is split into the two contiguous arrays the align
+// stage and the combine read by a small kernel, so that the host makes ONE call per chunk.
+// ---------------------------------------------------------------------------
+namespace xkb {
+namespace {
+__global__ void __launch_bounds__(256)
+split_routing_kernel(const int32_t* __restrict__ routing, int64_t numel, int top_k, int32_t* __restrict__ ids,
+                     float* __restrict__ w) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= numel) return;
+  const int64_t m = i / top_k;
+  const int j = (int)(i - m * top_k);
+  ids[i] = routing[m * 2 * top_k + j];
+  w[i] = __int_as_float(routing[m * 2 * top_k + top_k + j]);
+}
+}  // namespace
+}  // namespace xkb
+
+extern "C" int64_t xkb_moe_int4_w4a16_partial_workspace_bytes(int64_t M, int64_t N, int64_t K, int E, int top_k,
+                                                              int a_dtype) {
+  const int64_t base = xkb_fused_moe_int4_w4a16_workspace_bytes(M, N, K, E, top_k, a_dtype);
+  if (base < 0) return base;
+  return base + 2 * align_up(M * top_k * 4, 256);
+}
+
+extern "C" int xkb_moe_int4_w4a16_partial(const void* A, int a_dtype, const int32_t* packed, const void* scale,
+                                          const int32_t* routing, float* out, int64_t M, int64_t N, int64_t K,
+                                          int E, int top_k, int group_size, int path, void* workspace,
+                                          int64_t workspace_bytes, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  XKB_REQUIRE(M >= 0 && N >= 0 && K >= 0 && E >= 0 && top_k >= 1, "moe_int4_w4a16_partial: bad dimension");
+  if (M == 0 || N == 0) return XKB_OK;
+  XKB_REQUIRE(routing != nullptr && out != nullptr, "moe_int4_w4a16_partial: null routing/out");
+  const int64_t need = xkb_moe_int4_w4a16_partial_workspace_bytes(M, N, K, E, top_k, a_dtype);
+  if (workspace == nullptr || workspace_bytes < need)
+    return fail(XKB_ERR_WORKSPACE, "moe_int4_w4a16_partial: workspace of %lld bytes needed, %lld given",
+                (long long)need, (long long)workspace_bytes);
+  XKB_REQUIRE(reinterpret_cast<uintptr_t>(workspace) % 256 == 0, "workspace must be 256-byte aligned");
+  // the two routing arrays sit behind the fused op's own workspace
+  const int64_t base = xkb_fused_moe_int4_w4a16_workspace_bytes(M, N, K, E, top_k, a_dtype);
+  const int64_t numel = M * top_k;
+  int32_t* ids = reinterpret_cast<int32_t*>(static_cast<char*>(workspace) + align_up(base, 256));
+  float* w = reinterpret_cast<float*>(reinterpret_cast<char*>(ids) + align_up(numel * 4, 256));
+  split_routing_kernel<<<(unsigned)ceil_div(numel, 256), 256, 0, stream>>>(routing, numel, top_k, ids, w);
+  XKB_CHECK_LAUNCH("split_routing_kernel");
+  return int4_impl(A, a_dtype, packed, scale, ids, w, nullptr, 0, out, nullptr, M, N, K, E, top_k, group_size, 1,
+                   path, workspace, base, stream, XKB_F32);
 }
 
 // ---------------------------------------------------------------------------

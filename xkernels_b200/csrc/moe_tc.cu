@@ -184,10 +184,14 @@ template <int BT, int MATS = 1, bool INT4 = true> struct TcCfg {
 constexpr int kModeInt4 = 0;      // INT4 W4A16: rows = N, bf16 group scales by TMA, fp32 slot rows out
 constexpr int kModeMxGateUp = 1;  // MXFP4 w13: a tile is 128 gate rows + the 128 matching up rows, the
                                   // two matrices alternate 256-K stages and accumulators; SwiGLU epilogue
-constexpr int kModeMxDown = 2;    // MXFP4 w2: rows = hidden, bf16-rounded result x routing weight out
+constexpr int kModeMxDown = 2;    // MXFP4 w2: rows = hidden, bf16-rounded result x routing weight out; two 128-row
+                                  // weight tiles per token tile like kModeInt4Pair: with K = ispp of a few
+                                  // hundred a single-tile pass would be two stages long, and the per-tile work
+                                  // (read-out, loop bookkeeping) would weigh as much as the stages themselves
 constexpr int kModeInt4Pair = 3;  // INT4 with TWO 128-row weight tiles per token tile (they alternate
                                   // 256-K stages like gate/up): halves the token-tile traffic per flop
-constexpr int mode_mats(int mode) { return (mode == kModeMxGateUp || mode == kModeInt4Pair) ? 2 : 1; }
+constexpr bool mode_is_pair(int mode) { return mode == kModeInt4Pair || mode == kModeMxDown; }
+constexpr int mode_mats(int mode) { return (mode == kModeMxGateUp || mode_is_pair(mode)) ? 2 : 1; }
 constexpr bool mode_is_int4(int mode) { return mode == kModeInt4 || mode == kModeInt4Pair; }
 
 struct TcParams {
@@ -337,7 +341,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
 
   // tile index t -> (token block, row tile); the row tile varies fastest so that CTAs that run
   // together share the token block and walk through one expert's weights
-  const int n_tiles = p.N / (MODE == kModeInt4Pair ? 2 * kTileRows : kTileRows);
+  const int n_tiles = p.N / (mode_is_pair(MODE) ? 2 * kTileRows : kTileRows);
   const int n_blocks = p.num_post[0] / BT;
   const int total_tiles = n_blocks * n_tiles;   // the host checks that the worst case fits 31 bits
   const int k_stages = p.K / kStageK;   // 256-K stages per tile
@@ -349,7 +353,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
     const int e = p.expert_ids[b];
     if (MODE == kModeInt4) return e * p.N + nt * kTileRows;
     if (MODE == kModeInt4Pair) return e * p.N + (2 * nt + (vs & 1)) * kTileRows;
-    if (MODE == kModeMxDown) return e * p.rows_per_expert + nt * kTileRows;
+    if (MODE == kModeMxDown) return e * p.rows_per_expert + (2 * nt + (vs & 1)) * kTileRows;
     return e * p.rows_per_expert + (vs & 1) * p.N + nt * kTileRows;  // gate rows, then up rows
   };
 
@@ -503,13 +507,14 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
       }
       if (!mbar_wait(&d_full[dbuf], duse & 1u, guard, 7)) return false;
       tc_fence_after();
-      const int64_t n_glob = (int64_t)nt * (MODE == kModeInt4Pair ? 2 * kTileRows : kTileRows) + row;
+      const int64_t n_glob = (int64_t)nt * (mode_is_pair(MODE) ? 2 * kTileRows : kTileRows) + row;
       const int32_t* slots = p.sorted_ids + (int64_t)b * BT;
       float bias0 = 0.f, bias1 = 0.f;
       if (!mode_is_int4(MODE) && p.bias != nullptr) {
         const int64_t e_row = (int64_t)p.expert_ids[b] * p.rows_per_expert;
         bias0 = __bfloat162float(p.bias[e_row + n_glob]);
         if (MODE == kModeMxGateUp) bias1 = __bfloat162float(p.bias[e_row + p.N + n_glob]);
+        if (MODE == kModeMxDown) bias1 = __bfloat162float(p.bias[e_row + n_glob + kTileRows]);
       }
       // this warpgroup's 16-column groups: cg, cg + kWGs, ...
 #pragma unroll 1
@@ -571,10 +576,16 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
               v = p.topk_w[slot] * v;
             }
             p.scratch[(int64_t)slot * p.N + n_glob] = v;
-            if (MODE == kModeInt4Pair) {  // the second weight tile: rows 128 further down
+            if (mode_is_pair(MODE)) {  // the second weight tile: rows 128 further down
               float v2 = __uint_as_float(more[j]);
-              if (kInt4NoSubtract) v2 *= kInt4Unscale;
-              if (p.mul_w) v2 = p.topk_w[slot] * v2;
+              if (MODE == kModeInt4Pair) {
+                if (kInt4NoSubtract) v2 *= kInt4Unscale;
+                if (p.mul_w) v2 = p.topk_w[slot] * v2;
+              } else {
+                v2 = round_to_bf16(v2 * kMxUnscale);
+                if (p.bias != nullptr) v2 = round_to_bf16(v2 + bias1);
+                if (p.mul_w) v2 = v2 * p.topk_w[slot];
+              }
               p.scratch[(int64_t)slot * p.N + n_glob + kTileRows] = v2;
             }
           }
@@ -978,8 +989,9 @@ int launch_mxfp4_tc(const void* A, const uint8_t* w13, const uint8_t* w13_scale,
   prm.rows_per_expert = (int)hidden;
   prm.bias = static_cast<const __nv_bfloat16*>(b2);
   max_tiles = r.max_blocks * (hidden / kTileRows);
-  return r.block == 16 ? launch_bt<16, kModeMxDown>(tm_w2, tm_s2, tm_tok1, prm, max_tiles, stream)
-                       : launch_bt<128, kModeMxDown>(tm_w2, tm_s2, tm_tok1, prm, max_tiles, stream);
+  // (hidden is a multiple of 512 here, so the row tiles pair up)
+  return r.block == 16 ? launch_bt<16, kModeMxDown>(tm_w2, tm_s2, tm_tok1, prm, max_tiles / 2, stream)
+                       : launch_bt<128, kModeMxDown>(tm_w2, tm_s2, tm_tok1, prm, max_tiles / 2, stream);
 }
 
 }  // namespace xkb

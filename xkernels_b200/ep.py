@@ -30,6 +30,13 @@ lives on rank ``g % W`` as local expert ``g // W``), which spreads a popularity-
 evenly over the ranks, or ``"snake"`` (like round robin, but every second group of W experts is
 dealt in reverse rank order, so that no rank collects the most popular expert of every group).
 
+Replicas: :meth:`ExpertParallelInt4.rebalance` counts the expert popularity over all ranks, copies the
+weights of the ``n`` most popular experts to every rank (they are static model state: one broadcast
+each) and routes a slot of such an expert to the token's OWN rank.  That takes the hot experts'
+slots off the wire and off their owner's GEMM, which is what bounds the step when a router is
+skewed (one expert can bring a third of a rank's work).  The result is unchanged: a replica holds
+the same bits as the original.
+
 The exchange uses ``torch.distributed`` (NCCL on GPUs, gloo on CPU); data lands in local buffers
 before any kernel reads it.  The local compute is pluggable so the routing logic runs on CPU ranks
 in tests.
@@ -90,8 +97,25 @@ class DispatchPlan:
         return self
 
 
+def expert_table(experts_per_rank: int, world: int, placement: str, rank: int | None = None,
+                 replicas: list[int] | tuple[int, ...] = ()) -> torch.Tensor:
+    """``[E, 2]`` int32: (destination rank, expert index there) of every global expert as rank ``rank``
+    sees it.  Experts in ``replicas`` (global ids, in replica order) are held by every rank behind its
+    own ``experts_per_rank`` experts, so their destination is ``rank`` itself."""
+    E = experts_per_rank * world
+    owner, local = owner_and_local(torch.arange(E, dtype=torch.int64), experts_per_rank, world, placement)
+    table = torch.stack([owner, local], dim=1).to(torch.int32)
+    if replicas:
+        if rank is None:
+            raise ValueError("expert_table: replicas need the rank that looks them up")
+        for i, g in enumerate(replicas):
+            table[int(g), 0] = rank
+            table[int(g), 1] = experts_per_rank + i
+    return table
+
+
 def plan_dispatch(topk_ids: torch.Tensor, experts_per_rank: int, world: int, placement: str = "contiguous",
-                  chunks: int = 1, *, host_checks: bool = True) -> DispatchPlan:
+                  chunks: int = 1, *, host_checks: bool = True, table: torch.Tensor | None = None) -> DispatchPlan:
     """One pair per (token, rank that owns at least one of its experts), grouped by (chunk, rank).
 
     With ``host_checks`` (the default) invalid expert ids raise here and the plan comes back
@@ -105,7 +129,11 @@ def plan_dispatch(topk_ids: torch.Tensor, experts_per_rank: int, world: int, pla
     n_bad = bad.sum()
     if host_checks and ids.numel() and int(n_bad) != 0:
         raise ValueError("expert id outside [0, num_global_experts)")
-    dest, local = owner_and_local(ids.clamp(0, max(E - 1, 0)), experts_per_rank, world, placement)   # [M, top_k] each
+    if table is None:
+        dest, local = owner_and_local(ids.clamp(0, max(E - 1, 0)), experts_per_rank, world, placement)   # [M, top_k] each
+    else:
+        t = table.to(device=dev, dtype=torch.int64)[ids.clamp(0, max(E - 1, 0))]                         # [M, top_k, 2]
+        dest, local = t[..., 0], t[..., 1]
     # a slot opens a pair if no earlier slot of its token goes to the same rank
     same = dest.unsqueeze(2) == dest.unsqueeze(1)                                   # [M, j, i]
     earlier = torch.ones(top_k, top_k, dtype=torch.bool, device=dev).tril(-1)       # i < j
@@ -136,52 +164,79 @@ class ExchangeRefused(RuntimeError):
     group with the same message, so that no rank is left waiting in a collective the others skip."""
 
 
+class CountExchange:
+    """The count all-gather in flight: :func:`exchange_counts_begin` enqueues it and an asynchronous
+    copy to pinned host memory; :meth:`finish` waits for that copy only (work enqueued on the
+    stream in between keeps running), checks the whole matrix and returns the split sizes."""
+
+    def __init__(self, host, event, world, rank, chunks):
+        self.host, self.event, self.world, self.rank, self.chunks = host, event, world, rank, chunks
+
+    def finish(self):
+        if self.event is not None:
+            self.event.synchronize()
+        world, rank, chunks = self.world, self.rank, self.chunks
+        host = self.host.view(world, -1).tolist()
+        n = chunks * world
+        # matrix[src][chunk][dst]
+        matrix = [[row[c * world:(c + 1) * world] for c in range(chunks)] for row in host]
+        bad_ids = [int(row[n]) for row in host]
+        caps = [int(row[n + 1]) for row in host]
+        slots = [int(row[n + 2]) for row in host]
+        if any(bad_ids):
+            who = [r for r, b in enumerate(bad_ids) if b]
+            raise ValueError(f"expert id outside [0, num_global_experts) on rank(s) {who}")
+        for src in range(world):
+            flat = [v for c in range(chunks) for v in matrix[src][c]]
+            if min(flat, default=0) < 0:
+                raise ExchangeRefused(f"expert-parallel count exchange: rank {src} reported a negative count {matrix[src]}")
+            if slots[src] >= 0 and sum(flat) > slots[src]:
+                raise ExchangeRefused(f"expert-parallel count exchange: rank {src} reported {sum(flat)} pairs "
+                                      f"for {slots[src]} slots")
+        for dst in range(world):
+            n_in = sum(matrix[src][c][dst] for src in range(world) for c in range(chunks))
+            if caps[dst] >= 0 and n_in > caps[dst]:
+                raise ExchangeRefused(f"rank {dst} would receive {n_in} rows, capacity {caps[dst]}")
+        send_l = matrix[rank]
+        recv_l = [[matrix[src][c][rank] for src in range(world)] for c in range(chunks)]
+        return send_l, recv_l
+
+
+def exchange_counts_begin(send_counts: torch.Tensor, group, n_bad: torch.Tensor | None = None,
+                          capacity: int | None = None, n_slots: int | None = None) -> CountExchange:
+    """All-gather of every rank's [chunks, W] pair-count matrix, its count of invalid expert ids and
+    its receive capacity: one collective and one copy to the host, both only enqueued here."""
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    chunks = send_counts.shape[0]
+    dev = send_counts.device
+    tail = torch.tensor([0, -1 if capacity is None else int(capacity), -1 if n_slots is None else int(n_slots)],
+                        dtype=torch.int64).to(dev, non_blocking=True)
+    if n_bad is not None:
+        tail = tail + torch.nn.functional.pad(n_bad.reshape(1).to(torch.int64), (0, 2))
+    mine = torch.cat([send_counts.to(torch.int64).reshape(-1), tail])          # [chunks * W + 3]
+    everyone = torch.empty((world * mine.numel(),), dtype=torch.int64, device=dev)
+    dist.all_gather_into_tensor(everyone, mine.contiguous(), group=group)
+    if dev.type == "cuda":
+        host = torch.empty(everyone.shape, dtype=torch.int64, pin_memory=True)
+        host.copy_(everyone, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        return CountExchange(host, event, world, rank, chunks)
+    return CountExchange(everyone, None, world, rank, chunks)
+
+
 def exchange_counts(send_counts: torch.Tensor, group, n_bad: torch.Tensor | None = None,
                     capacity: int | None = None, n_slots: int | None = None):
-    """All-gather of every rank's [chunks, W] pair-count matrix, its count of invalid expert ids and
-    its receive capacity: one collective, one host read.  Returns ``(send, recv)`` as nested Python
-    lists indexed [chunk][peer].
+    """The count exchange in one call.  Returns ``(send, recv)`` as nested Python lists indexed
+    [chunk][peer].
 
     Every rank sees the whole W x W matrix, so every rank reaches the SAME verdict before any
     payload moves: an invalid expert id anywhere raises ``ValueError`` everywhere; a negative
     count, a rank that claims more pairs than it has slots, or a rank whose receive capacity would
     be exceeded raises :class:`ExchangeRefused` everywhere.  (What a rank receives is by
     construction what the others send it: both are read from the one gathered matrix.)"""
-    world = dist.get_world_size(group)
-    rank = dist.get_rank(group)
-    chunks = send_counts.shape[0]
-    dev = send_counts.device
-    tail = torch.stack([
-        (torch.zeros((), dtype=torch.int64, device=dev) if n_bad is None else n_bad.reshape(()).to(torch.int64)),
-        torch.tensor(-1 if capacity is None else int(capacity), dtype=torch.int64, device=dev),
-        torch.tensor(-1 if n_slots is None else int(n_slots), dtype=torch.int64, device=dev)])
-    mine = torch.cat([send_counts.to(torch.int64).reshape(-1), tail])          # [chunks * W + 3]
-    everyone = torch.empty((world * mine.numel(),), dtype=torch.int64, device=dev)
-    dist.all_gather_into_tensor(everyone, mine.contiguous(), group=group)
-    host = everyone.view(world, mine.numel()).cpu().tolist()                    # the one host read
-    n = chunks * world
-    # matrix[src][chunk][dst]
-    matrix = [[row[c * world:(c + 1) * world] for c in range(chunks)] for row in host]
-    bad_ids = [int(row[n]) for row in host]
-    caps = [int(row[n + 1]) for row in host]
-    slots = [int(row[n + 2]) for row in host]
-    if any(bad_ids):
-        who = [r for r, b in enumerate(bad_ids) if b]
-        raise ValueError(f"expert id outside [0, num_global_experts) on rank(s) {who}")
-    for src in range(world):
-        flat = [v for c in range(chunks) for v in matrix[src][c]]
-        if min(flat, default=0) < 0:
-            raise ExchangeRefused(f"expert-parallel count exchange: rank {src} reported a negative count {matrix[src]}")
-        if slots[src] >= 0 and sum(flat) > slots[src]:
-            raise ExchangeRefused(f"expert-parallel count exchange: rank {src} reported {sum(flat)} pairs "
-                                  f"for {slots[src]} slots")
-    for dst in range(world):
-        n_in = sum(matrix[src][c][dst] for src in range(world) for c in range(chunks))
-        if caps[dst] >= 0 and n_in > caps[dst]:
-            raise ExchangeRefused(f"rank {dst} would receive {n_in} rows, capacity {caps[dst]}")
-    send_l = matrix[rank]
-    recv_l = [[matrix[src][c][rank] for src in range(world)] for c in range(chunks)]
-    return send_l, recv_l
+    return exchange_counts_begin(send_counts, group, n_bad, capacity, n_slots).finish()
 
 
 class ExpertParallelInt4:
@@ -222,6 +277,58 @@ class ExpertParallelInt4:
         self.last_recv_rows = 0          # pairs (activation rows) received in the last call
         self.last_recv_slots = 0         # expert slots among them (the GEMM work of this rank)
         self.last_send_counts: list[int] = []
+        self.own_packed, self.own_scale = packed, scale
+        self.replicas: list[int] = []    # global ids of the experts every rank holds a copy of
+        self.table = None                # [E, 2] int32 on the weights' device when replicas exist
+
+    # ---- replicas of popular experts -------------------------------------------------
+    def set_replicas(self, global_ids, packed_rep=None, scale_rep=None) -> None:
+        """Install copies of the experts ``global_ids`` (their weights in that order, ``[R, N, K//8]``
+        and ``[R, N, K//group]``) behind this rank's own experts; an empty list removes them."""
+        global_ids = [int(g) for g in global_ids]
+        E = self.e_local * self.world
+        if len(set(global_ids)) != len(global_ids) or any(g < 0 or g >= E for g in global_ids):
+            raise ValueError("set_replicas: ids must be distinct global expert ids")
+        if not global_ids:
+            self.packed, self.scale, self.replicas, self.table = self.own_packed, self.own_scale, [], None
+            return
+        if packed_rep.shape[0] != len(global_ids) or scale_rep.shape[0] != len(global_ids):
+            raise ValueError("set_replicas: one weight slice per replicated expert")
+        self.packed = torch.cat([self.own_packed, packed_rep.to(self.own_packed.device)], dim=0).contiguous()
+        self.scale = torch.cat([self.own_scale, scale_rep.to(self.own_scale.device)], dim=0).contiguous()
+        self.replicas = global_ids
+        self.table = expert_table(self.e_local, self.world, self.placement, self.rank, global_ids).to(
+            self.own_packed.device)
+
+    def rebalance(self, topk_ids: torch.Tensor, n_replicas: int) -> list[int]:
+        """Collective.  Counts how often each global expert is chosen in ``topk_ids`` over all ranks,
+        copies the ``n_replicas`` most popular experts to every rank (a broadcast from each owner)
+        and from then on routes their slots to the token's own rank.  Returns their global ids."""
+        E = self.e_local * self.world
+        dev = self.own_packed.device
+        hist = torch.bincount(topk_ids.reshape(-1).to(device=dev, dtype=torch.int64).clamp(0, E - 1), minlength=E)
+        dist.all_reduce(hist, group=self.group)
+        n = max(0, min(int(n_replicas), E))
+        # most popular first; ties by ascending id so that every rank picks the same set
+        order = torch.argsort(hist.cpu() * E + (E - 1 - torch.arange(E)), descending=True)
+        hot = order[:n].tolist()
+        if not hot:
+            self.set_replicas([])
+            return []
+        owner, local = owner_and_local(torch.tensor(hot, dtype=torch.int64), self.e_local, self.world, self.placement)
+        reps_p, reps_s = [], []
+        for g, o, l in zip(hot, owner.tolist(), local.tolist()):
+            if o == self.rank:
+                pk, sc = self.own_packed[l].clone(), self.own_scale[l].clone()
+            else:
+                pk, sc = torch.empty_like(self.own_packed[0]), torch.empty_like(self.own_scale[0])
+            src = dist.get_global_rank(self.group, o) if self.group is not dist.group.WORLD else o
+            dist.broadcast(pk, src=src, group=self.group)
+            dist.broadcast(sc, src=src, group=self.group)
+            reps_p.append(pk)
+            reps_s.append(sc)
+        self.set_replicas(hot, torch.stack(reps_p), torch.stack(reps_s))
+        return hot
 
     # ---- default CUDA compute ---------------------------------------------------------
     def _partial_cuda(self, rows_A: torch.Tensor, ids: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
@@ -246,18 +353,23 @@ class ExpertParallelInt4:
         top_k = topk_ids.shape[1]
         chunks = max(1, min(self.chunks, M))
         if A.is_cuda:
-            # the plan on the device (three launches, no host read); the one read below also brings
-            # the pair count and the invalid-id count
+            # the plan on the device (three launches, no host read); the one read of the count exchange
+            # also brings the pair count and the invalid-id count.  The send buffer is filled by a
+            # gather whose row count is read on the device, enqueued BEFORE the host waits for the
+            # counts, so the copy runs while the host is still blocked.
             from . import ops
 
             pair_token, _dest, routing, pair_of, counts, info = ops.ep_plan(
-                topk_ids, topk_w, self.e_local, self.world, self.placement, chunks)
-            send_l, recv_l = exchange_counts(counts, self.group, n_bad=info[1], capacity=self.max_recv_rows,
-                                             n_slots=M * top_k)
+                topk_ids, topk_w, self.e_local, self.world, self.placement, chunks, table=self.table)
+            pending = exchange_counts_begin(counts, self.group, n_bad=info[1], capacity=self.max_recv_rows,
+                                            n_slots=M * top_k)
+            send_all = ops.gather_rows(A, pair_token, info[0:1])          # [M * top_k, K]; the first P rows are set
+            send_l, recv_l = pending.finish()
             P = sum(sum(r) for r in send_l)
-            pair_token, send_R = pair_token[:P], routing[:P]
+            pair_token, send_R, send_A = pair_token[:P], routing[:P], send_all[:P]
         else:
-            plan = plan_dispatch(topk_ids, self.e_local, self.world, self.placement, chunks, host_checks=False)
+            plan = plan_dispatch(topk_ids, self.e_local, self.world, self.placement, chunks, host_checks=False,
+                                 table=self.table)
             send_l, recv_l = exchange_counts(plan.send_counts, self.group, n_bad=plan.n_bad,
                                              capacity=self.max_recv_rows, n_slots=M * top_k)
             P = sum(sum(r) for r in send_l)
@@ -267,11 +379,11 @@ class ExpertParallelInt4:
             w_pairs = torch.where(plan.pair_ids >= 0, topk_w.to(torch.float32)[pair_token],
                                   torch.zeros((), dtype=torch.float32, device=A.device))
             send_R = torch.cat([plan.pair_ids, w_pairs.view(torch.int32)], dim=1).contiguous()
+            send_A = A.index_select(0, pair_token)
         n_recv = sum(sum(r) for r in recv_l)
         self.last_recv_rows = n_recv
         self.last_send_counts = [sum(send_l[c][p] for c in range(chunks)) for p in range(self.world)]
 
-        send_A = A.index_select(0, pair_token)
         back = torch.empty((P, self.N), dtype=torch.float32, device=A.device)
         use_async = A.is_cuda and chunks > 1
 
@@ -290,7 +402,8 @@ class ExpertParallelInt4:
             off += n_send
         # ... then per chunk: wait for its rows, expert GEMM + per-row sum, send the fp32 partials home
         back_works = []
-        margin = use_async and self.partial_fn == self._partial_cuda and self.sm_margin > 0
+        fused_partial = A.is_cuda and self.partial_fn == self._partial_cuda
+        margin = use_async and fused_partial and self.sm_margin > 0
         if margin:
             from . import _lib
 
@@ -301,22 +414,27 @@ class ExpertParallelInt4:
                 if use_async:
                     works[c][0].wait()
                     works[c][1].wait()
-                r_ids = rR[:, :top_k].contiguous()
-                r_w = rR[:, top_k:].contiguous().view(torch.float32)
-                partial = self.partial_fn(rA, r_ids, r_w)  # [n_in, N] fp32
+                if fused_partial:
+                    # one C call: routing split, align, gather, grouped GEMM, fp32 sum per received row
+                    partial = ops.moe_int4_w4a16_partial(rA, self.packed, self.scale, rR, group_size=self.group_size)
+                else:
+                    r_ids = rR[:, :top_k].contiguous()
+                    r_w = rR[:, top_k:].contiguous().view(torch.float32)
+                    partial = self.partial_fn(rA, r_ids, r_w)  # [n_in, N] fp32
                 wb = dist.all_to_all_single(back[coff:coff + n_send], partial, send_l[c], recv_l[c], group=self.group,
                                             async_op=use_async)
-                back_works.append((wb, partial, r_ids))
+                back_works.append((wb, partial, rR))
         finally:
             if margin:
                 _lib.set_sm_margin(0)
         if use_async:
             for wb, _p, _i in back_works:
                 wb.wait()
-        self._last_ids = [i for _wb, _p, i in back_works]
+        self._last_routing = [r for _wb, _p, r in back_works]
         return self.reduce_fn(back, pair_of, M, A.dtype)
 
     def count_recv_slots(self) -> int:
         """Expert slots among the rows received in the last call (one host read; diagnostics only)."""
-        self.last_recv_slots = int(sum(int((i >= 0).sum()) for i in self._last_ids))
+        top_k = self._last_routing[0].shape[1] // 2 if self._last_routing else 0
+        self.last_recv_slots = int(sum(int((r[:, :top_k] >= 0).sum()) for r in self._last_routing))
         return self.last_recv_slots

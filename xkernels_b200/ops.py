@@ -45,19 +45,71 @@ def _stream(dev: torch.device) -> int:
     return torch.cuda.current_stream(dev).cuda_stream
 
 
+_retired: list[torch.Tensor] = []
+
+
 def get_workspace(dev: torch.device, nbytes: int, tag: int = 0) -> torch.Tensor:
     """Grow-only per-device scratch buffer shared by calls on one stream.
 
     Calls that overlap on different streams of one device must pass distinct
     ``tag`` values (or serialise): the buffer holds the routing and the fp32
-    partial rows of the call in flight.
+    partial rows of the call in flight.  When a larger call needs a new buffer the old one is kept
+    alive (until :func:`release_workspaces`): a CUDA graph captured earlier, or work still queued
+    on another stream, may hold its address.  A caller that wants to own the memory passes
+    ``workspace=`` to the fused ops instead.
     """
     key = (dev.index if dev.index is not None else torch.cuda.current_device(), tag)
     buf = _workspaces.get(key)
     if buf is None or buf.numel() < nbytes:
-        buf = torch.empty(max(int(nbytes), 1 << 20), dtype=torch.uint8, device=dev)
+        if buf is not None:
+            _retired.append(buf)
+        size = max(int(nbytes), 1 << 20)
+        if buf is not None:
+            size = max(size, 2 * buf.numel())        # geometric growth bounds what the retired buffers hold
+        buf = torch.empty(size, dtype=torch.uint8, device=dev)
         _workspaces[key] = buf
     return buf
+
+
+def _caller_workspace(workspace, fits: bool, nbytes_at_capacity: int, dev: torch.device, nbytes: int) -> torch.Tensor:
+    """The scratch memory of one fused call.
+
+    ``workspace`` None: this package's per-device buffer.  A CUDA ``uint8`` tensor: used as it is
+    (ValueError if it is too small or misaligned).  One of the reference's workspace objects
+    (``MoeInt4Workspace`` / ``MoeMxfp4Workspace``, src/xkernels/ops/moe/workspace.py:159-289):
+    when its ``matches()`` accepted the call (``fits``), the call's scratch lives in a buffer that is
+    created once, sized for the object's capacity, and kept ON the object, so every call through
+    that object sees the same addresses - which is what the reference's workspaces are for (CUDA
+    graph capture, workspace.py:32-35).  The layout of the kernels here (routing, fp32 slot rows,
+    gathered activations) is not the reference's, so its ``scratch`` / ``combine_out`` / ``act``
+    tensors are not reinterpreted.  When ``matches()`` refused, the object is ignored and the call
+    falls back to the per-device buffer, as the reference falls back to fresh allocations
+    (triton/moe_int4_kernel.py:550-558)."""
+    if workspace is None:
+        return get_workspace(dev, nbytes)
+    if isinstance(workspace, torch.Tensor):
+        if workspace.dtype != torch.uint8 or not workspace.is_cuda or workspace.device != dev or not workspace.is_contiguous():
+            raise ValueError("workspace tensor must be a contiguous uint8 tensor on the inputs' device")
+        if workspace.numel() < nbytes or workspace.data_ptr() % 256:
+            raise ValueError(f"workspace tensor needs {nbytes} bytes at a 256-byte aligned address "
+                             f"(got {workspace.numel()} bytes)")
+        return workspace
+    if not fits:
+        return get_workspace(dev, nbytes)
+    buf = getattr(workspace, "_xkb200_scratch", None)
+    if buf is None or buf.numel() < nbytes or buf.device != dev:
+        buf = torch.empty(max(int(nbytes_at_capacity), int(nbytes)), dtype=torch.uint8, device=dev)
+        workspace._xkb200_scratch = buf
+    return buf
+
+
+def check_workspace_status(workspace) -> None:
+    """As :func:`check_status`, for a call that was given ``workspace=``."""
+    buf = workspace if isinstance(workspace, torch.Tensor) else getattr(workspace, "_xkb200_scratch", None)
+    if buf is None:
+        return
+    with torch.cuda.device(buf.device):
+        _lib.check(_lib.load().xkb_workspace_status(buf.data_ptr(), _stream(buf.device)), "xkb_workspace_status")
 
 
 def check_status(dev=None, tag: int = 0) -> None:
@@ -73,7 +125,9 @@ def check_status(dev=None, tag: int = 0) -> None:
 
 
 def release_workspaces() -> None:
+    """Drop the per-device buffers (only when no captured graph or queued work still uses them)."""
     _workspaces.clear()
+    _retired.clear()
 
 
 # ---------------------------------------------------------------------------
@@ -106,20 +160,37 @@ def moe_align_block_size(topk_ids, block_size, num_experts, truncate=True, works
         emap = expert_map.to(device=dev, dtype=torch.int32).contiguous()
     max_pad = numel + (num_experts + 1) * (block_size - 1)
     max_blocks = -(-max_pad // block_size)
+    # A reference MoeAlignWorkspace (src/xkernels/ops/moe/workspace.py:85-151) that matches the call:
+    # the three outputs are written INTO its buffers (address-stable, the reference's contract at
+    # triton/align_kernel.py:198-213,245-250) and this kernel's own scratch is kept on the object.
+    use_ws = False
+    if workspace is not None and hasattr(workspace, "matches") and topk_ids.dim() == 2:
+        use_ws = bool(workspace.matches(topk_ids.shape[0], topk_ids.shape[1], num_experts, block_size, device=dev))
     with torch.cuda.device(dev):
-        sorted_ids = torch.empty(max_pad, dtype=torch.int32, device=dev)
-        expert_ids = torch.empty(max(max_blocks, 1), dtype=torch.int32, device=dev)
-        num_post = torch.empty(1, dtype=torch.int32, device=dev)
-        if max_blocks == 0:
-            expert_ids.zero_()
         ws_bytes = int(lib.xkb_moe_align_workspace_bytes(numel, num_experts))
-        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+        if use_ws:
+            sorted_ids, expert_ids, num_post = workspace.sorted_ids, workspace.expert_ids, workspace.num_post
+            if max_blocks == 0:
+                expert_ids[:1].zero_()
+            ws = getattr(workspace, "_xkb200_scratch", None)
+            if ws is None or ws.numel() < ws_bytes:
+                cap = int(lib.xkb_moe_align_workspace_bytes(max(workspace.sorted_ids.numel(), numel), num_experts))
+                ws = torch.empty(max(cap, ws_bytes, 256), dtype=torch.uint8, device=dev)
+                workspace._xkb200_scratch = ws
+        else:
+            sorted_ids = torch.empty(max_pad, dtype=torch.int32, device=dev)
+            expert_ids = torch.empty(max(max_blocks, 1), dtype=torch.int32, device=dev)
+            num_post = torch.empty(1, dtype=torch.int32, device=dev)
+            if max_blocks == 0:
+                expert_ids.zero_()
+            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
         _lib.check(
             lib.xkb_moe_align_block_size(
                 _ptr(ids), numel, num_experts, block_size, _ptr(emap),
                 0 if emap is None else emap.numel(), _ptr(sorted_ids), _ptr(expert_ids),
-                _ptr(num_post), 0, _ptr(ws), ws_bytes, _stream(dev)),
+                _ptr(num_post), 0, _ptr(ws), ws.numel(), _stream(dev)),
             "xkb_moe_align_block_size")
+    sorted_ids = sorted_ids[:max_pad]
     if truncate:
         used = int(num_post.item()) // block_size
         expert_ids = expert_ids[: max(used, 1)]
@@ -233,9 +304,13 @@ def fused_moe_int4_w4a16(A, packed, scale, topk_ids, topk_w, group_size=32, mul_
     """INT4 W4A16 grouped fused-MoE GEMM ``out[m] = sum_j w[m,j] * (A[m] @ W[e_mj]^T)``.
 
     Signature of the reference backends (src/xkernels/ops/moe/reference.py:22-33,
-    triton/moe_int4_kernel.py:438-449).  ``fused_combine`` and ``workspace`` are
-    accepted for API parity: the combine is always the fixed-order fp32 reduce
-    and scratch memory comes from this package's per-device buffer.
+    triton/moe_int4_kernel.py:438-449).  ``fused_combine`` is accepted for API
+    parity: the combine is always the fixed-order fp32 reduce.  ``workspace``:
+    None (this package's per-device buffer), a CUDA uint8 tensor, or the
+    reference's ``MoeInt4Workspace`` (see :func:`_caller_workspace`): with the
+    latter two every call runs at the same addresses, e.g. under a CUDA graph.
+    The tcgen05 kernels never wait without a limit; after a call
+    :func:`check_status` (or :func:`check_workspace_status`) tells whether one gave up.
     ``expert_map`` selects the replicated expert-parallel mode (partial output).
     ``path``: ``"auto"`` | ``"simt"`` | ``"tc"``.
     """
@@ -265,7 +340,13 @@ def fused_moe_int4_w4a16(A, packed, scale, topk_ids, topk_w, group_size=32, mul_
     with torch.cuda.device(dev):
         out = torch.empty((M, N), dtype=A.dtype, device=dev)
         ws_bytes = int(lib.xkb_fused_moe_int4_w4a16_workspace_bytes(M, N, K, E, top_k, _DT[A.dtype]))
-        ws = get_workspace(dev, ws_bytes)
+        fits, cap_bytes = False, ws_bytes
+        if workspace is not None and hasattr(workspace, "matches"):
+            fits = bool(workspace.matches(M, top_k, N, dtype=A.dtype, device=dev))
+            if fits:   # capacity of the object = rows of its combine buffer (workspace.py:199-213)
+                cap_bytes = int(lib.xkb_fused_moe_int4_w4a16_workspace_bytes(int(workspace.combine_out.shape[0]), N, K, E,
+                                                                             top_k, _DT[A.dtype]))
+        ws = _caller_workspace(workspace, fits, cap_bytes, dev, ws_bytes)
         _lib.check(
             lib.xkb_fused_moe_int4_w4a16(
                 _ptr(A), _DT[A.dtype], _ptr(packed), _ptr(scale), _ptr(ids), _ptr(tw), _ptr(emap),
@@ -316,7 +397,15 @@ def fused_moe_mxfp4(A, w13, w13_scale, w2, w2_scale, topk_ids, topk_w, b13=None,
     with torch.cuda.device(dev):
         out = torch.empty((M, hidden), dtype=A.dtype, device=dev)
         ws_bytes = int(lib.xkb_fused_moe_mxfp4_workspace_bytes(M, hidden, ispp, E, top_k))
-        ws = get_workspace(dev, ws_bytes)
+        fits, cap_bytes = False, ws_bytes
+        if workspace is not None and hasattr(workspace, "out") and hasattr(workspace, "act"):
+            # matches() of MoeMxfp4Workspace wants the align block of ITS kernel; what matters here is
+            # that the object was built for this problem: same ispp / hidden / dtype, enough rows
+            fits = (workspace.act.shape[1] == ispp and workspace.out.shape[1] == hidden and workspace.out.shape[0] >= M
+                    and workspace.act.dtype == A.dtype and workspace.act.device == dev)
+            if fits:
+                cap_bytes = int(lib.xkb_fused_moe_mxfp4_workspace_bytes(int(workspace.out.shape[0]), hidden, ispp, E, top_k))
+        ws = _caller_workspace(workspace, fits, cap_bytes, dev, ws_bytes)
         _lib.check(
             lib.xkb_fused_moe_mxfp4(
                 _ptr(A), _DT[A.dtype], _ptr(w13), _ptr(w13_scale), _ptr(w2), _ptr(w2_scale), _ptr(ids),
@@ -361,6 +450,44 @@ def moe_int4_w4a16_rows(A, packed, scale, topk_ids, topk_w=None, group_size=32, 
     return rows
 
 
+def moe_int4_w4a16_partial(A, packed, scale, routing, group_size=32, *, out=None, path="auto"):
+    """Expert side of the all-to-all mode in one C call: ``A [R, K]`` received rows, ``routing
+    [R, 2*top_k]`` int32 (local expert ids, -1 = elsewhere, then the routing weights' bit patterns)
+    -> ``[R, N]`` fp32, per row the weighted sum over its local experts in ascending slot order."""
+    lib = _lib.load()
+    dev = _require_cuda("moe_int4_w4a16_partial", A, packed, scale, routing, out)
+    if A.dtype not in _DT:
+        raise TypeError(f"moe_int4_w4a16_partial: A must be bf16 or fp32, got {A.dtype}")
+    if routing.dtype != torch.int32 or routing.dim() != 2 or routing.shape[1] % 2:
+        raise TypeError("moe_int4_w4a16_partial: routing must be int32 [R, 2*top_k]")
+    A, packed, routing = A.contiguous(), packed.contiguous(), routing.contiguous()
+    scale = scale if scale.dtype == torch.bfloat16 else scale.to(torch.bfloat16)
+    scale = scale.contiguous()
+    R, K = A.shape
+    E, N, _ = packed.shape
+    top_k = routing.shape[1] // 2
+    if routing.shape[0] != R:
+        raise ValueError("moe_int4_w4a16_partial: one routing row per received row")
+    pcode = {"auto": _lib.PATH_AUTO, "simt": _lib.PATH_SIMT, "tc": _lib.PATH_TC}[path]
+    if path != "simt":
+        _check_int4_scales(scale)
+    with torch.cuda.device(dev):
+        if out is None:
+            out = torch.empty((R, N), dtype=torch.float32, device=dev)
+        if out.dtype != torch.float32 or tuple(out.shape) != (R, N) or not out.is_contiguous():
+            raise ValueError("moe_int4_w4a16_partial: out must be a contiguous fp32 [R, N] tensor")
+        if R == 0:
+            return out
+        ws_bytes = int(lib.xkb_moe_int4_w4a16_partial_workspace_bytes(R, N, K, E, top_k, _DT[A.dtype]))
+        ws = get_workspace(dev, ws_bytes)
+        _lib.check(
+            lib.xkb_moe_int4_w4a16_partial(_ptr(A), _DT[A.dtype], _ptr(packed), _ptr(scale), _ptr(routing), _ptr(out),
+                                           R, N, K, E, top_k, int(group_size), pcode, _ptr(ws), ws.numel(),
+                                           _stream(dev)),
+            "xkb_moe_int4_w4a16_partial")
+    return out
+
+
 def moe_gather_sum_reduce(rows, row_index, w, out_dtype=torch.bfloat16):
     """``out[m] = sum_k w[m,k] * rows[row_index[m,k]]`` in fp32, ascending k (index < 0 skips)."""
     lib = _lib.load()
@@ -381,14 +508,36 @@ def moe_gather_sum_reduce(rows, row_index, w, out_dtype=torch.bfloat16):
     return out
 
 
+def gather_rows(src, index, count=None, out=None):
+    """``out[p] = src[index[p]]`` for ``p < count[0]`` (``count`` a device int32 tensor; all of
+    ``index`` if None).  ``out`` (``[>= len(index), row]``) may be a preallocated buffer; rows at and
+    beyond the count are left untouched."""
+    lib = _lib.load()
+    dev = _require_cuda("gather_rows", src, index, count, out)
+    src = src.contiguous()
+    idx = index if index.dtype == torch.int32 else index.to(torch.int32)
+    idx = idx.contiguous()
+    row_bytes = src.shape[1] * src.element_size()
+    n = idx.numel()
+    with torch.cuda.device(dev):
+        if out is None:
+            out = torch.empty((n, src.shape[1]), dtype=src.dtype, device=dev)
+        if out.dtype != src.dtype or out.shape[1] != src.shape[1] or out.shape[0] < n or not out.is_contiguous():
+            raise ValueError("gather_rows: out must be a contiguous [>= len(index), row] tensor of src's dtype")
+        _lib.check(lib.xkb_gather_rows(_ptr(src), src.shape[0], row_bytes, _ptr(idx), _ptr(count), n, _ptr(out),
+                                       _stream(dev)), "xkb_gather_rows")
+    return out
+
+
 _PLACEMENT = {"contiguous": 0, "round_robin": 1, "snake": 2}
 
 
-def ep_plan(topk_ids, topk_w, experts_per_rank, world, placement="contiguous", chunks=1):
+def ep_plan(topk_ids, topk_w, experts_per_rank, world, placement="contiguous", chunks=1, table=None):
     """Device-side dispatch plan of the all-to-all expert-parallel mode (``xkb_ep_plan``): no host
     read.  Returns ``(pair_token, pair_dest, routing, pair_of, counts, info)`` with the per-pair
     arrays sized ``M * top_k`` (the first ``info[0]`` entries are the pairs); see
-    ``xkernels_b200/ep.py:plan_dispatch`` for the meaning of each."""
+    ``xkernels_b200/ep.py:plan_dispatch`` for the meaning of each.  ``table`` (``[E, 2]`` int32 on the
+    device: destination rank and expert index there, per global expert) overrides ``placement``."""
     lib = _lib.load()
     dev = _require_cuda("ep_plan", topk_ids, topk_w)
     if placement not in _PLACEMENT:
@@ -397,6 +546,10 @@ def ep_plan(topk_ids, topk_w, experts_per_rank, world, placement="contiguous", c
     w = topk_w.to(torch.float32).contiguous()
     M, top_k = ids.shape
     numel = M * top_k
+    if table is not None:
+        if table.dtype != torch.int32 or tuple(table.shape) != (int(experts_per_rank) * int(world), 2) or not table.is_cuda:
+            raise ValueError("ep_plan: table must be a CUDA int32 tensor of shape [experts_per_rank * world, 2]")
+        table = table.contiguous()
     with torch.cuda.device(dev):
         pair_token = torch.empty((numel,), dtype=torch.int32, device=dev)
         pair_dest = torch.empty((numel,), dtype=torch.int32, device=dev)
@@ -408,7 +561,7 @@ def ep_plan(topk_ids, topk_w, experts_per_rank, world, placement="contiguous", c
         ws = get_workspace(dev, ws_bytes, tag=1)     # not the fused ops' buffer: that one starts with their status words
         _lib.check(
             lib.xkb_ep_plan(_ptr(ids), _ptr(w), M, top_k, int(experts_per_rank), int(world),
-                            _PLACEMENT[placement], int(chunks), _ptr(pair_token), _ptr(pair_dest),
+                            _PLACEMENT[placement], _ptr(table), int(chunks), _ptr(pair_token), _ptr(pair_dest),
                             _ptr(routing), _ptr(pair_of), _ptr(counts), _ptr(info), _ptr(ws), ws.numel(),
                             _stream(dev)),
             "xkb_ep_plan")

@@ -111,3 +111,24 @@ def install(overlay_dir: str | Path | None = None) -> Path:
     input_gen.register_input_gen("moe_mxfp4@1.0.0", _mxfp4_input_gen)
     _installed_root = dest
     return dest
+
+
+def write_back(card_id: str, *, shape: dict, dtype: str, source: str, ms: float | None = None,
+               tflops: float | None = None, achieved_bw_pct: float | None = None, knobs: dict | None = None,
+               arch: str = "nvidia_sm100", cards_dir: str | Path | None = None) -> dict:
+    """Record one measurement on a card of this package through the reference's OWN
+    ``record_measurement`` (src/xkernels/registry/writeback.py:30-93: a source and an arch are
+    mandatory, an entry for the same (arch, shape, dtype, knobs) point is replaced), then copy the
+    updated card file from the overlay registry to ``cards_dir`` (default: this package's
+    ``registry/impls``), so that ``perf.measured`` in the repository is written by code."""
+    install()
+    from xkernels.registry import schemas
+    from xkernels.registry.writeback import record_measurement
+
+    res = record_measurement(card_id, arch, shape, dtype, source, knobs=knobs, tflops=tflops,
+                             achieved_bw_pct=achieved_bw_pct, ms=ms)
+    name = card_id.split("@", 1)[0] + ".card.json"
+    dest_dir = Path(cards_dir) if cards_dir is not None else OVERLAY_SRC / "impls"
+    dest_dir.mkdir(parents=True, exist_ok=True)
+    shutil.copyfile(Path(schemas.registry_root()) / "impls" / name, dest_dir / name)
+    return res
