@@ -499,6 +499,41 @@ def extras(dev, peaks):
         out["int4_prefill"] = {"error": repr(exc)[:300]}
     torch.cuda.empty_cache()
     try:
+        # The two expert-GEMM shapes of the reference's own INT4 benchmark (E=48, top_k=8, group 32;
+        # meta/benchmarks/bench_moe_int4_w4a16.py:3-12,88-91): gate_up N=4096 K=7168 and the
+        # down projection N=7168 K=2048, at decode and prefill batch sizes.  Small batches are
+        # weight-stream bound (fraction of the measured HBM peak), large ones tensor bound.
+        table = {}
+        for name, (N, K) in {"gate_up_N4096_K7168": (4096, 7168), "down_N7168_K2048": (7168, 2048)}.items():
+            packed, scale = synth.int4_weights(48, N, K, 32, seed=11, device=dev)
+            rows = {}
+            for M in (1, 16, 64, 512, 4096):
+                cfg = synth.Int4Config(name, M=M, K=K, N=N, E=48, top_k=8)
+                A = synth.activations(M, K, seed=M, device=dev)
+                ids, w = synth.routing(M, 48, 8, seed=M + 3, device=dev)
+                fn = lambda: xkb.fused_moe_int4_w4a16(A, packed, scale, ids, w)  # noqa: E731
+                for _ in range(3):
+                    fn()
+                torch.cuda.synchronize()
+                n = 20 if M <= 512 else 5
+                _lib.gemm_timer_enable(n)
+                ms = time_call(fn, 0, n)
+                g = _lib.gemm_timer_read()
+                _lib.gemm_timer_enable(0)
+                gm = sum(g) / len(g)
+                b = synth.int4_algorithmic_bytes(cfg, int(torch.unique(ids).numel()))
+                fl = synth.int4_flops(cfg)
+                rows[f"M={M}"] = {"us_per_call": ms * 1e3, "gemm_kernel_us": gm * 1e3,
+                                  "kernel_frac_of_hbm_peak": b / (gm * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                                  "kernel_frac_of_bf16_peak": fl / (gm * 1e-3) / 1e12 / peaks["bf16_tflops"]}
+            ops.check_status(dev)
+            table[name] = rows
+            del packed, scale
+        out["int4_kimi_shapes"] = table
+    except Exception as exc:  # noqa: BLE001
+        out["int4_kimi_shapes"] = {"error": repr(exc)[:300]}
+    torch.cuda.empty_cache()
+    try:
         cfg = synth.CONFIGS["mxfp4_decode"]
         d = synth.make_mxfp4(cfg, seed=1729, device=dev)
         n_active = int(torch.unique(d["topk_ids"]).numel())

@@ -153,6 +153,33 @@ int xkb_fused_moe_int4_w4a16(const void* A, int a_dtype, const int32_t* packed,
                              int64_t workspace_bytes, void* stream);
 
 /* ------------------------------------------------------------------------
+ * fused_moe_int4_ffn: one expert layer made of two INT4 W4A16 GEMMs,
+ *   out[m] = sum_j bf16( w[m,j] * (act_mj @ dequant(W2[e_mj])^T) ),
+ *   act_mj = bf16( silu(gate) * up ),  [gate | up] = bf16( A[m] @ dequant(W13[e_mj])^T )
+ * in one call: align -> gate_up GEMM with fused SwiGLU -> down GEMM -> combine.
+ * The reference has no such op; it stands for what a caller of the reference
+ * composes from fused_moe_int4_w4a16 (ops/moe/interface.py:19-32) twice, with
+ * top_k = 1 over the slots, and moe_sum_reduce (ops/moe/sum_reduce.py:20-39),
+ * and it rounds where that composition rounds.  The two shapes are those of
+ * meta/benchmarks/bench_moe_int4_w4a16.py:3-12 (gate_up N = 2*inter, K = hidden;
+ * down N = hidden, K = inter).  w13_packed [E, 2*inter, hidden/8] int32 with the
+ * gate rows first, w13_scale [E, 2*inter, hidden/group] bf16, w2_packed
+ * [E, hidden, inter/8], w2_scale [E, hidden, inter/group]; swiglu_limit <= 0:
+ * no clamp, else gate <= limit and |up| <= limit as in fused_moe_mxfp4.
+ * ---------------------------------------------------------------------- */
+int64_t xkb_fused_moe_int4_ffn_workspace_bytes(int64_t M, int64_t hidden,
+                                               int64_t inter, int E, int top_k,
+                                               int a_dtype);
+int xkb_fused_moe_int4_ffn(const void* A, int a_dtype, const int32_t* w13_packed,
+                           const void* w13_scale, const int32_t* w2_packed,
+                           const void* w2_scale, const int32_t* topk_ids,
+                           const float* topk_w, const int32_t* expert_map,
+                           int num_map, void* out, int64_t M, int64_t hidden,
+                           int64_t inter, int E, int top_k, int group_size,
+                           float swiglu_limit, int path, void* workspace,
+                           int64_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------
  * Expert-parallel building blocks (all-to-all mode).  The reference has no
  * all-to-all; its expert-parallel contract is "per-rank partials sum to the
  * dense result" (tests/test_moe_int4_ep.py:152-177).  These two calls are the

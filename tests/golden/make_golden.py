@@ -164,6 +164,36 @@ def gen_mxfp4_tensor_core_shape():
     save_case("mxfp4_tc_scales", {**kw, "swiglu_limit": 10.0, "out": out})
 
 
+def gen_int4_ffn():
+    """The reference's own ops composed into a two-GEMM expert layer (what oracle.moe_int4_ffn restates):
+    moe_w4a16_ref over the slots, SwiGLU, moe_w4a16_ref with the routing weights, moe_sum_reduce_ref."""
+    import torch.nn.functional as F
+
+    for name, (M, hidden, inter, E, top_k, dt, limit) in {
+        "int4_ffn_small": (6, 64, 32, 4, 2, torch.bfloat16, None),
+        "int4_ffn_tc": (24, 256, 256, 4, 3, torch.bfloat16, 7.0),
+        "int4_ffn_fp32": (5, 64, 64, 3, 2, torch.float32, None),
+    }.items():
+        g = torch.Generator().manual_seed(SEED + M)
+        A = torch.randn(M, hidden, generator=g).to(dt)
+        w13, s13 = synth.int4_weights(E, 2 * inter, hidden, 32, seed=SEED + 50)
+        w2, s2 = synth.int4_weights(E, hidden, inter, 32, seed=SEED + 60)
+        ids = torch.stack([torch.randperm(E, generator=g)[:top_k] for _ in range(M)]).to(torch.int32)
+        w = torch.rand(M, top_k, generator=g, dtype=torch.float32)
+        slot_ids = ids.reshape(-1, 1)
+        rows1 = moe_w4a16_ref(A.repeat_interleave(top_k, dim=0), w13, s13, slot_ids, torch.ones(M * top_k, 1),
+                              group_size=32, mul_routed_weight=False)
+        gate, up = rows1.float().chunk(2, dim=-1)
+        if limit is not None:
+            gate = torch.clamp(gate, max=limit)
+            up = torch.clamp(up, min=-limit, max=limit)
+        act = (F.silu(gate) * up).to(dt)
+        rows2 = moe_w4a16_ref(act, w2, s2, slot_ids, w.reshape(-1, 1), group_size=32, mul_routed_weight=True)
+        out = moe_sum_reduce_ref(rows2.view(M, top_k, hidden))
+        save_case(name, {"A": A, "w13_packed": w13, "w13_scale": s13, "w2_packed": w2, "w2_scale": s2, "topk_ids": ids,
+                         "topk_w": w, "swiglu_limit": 0.0 if limit is None else limit, "out": out})
+
+
 # ---- moe_sum_reduce ---------------------------------------------------------------
 def gen_sum_reduce():
     for i, pt in enumerate(sweep_points("moe_sum_reduce")):
@@ -211,6 +241,10 @@ if __name__ == "__main__":
         gen_topk_softmax()
         print("wrote the topk_softmax cases")
         sys.exit(0)
+    if "--only-int4-ffn" in sys.argv:          # add the two-GEMM INT4 cases without touching the others
+        gen_int4_ffn()
+        print("wrote the int4_ffn cases")
+        sys.exit(0)
     if "--only-mxfp4-tc" in sys.argv:          # add the 512-multiple MXFP4 case without touching the others
         gen_mxfp4_tensor_core_shape()
         print("wrote mxfp4_tc_scales")
@@ -219,6 +253,7 @@ if __name__ == "__main__":
     gen_int4()
     gen_mxfp4()
     gen_mxfp4_tensor_core_shape()
+    gen_int4_ffn()
     gen_sum_reduce()
     gen_topk_softmax()
     (GOLDEN_DIR / "manifest.json").write_text(json.dumps(manifest, indent=1, sort_keys=True))

@@ -134,6 +134,21 @@ def test_decode_config_full_output_and_properties(cuda_device):
     assert_within(out2.float(), 2 * out.float(), 1.6e-2, 1e-2, what="linearity in topk_w")
 
 
+@pytest.mark.parametrize("M", [1, 64])
+def test_down_projection_shape_against_oracle(M, cuda_device):
+    """The second expert-GEMM shape of the reference's INT4 benchmark (N=7168, K=2048, E=48, top_k=8:
+    meta/benchmarks/bench_moe_int4_w4a16.py:8-12,90-91), where a tile is only eight 256-K stages
+    long: the whole output against the oracle."""
+    from xkernels_b200 import ops
+
+    cfg = synth.Int4Config("down", M=M, K=2048, N=7168, E=48, top_k=8)
+    d = synth.make_int4(cfg, seed=77, device=cuda_device)
+    out = xkb.fused_moe_int4_w4a16(d["A"], d["packed"], d["scale"], d["topk_ids"], d["topk_w"])
+    ops.check_status(cuda_device)
+    want = oracle.moe_w4a16(d["A"].cpu(), d["packed"].cpu(), d["scale"].cpu(), d["topk_ids"].cpu(), d["topk_w"].cpu(), 32)
+    assert_within(out, want, *TOL[torch.bfloat16], what=f"down projection shape, M={M}")
+
+
 def prefill_token_sample(topk_ids: torch.Tensor, E: int, block: int, n_tokens: int, seed: int) -> torch.Tensor:
     """Token rows to check at the prefill configuration: for every expert the tokens whose slots sit
     at the first and the last position of the expert's sorted run (so the first and the last,

@@ -158,3 +158,17 @@ def test_topk_softmax_tie_rule_and_argument_check():
         oracle.topk_softmax(torch.zeros(2, 4), 5)
     with pytest.raises(ValueError):
         oracle.topk_softmax(torch.zeros(2, 4), 0)
+
+
+@pytest.mark.parametrize("name", ["int4_ffn_small", "int4_ffn_tc", "int4_ffn_fp32"])
+def test_int4_ffn_matches_the_reference_composition(name):
+    """oracle.moe_int4_ffn against fixtures made by composing the reference's own ops
+    (moe_w4a16_ref twice + moe_sum_reduce_ref, tests/golden/make_golden.py:gen_int4_ffn)."""
+    c = load_case(name)
+    args = (c["A"], c["w13_packed"], c["w13_scale"], c["w2_packed"], c["w2_scale"], c["topk_ids"], c["topk_w"], 32)
+    out = oracle.moe_int4_ffn(*args, swiglu_limit=c["swiglu_limit"] or None, literal=True)
+    assert out.dtype == c["out"].dtype and torch.equal(out, c["out"])
+    # the grouped form used for larger shapes: same arithmetic, another summation order in the matmuls
+    grouped = oracle.moe_int4_ffn(*args, swiglu_limit=c["swiglu_limit"] or None)
+    tol = (2e-2, 1e-2) if c["A"].dtype == torch.bfloat16 else (1e-4, 1e-5)
+    assert oracle.count_violations(grouped, c["out"], *tol) == 0

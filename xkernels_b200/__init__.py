@@ -6,12 +6,15 @@ Public callables (same argument names and meaning as the reference backends):
 * :func:`fused_moe_int4_w4a16`
 * :func:`fused_moe_mxfp4`
 * :func:`moe_sum_reduce`
+* :func:`topk_softmax` (the router in front of the path)
+* :func:`fused_moe_int4_ffn` (two INT4 GEMMs with SwiGLU between them, one call)
 
 ``plugin.install()`` registers them as the ``backend="cuda"`` cards of an
 installed ``xkernels`` package.
 """
 
 from .ops import (  # noqa: F401
+    fused_moe_int4_ffn,
     fused_moe_int4_w4a16,
     fused_moe_mxfp4,
     moe_align_block_size,
@@ -20,6 +23,7 @@ from .ops import (  # noqa: F401
 )
 
 __all__ = [
+    "fused_moe_int4_ffn",
     "fused_moe_int4_w4a16",
     "fused_moe_mxfp4",
     "moe_align_block_size",

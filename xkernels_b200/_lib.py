@@ -45,6 +45,12 @@ SIGNATURES = {
         [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
          c_int64, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int64, c_void_p],
     ),
+    "xkb_fused_moe_int4_ffn_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64, c_int, c_int, c_int]),
+    "xkb_fused_moe_int4_ffn": (
+        c_int,
+        [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+         c_int64, c_int64, c_int64, c_int, c_int, c_int, c_float, c_int, c_void_p, c_int64, c_void_p],
+    ),
     "xkb_moe_int4_w4a16_rows": (
         c_int,
         [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,

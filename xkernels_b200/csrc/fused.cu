@@ -253,6 +253,73 @@ extern "C" int xkb_moe_int4_w4a16_partial(const void* A, int a_dtype, const int3
 }
 
 // ---------------------------------------------------------------------------
+// INT4 two-GEMM expert layer
+// ---------------------------------------------------------------------------
+extern "C" int64_t xkb_fused_moe_int4_ffn_workspace_bytes(int64_t M, int64_t hidden, int64_t inter, int E, int top_k,
+                                                          int a_dtype) {
+  (void)a_dtype;
+  if (M < 0 || hidden < 0 || inter < 0 || E < 0 || top_k < 0) return -1;
+  const int64_t numel = M * top_k;
+  int64_t total = routing_bytes(numel, E);
+  total += align_up(numel * hidden * 4, 256);                                   // fp32 slot rows of the down GEMM
+  total += align_up(numel * 2 * inter * 4, 256);                                // fp32 gate_up slot rows (generic path)
+  total += align_up(routing_max_pad(numel, E, kMaxBlock) * inter * 4, 256);     // activations (bf16 by position, or by slot)
+  total += int4_tc_workspace_bytes(numel, hidden, hidden, E);                   // gathered input activations
+  return total + 256;
+}
+
+extern "C" int xkb_fused_moe_int4_ffn(const void* A, int a_dtype, const int32_t* w13_packed, const void* w13_scale,
+                                      const int32_t* w2_packed, const void* w2_scale, const int32_t* topk_ids,
+                                      const float* topk_w, const int32_t* expert_map, int num_map, void* out,
+                                      int64_t M, int64_t hidden, int64_t inter, int E, int top_k, int group_size,
+                                      float swiglu_limit, int path, void* workspace, int64_t workspace_bytes,
+                                      void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  XKB_REQUIRE(a_dtype == XKB_BF16 || a_dtype == XKB_F32, "fused_moe_int4_ffn: bad a_dtype %d", a_dtype);
+  XKB_REQUIRE(M >= 0 && hidden >= 0 && inter >= 0 && E >= 0 && top_k >= 0, "fused_moe_int4_ffn: negative dim");
+  XKB_REQUIRE(group_size > 0 && group_size % 8 == 0 && hidden % group_size == 0 && inter % group_size == 0,
+              "fused_moe_int4_ffn: hidden and inter must be multiples of group_size, group_size of 8 "
+              "(hidden=%lld inter=%lld group_size=%d)", (long long)hidden, (long long)inter, group_size);
+  XKB_REQUIRE(path == XKB_PATH_AUTO || path == XKB_PATH_SIMT || path == XKB_PATH_TC, "fused_moe_int4_ffn: bad path %d", path);
+  if (M == 0 || hidden == 0) return XKB_OK;
+  XKB_REQUIRE(A && w13_packed && w13_scale && w2_packed && w2_scale && topk_ids && topk_w && out,
+              "fused_moe_int4_ffn: null pointer argument");
+  const int64_t need = xkb_fused_moe_int4_ffn_workspace_bytes(M, hidden, inter, E, top_k, a_dtype);
+  if (workspace == nullptr || workspace_bytes < need)
+    return fail(XKB_ERR_WORKSPACE, "fused_moe_int4_ffn: workspace of %lld bytes needed, %lld given", (long long)need,
+                (long long)workspace_bytes);
+  XKB_REQUIRE(reinterpret_cast<uintptr_t>(workspace) % 256 == 0, "workspace must be 256-byte aligned");
+
+  const int64_t numel = M * top_k;
+  Carver carve(workspace);
+  RoutingBuffers rb = carve_routing(carve, numel, E);
+  float* scratch = carve.take<float>(numel * hidden);
+  float* rows1 = carve.take<float>(numel * 2 * inter);
+  void* act = carve.take<float>(routing_max_pad(numel, E, kMaxBlock) * inter);
+  void* tc_ws = carve.take<char>(int4_tc_workspace_bytes(numel, hidden, hidden, E));
+
+  const bool tc_fit = int4_ffn_tc_supported(a_dtype, M, hidden, inter, E, top_k, group_size);
+  if (path == XKB_PATH_TC && !tc_fit)
+    return fail(XKB_ERR_ARG, "fused_moe_int4_ffn: shape not supported by the tcgen05 path (needs bf16 A, "
+                             "hidden %% 256 == 0, inter %% 256 == 0, group_size 32)");
+  const bool use_tc = (path == XKB_PATH_TC) || (path == XKB_PATH_AUTO && tc_fit);
+  const int block = use_tc ? int4_tc_block(numel, E) : kSimtBlock;
+  Routing r = make_routing(rb, numel, E, block);
+  XKB_CHECK_CUDA(cudaMemsetAsync(rb.status, 0, sizeof(int), stream));
+  int rc = launch_align(topk_ids, numel, E, block, expert_map, num_map, rb.sorted_ids, rb.expert_ids, rb.num_post,
+                        rb.expert_off, rb.align_ws, rb.align_ws_bytes, stream);
+  if (rc != XKB_OK) return rc;
+  if (use_tc)
+    rc = launch_int4_ffn_tc(A, w13_packed, w13_scale, w2_packed, w2_scale, r, topk_w, static_cast<__nv_bfloat16*>(act),
+                            scratch, hidden, inter, E, top_k, swiglu_limit, tc_ws, rb.status, stream);
+  else
+    rc = launch_int4_ffn_simt(A, a_dtype, w13_packed, w13_scale, w2_packed, w2_scale, r, topk_ids, expert_map, num_map,
+                              E, topk_w, rows1, act, scratch, hidden, inter, top_k, group_size, swiglu_limit, stream);
+  if (rc != XKB_OK) return rc;
+  return launch_combine(scratch, topk_ids, expert_map, num_map, E, out, a_dtype, M, top_k, hidden, stream);
+}
+
+// ---------------------------------------------------------------------------
 // MXFP4
 // ---------------------------------------------------------------------------
 extern "C" int64_t xkb_fused_moe_mxfp4_workspace_bytes(int64_t M, int64_t hidden, int64_t ispp, int E,

@@ -57,7 +57,7 @@ int4_simt_kernel(const TA* __restrict__ A, const int32_t* __restrict__ packed,
                  const __nv_bfloat16* __restrict__ scale, const int32_t* __restrict__ sorted_ids,
                  const int32_t* __restrict__ expert_ids, const int32_t* __restrict__ num_post,
                  const float* __restrict__ topk_w, float* __restrict__ scratch, int64_t numel,
-                 int64_t N, int64_t K, int top_k, int group, int mul_w) {
+                 int64_t N, int64_t K, int top_k, int group, int mul_w, int round_out) {
   __shared__ float As[kSimtBM][kSimtKC];
   __shared__ int64_t rows[kSimtBM];
   __shared__ int32_t slots[kSimtBM];
@@ -111,6 +111,7 @@ int4_simt_kernel(const TA* __restrict__ A, const int32_t* __restrict__ packed,
     if (s < 0 || s >= numel) continue;
     float v = acc[i];
     if (mul_w) v = topk_w[s] * v;
+    if (round_out && kBf16) v = round_to_bf16(v);
     scratch[(int64_t)s * N + n] = v;
   }
 }
@@ -275,7 +276,7 @@ mxfp4_stage1_simt_kernel(const __nv_bfloat16* __restrict__ act, const uint8_t* _
 // ---------------------------------------------------------------------------
 int launch_int4_simt(const void* A, int a_dtype, const int32_t* packed, const void* scale,
                      const Routing& r, const float* topk_w, float* scratch, int64_t N, int64_t K,
-                     int top_k, int group, int mul_w, cudaStream_t stream) {
+                     int top_k, int group, int mul_w, cudaStream_t stream, int round_out) {
   if (r.max_blocks == 0 || N == 0) return XKB_OK;
   XKB_REQUIRE(r.block == kSimtBM, "int4 SIMT kernel needs align block %d", kSimtBM);
   XKB_REQUIRE(r.max_blocks <= 65535 * 32, "too many routing blocks for one launch");
@@ -285,13 +286,61 @@ int launch_int4_simt(const void* A, int a_dtype, const int32_t* packed, const vo
   if (a_dtype == XKB_BF16)
     int4_simt_kernel<__nv_bfloat16><<<grid, kSimtBN, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(A), packed, static_cast<const __nv_bfloat16*>(scale),
-        r.sorted_ids, r.expert_ids, r.num_post, topk_w, scratch, r.numel, N, K, top_k, group, mul_w);
+        r.sorted_ids, r.expert_ids, r.num_post, topk_w, scratch, r.numel, N, K, top_k, group, mul_w, round_out);
   else
     int4_simt_kernel<float><<<grid, kSimtBN, 0, stream>>>(
         static_cast<const float*>(A), packed, static_cast<const __nv_bfloat16*>(scale), r.sorted_ids,
-        r.expert_ids, r.num_post, topk_w, scratch, r.numel, N, K, top_k, group, mul_w);
+        r.expert_ids, r.num_post, topk_w, scratch, r.numel, N, K, top_k, group, mul_w, round_out);
   XKB_CHECK_LAUNCH("int4_simt_kernel");
   return XKB_OK;
+}
+
+// ---------------------------------------------------------------------------
+// INT4 two-GEMM expert layer on the generic kernels: gate_up slot rows (fp32) -> SwiGLU per slot ->
+// down GEMM over the slots' activation rows (every slot is its own "token": top_k = 1 below) with
+// the weighted rows rounded to the activation dtype.
+// ---------------------------------------------------------------------------
+namespace {
+template <typename TA>
+__global__ void __launch_bounds__(256)
+swiglu_rows_kernel(const float* __restrict__ rows1, TA* __restrict__ act, int64_t numel, int64_t inter, float limit,
+                   const int32_t* __restrict__ ids, const int32_t* __restrict__ emap, int num_map, int E) {
+  const int64_t total = numel * inter;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t s = i / inter, j = i - s * inter;
+    // slots the align stage dropped have no gate_up row: same predicate as the combine
+    int g = ids[s];
+    if (emap != nullptr) g = (g < 0 || g >= num_map) ? -1 : emap[g];
+    if (g < 0 || g >= E) continue;
+    float gate = rows1[s * 2 * inter + j], up = rows1[s * 2 * inter + inter + j];
+    if (sizeof(TA) == 2) { gate = round_to_bf16(gate); up = round_to_bf16(up); }   // the first GEMM's output dtype
+    if (limit > 0.f) { gate = fminf(gate, limit); up = fminf(fmaxf(up, -limit), limit); }
+    const float v = gate / (1.f + expf(-gate)) * up;
+    if (sizeof(TA) == 2) act[i] = __float2bfloat16_rn(v);
+    else reinterpret_cast<float*>(act)[i] = v;
+  }
+}
+}  // namespace
+
+int launch_int4_ffn_simt(const void* A, int a_dtype, const int32_t* w13, const void* s13, const int32_t* w2,
+                         const void* s2, const Routing& r, const int32_t* topk_ids, const int32_t* expert_map,
+                         int num_map, int E, const float* topk_w, float* rows1, void* act, float* scratch,
+                         int64_t hidden, int64_t inter, int top_k, int group, float limit, cudaStream_t stream) {
+  int rc = launch_int4_simt(A, a_dtype, w13, s13, r, nullptr, rows1, 2 * inter, hidden, top_k, group, 0, stream);
+  if (rc != XKB_OK) return rc;
+  if (r.numel > 0 && inter > 0) {
+    int64_t blocks = ceil_div(r.numel * inter, 256);
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (a_dtype == XKB_BF16)
+      swiglu_rows_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>(
+          rows1, static_cast<__nv_bfloat16*>(act), r.numel, inter, limit, topk_ids, expert_map, num_map, E);
+    else
+      swiglu_rows_kernel<float><<<(unsigned)blocks, 256, 0, stream>>>(rows1, static_cast<float*>(act), r.numel, inter,
+                                                                      limit, topk_ids, expert_map, num_map, E);
+    XKB_CHECK_LAUNCH("swiglu_rows_kernel");
+  }
+  // slot s reads activation row s: the same routing with one slot per "token"
+  return launch_int4_simt(act, a_dtype, w2, s2, r, topk_w, scratch, hidden, inter, 1, group, 1, stream, 1);
 }
 
 int launch_mxfp4_simt(const void* A, int a_dtype, const uint8_t* w13, const uint8_t* w13_scale,

@@ -113,7 +113,7 @@ template <int BT, int MATS = 1, bool INT4 = true> struct TcCfg {
   // Control warps: weight producer, the issuers, token producer.  Narrow INT4 tiles run three
   // issuers (five control warps; 21 warps get 80 registers each, enough for the INT4 dequantiser);
   // the others two issuers (four control warps, 96 registers, which the E2M1 dequantiser needs).
-  static constexpr int kCtrlWarps = (INT4 && BT <= 32) ? 5 : 4;
+  static constexpr int kCtrlWarps = (INT4 && MATS == 1 && BT <= 32) ? 5 : 4;
   static constexpr int kThreads = 32 * (kCtrlWarps + kDequantWarps);
   static constexpr int kGroups = (BT <= 64) ? kWGs / 2 : 1;
   static constexpr int kGroupWarps = kDequantWarps / kGroups;
@@ -190,9 +190,12 @@ constexpr int kModeMxDown = 2;    // MXFP4 w2: rows = hidden, bf16-rounded resul
                                   // (read-out, loop bookkeeping) would weigh as much as the stages themselves
 constexpr int kModeInt4Pair = 3;  // INT4 with TWO 128-row weight tiles per token tile (they alternate
                                   // 256-K stages like gate/up): halves the token-tile traffic per flop
+constexpr int kModeInt4GateUp = 4;  // INT4 w13 of a two-GEMM expert layer: gate rows and up rows alternate stages like
+                                    // kModeMxGateUp, SwiGLU epilogue, bf16 activations out
 constexpr bool mode_is_pair(int mode) { return mode == kModeInt4Pair || mode == kModeMxDown; }
-constexpr int mode_mats(int mode) { return (mode == kModeMxGateUp || mode_is_pair(mode)) ? 2 : 1; }
-constexpr bool mode_is_int4(int mode) { return mode == kModeInt4 || mode == kModeInt4Pair; }
+constexpr bool mode_is_gate_up(int mode) { return mode == kModeMxGateUp || mode == kModeInt4GateUp; }
+constexpr int mode_mats(int mode) { return (mode_is_gate_up(mode) || mode_is_pair(mode)) ? 2 : 1; }
+constexpr bool mode_is_int4(int mode) { return mode == kModeInt4 || mode == kModeInt4Pair || mode == kModeInt4GateUp; }
 
 struct TcParams {
   const int32_t* sorted_ids;
@@ -204,6 +207,8 @@ struct TcParams {
   int64_t numel;
   int N, K;                     // tile rows are taken from N rows per expert; K = contraction length
   int mul_w;
+  int round_rows;               // INT4: round each weighted slot row to bf16 (the second GEMM of a two-GEMM layer,
+                                // whose per-slot results the reference composition holds in bf16)
   // MXFP4 only
   const __nv_bfloat16* bias;    // b13 [E, 2*ispp] or b2 [E, hidden] or nullptr
   __nv_bfloat16* act;           // gate_up mode output: [positions, N] bf16 in the K-permuted order
@@ -545,7 +550,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
             }
           }
         }
-        if (MODE == kModeMxGateUp) {
+        if (mode_is_gate_up(MODE)) {
           // acc = gate, more = up.  Rounding points of the reference
           // (src/xkernels/ops/moe/mxfp4_reference.py:92-100): gate_up to bf16, (+ bf16 bias, rounded),
           // fp32 clamp and silu(gate) * up, then bf16.  The activation goes out in the K order the
@@ -554,8 +559,9 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             if (!((live >> j) & 1u)) continue;          // warp-uniform
-            float g = round_to_bf16(__uint_as_float(acc[j]) * kMxUnscale);   // exact: a power of two
-            float u = round_to_bf16(__uint_as_float(more[j]) * kMxUnscale);
+            constexpr float kUnscale = (MODE == kModeInt4GateUp) ? kInt4Unscale : kMxUnscale;
+            float g = round_to_bf16(__uint_as_float(acc[j]) * kUnscale);   // exact: a power of two
+            float u = round_to_bf16(__uint_as_float(more[j]) * kUnscale);
             if (p.bias != nullptr) { g = round_to_bf16(g + bias0); u = round_to_bf16(u + bias1); }
             if (p.limit > 0.f) { g = fminf(g, p.limit); u = fminf(fmaxf(u, -p.limit), p.limit); }
             const float silu = g / (1.f + expf(-g));
@@ -572,8 +578,9 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
               v = round_to_bf16(v * kMxUnscale);
               if (p.bias != nullptr) v = round_to_bf16(v + bias0);
               if (p.mul_w) v = v * p.topk_w[slot];
-            } else if (p.mul_w) {
-              v = p.topk_w[slot] * v;
+            } else {
+              if (p.mul_w) v = p.topk_w[slot] * v;
+              if (p.round_rows) v = round_to_bf16(v);
             }
             p.scratch[(int64_t)slot * p.N + n_glob] = v;
             if (mode_is_pair(MODE)) {  // the second weight tile: rows 128 further down
@@ -581,6 +588,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
               if (MODE == kModeInt4Pair) {
                 if (kInt4NoSubtract) v2 *= kInt4Unscale;
                 if (p.mul_w) v2 = p.topk_w[slot] * v2;
+                if (p.round_rows) v2 = round_to_bf16(v2);
               } else {
                 v2 = round_to_bf16(v2 * kMxUnscale);
                 if (p.bias != nullptr) v2 = round_to_bf16(v2 + bias1);
@@ -851,6 +859,22 @@ int64_t int4_tc_workspace_bytes(int64_t numel, int64_t N, int64_t K, int E) {
   return align_up((numel + (int64_t)(E + 1) * 255) * K * 2, 256);
 }
 
+// one INT4 GEMM (tokens through `tm_tokens`) at the token tile the routing was aligned for
+static int launch_int4_by_block(const CUtensorMap& tm_packed, const CUtensorMap& tm_scale, const CUtensorMap& tm_tokens,
+                                const TcParams& prm, const Routing& r, int64_t N, cudaStream_t stream) {
+  const int64_t max_tiles = r.max_blocks * (N / kTileRows);
+  switch (r.block) {
+    case 16: return launch_bt<16, kModeInt4>(tm_packed, tm_scale, tm_tokens, prm, max_tiles, stream);
+    case 32: return launch_bt<32, kModeInt4>(tm_packed, tm_scale, tm_tokens, prm, max_tiles, stream);
+    case 64: return launch_bt<64, kModeInt4>(tm_packed, tm_scale, tm_tokens, prm, max_tiles, stream);
+    case 128:
+      if (N % (2 * kTileRows) == 0)
+        return launch_bt<128, kModeInt4Pair>(tm_packed, tm_scale, tm_tokens, prm, max_tiles / 2, stream);
+      return launch_bt<128, kModeInt4>(tm_packed, tm_scale, tm_tokens, prm, max_tiles, stream);
+    default: return fail(XKB_ERR_ARG, "int4 tcgen05 path: unsupported token tile %d", r.block);
+  }
+}
+
 int launch_int4_tc(const void* A, const int32_t* packed, const void* scale, const Routing& r,
                    const float* topk_w, float* scratch, int64_t N, int64_t K, int E, int top_k, int mul_w,
                    void* tc_ws, int* status, cudaStream_t stream) {
@@ -886,21 +910,91 @@ int launch_int4_tc(const void* A, const int32_t* packed, const void* scale, cons
   prm.N = (int)N;
   prm.K = (int)K;
   prm.mul_w = mul_w;
+  prm.round_rows = 0;
   prm.bias = nullptr;
   prm.act = nullptr;
   prm.rows_per_expert = (int)N;
   prm.limit = 0.f;
-  const int64_t max_tiles = r.max_blocks * (N / kTileRows);
+  return launch_int4_by_block(tm_packed, tm_scale, tm_tokens, prm, r, N, stream);
+}
+
+// ---------------------------------------------------------------------------
+// INT4 two-GEMM expert layer: gate_up GEMM with fused SwiGLU, then the down GEMM whose weighted
+// slot rows are rounded to bf16 (what the composition of the reference's ops holds between its
+// second fused_moe_int4_w4a16 call and moe_sum_reduce).
+// ---------------------------------------------------------------------------
+bool int4_ffn_tc_supported(int a_dtype, int64_t M, int64_t hidden, int64_t inter, int E, int top_k, int group) {
+  return a_dtype == XKB_BF16 && group == 32 && M > 0 && E > 0 && top_k > 0 && hidden > 0 && inter > 0 &&
+         hidden % kStageK == 0 && inter % kStageK == 0 &&   // both are contraction lengths and tile-row counts
+         (int64_t)E * 2 * inter < (1ll << 31) && (int64_t)E * hidden < (1ll << 31);
+}
+
+int launch_int4_ffn_tc(const void* A, const int32_t* w13, const void* s13, const int32_t* w2, const void* s2,
+                       const Routing& r, const float* topk_w, __nv_bfloat16* act, float* scratch, int64_t hidden,
+                       int64_t inter, int E, int top_k, float limit, void* tc_ws, int* status, cudaStream_t stream) {
+  Carver carve(tc_ws);
+  __nv_bfloat16* Ag = carve.take<__nv_bfloat16>(r.max_pad * hidden);
+  int64_t gblocks = r.max_pad < 148 * 16 ? r.max_pad : 148 * 16;
+  if (gblocks < 1) gblocks = 1;
+  gather_permute_kernel<<<(unsigned)gblocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(A), r.sorted_ids,
+                                                               r.num_post, Ag, r.numel, (int)hidden, top_k);
+  XKB_CHECK_LAUNCH("gather_permute_kernel");
+  CUtensorMap tm_w13, tm_s13, tm_w2, tm_s2, tm_tok0, tm_tok1;
+  int rc = make_map_2d(&tm_w13, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w13, (uint64_t)E * 2 * inter, (uint64_t)hidden / 2,
+                       kTileRows, kStageK / 2, CU_TENSOR_MAP_SWIZZLE_128B, "w13 packed weights");
+  if (rc != XKB_OK) return rc;
+  rc = make_map_2d(&tm_s13, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, s13, (uint64_t)E * 2 * inter, (uint64_t)hidden / 32,
+                   kTileRows, kStageK / 32, CU_TENSOR_MAP_SWIZZLE_NONE, "w13 group scales");
+  if (rc != XKB_OK) return rc;
+  rc = make_map_2d(&tm_w2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w2, (uint64_t)E * hidden, (uint64_t)inter / 2, kTileRows,
+                   kStageK / 2, CU_TENSOR_MAP_SWIZZLE_128B, "w2 packed weights");
+  if (rc != XKB_OK) return rc;
+  rc = make_map_2d(&tm_s2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, s2, (uint64_t)E * hidden, (uint64_t)inter / 32,
+                   kTileRows, kStageK / 32, CU_TENSOR_MAP_SWIZZLE_NONE, "w2 group scales");
+  if (rc != XKB_OK) return rc;
+  rc = make_map_2d(&tm_tok0, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, Ag, (uint64_t)r.max_pad, (uint64_t)hidden,
+                   (uint32_t)r.block, kSubK, CU_TENSOR_MAP_SWIZZLE_128B, "gathered activations");
+  if (rc != XKB_OK) return rc;
+  rc = make_map_2d(&tm_tok1, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, act, (uint64_t)r.max_pad, (uint64_t)inter,
+                   (uint32_t)r.block, kSubK, CU_TENSOR_MAP_SWIZZLE_128B, "SwiGLU activations");
+  if (rc != XKB_OK) return rc;
+
+  TcParams prm;
+  prm.sorted_ids = r.sorted_ids;
+  prm.expert_ids = r.expert_ids;
+  prm.num_post = r.num_post;
+  prm.topk_w = topk_w;
+  prm.status = status;
+  prm.numel = r.numel;
+  prm.bias = nullptr;
+  prm.limit = limit;
+  // gate_up + SwiGLU -> act
+  prm.scratch = nullptr;
+  prm.act = act;
+  prm.N = (int)inter;
+  prm.K = (int)hidden;
+  prm.rows_per_expert = (int)(2 * inter);
+  prm.mul_w = 0;
+  prm.round_rows = 0;
+  const int64_t tiles0 = r.max_blocks * (inter / kTileRows);
   switch (r.block) {
-    case 16: return launch_bt<16, kModeInt4>(tm_packed, tm_scale, tm_tokens, prm, max_tiles, stream);
-    case 32: return launch_bt<32, kModeInt4>(tm_packed, tm_scale, tm_tokens, prm, max_tiles, stream);
-    case 64: return launch_bt<64, kModeInt4>(tm_packed, tm_scale, tm_tokens, prm, max_tiles, stream);
-    case 128:
-      if (N % (2 * kTileRows) == 0)
-        return launch_bt<128, kModeInt4Pair>(tm_packed, tm_scale, tm_tokens, prm, max_tiles / 2, stream);
-      return launch_bt<128, kModeInt4>(tm_packed, tm_scale, tm_tokens, prm, max_tiles, stream);
+    case 16: rc = launch_bt<16, kModeInt4GateUp>(tm_w13, tm_s13, tm_tok0, prm, tiles0, stream); break;
+    case 32: rc = launch_bt<32, kModeInt4GateUp>(tm_w13, tm_s13, tm_tok0, prm, tiles0, stream); break;
+    case 64: rc = launch_bt<64, kModeInt4GateUp>(tm_w13, tm_s13, tm_tok0, prm, tiles0, stream); break;
+    case 128: rc = launch_bt<128, kModeInt4GateUp>(tm_w13, tm_s13, tm_tok0, prm, tiles0, stream); break;
     default: return fail(XKB_ERR_ARG, "int4 tcgen05 path: unsupported token tile %d", r.block);
   }
+  if (rc != XKB_OK) return rc;
+  // down: weighted slot rows, rounded to bf16
+  prm.scratch = scratch;
+  prm.act = nullptr;
+  prm.N = (int)hidden;
+  prm.K = (int)inter;
+  prm.rows_per_expert = (int)hidden;
+  prm.mul_w = 1;
+  prm.round_rows = 1;
+  prm.limit = 0.f;
+  return launch_int4_by_block(tm_w2, tm_s2, tm_tok1, prm, r, hidden, stream);
 }
 
 // ---------------------------------------------------------------------------
@@ -969,6 +1063,7 @@ int launch_mxfp4_tc(const void* A, const uint8_t* w13, const uint8_t* w13_scale,
   prm.status = status;
   prm.numel = r.numel;
   prm.mul_w = mul_w;
+  prm.round_rows = 0;
   prm.limit = limit;
   // stage 0: gate_up + SwiGLU -> act
   prm.scratch = nullptr;

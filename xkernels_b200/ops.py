@@ -416,6 +416,57 @@ def fused_moe_mxfp4(A, w13, w13_scale, w2, w2_scale, topk_ids, topk_w, b13=None,
     return out
 
 
+def fused_moe_int4_ffn(A, w13_packed, w13_scale, w2_packed, w2_scale, topk_ids, topk_w, group_size=32,
+                       swiglu_limit=None, expert_map=None, workspace=None, *, path="auto"):
+    """One expert layer of two INT4 W4A16 GEMMs in one call: gate_up GEMM -> SwiGLU -> down GEMM ->
+    weighted top-k combine.
+
+    The reference has the single GEMM only (``fused_moe_int4_w4a16``, src/xkernels/ops/moe/interface.py:19-32;
+    its INT4 benchmark measures the two shapes of such a layer, meta/benchmarks/bench_moe_int4_w4a16.py:3-12).
+    This op returns what a caller of the reference gets from composing it: the first GEMM over the
+    token's slots (bf16 result), ``act = (silu(gate) * up).to(A.dtype)`` with the gate rows first in
+    ``w13``, the second GEMM with the routing weights (bf16 result per slot), ``moe_sum_reduce`` over
+    the slots.  ``w13_packed [E, 2*inter, hidden//8]``, ``w13_scale [E, 2*inter, hidden//group]``,
+    ``w2_packed [E, hidden, inter//8]``, ``w2_scale [E, hidden, inter//group]``.
+    """
+    lib = _lib.load()
+    dev = _require_cuda("fused_moe_int4_ffn", A, w13_packed, w13_scale, w2_packed, w2_scale, topk_ids, topk_w, expert_map)
+    if A.dtype not in _DT:
+        raise TypeError(f"fused_moe_int4_ffn: A must be bf16 or fp32, got {A.dtype}")
+    for name, t in (("w13_packed", w13_packed), ("w2_packed", w2_packed)):
+        if t.dtype != torch.int32 or t.dim() != 3:
+            raise TypeError(f"fused_moe_int4_ffn: {name} must be int32 [E, rows, K//8]")
+    A, w13_packed, w2_packed = A.contiguous(), w13_packed.contiguous(), w2_packed.contiguous()
+    M, hidden = A.shape
+    E, two_inter, kp = w13_packed.shape
+    inter = two_inter // 2
+    group_size = int(group_size)
+    if kp * 8 != hidden or two_inter % 2 or tuple(w2_packed.shape) != (E, hidden, inter // 8):
+        raise ValueError("fused_moe_int4_ffn: w13_packed must be [E, 2*inter, hidden//8] and w2_packed [E, hidden, inter//8]")
+    w13_scale = (w13_scale if w13_scale.dtype == torch.bfloat16 else w13_scale.to(torch.bfloat16)).contiguous()
+    w2_scale = (w2_scale if w2_scale.dtype == torch.bfloat16 else w2_scale.to(torch.bfloat16)).contiguous()
+    if tuple(w13_scale.shape) != (E, 2 * inter, hidden // group_size) or tuple(w2_scale.shape) != (E, hidden, inter // group_size):
+        raise ValueError("fused_moe_int4_ffn: scale shapes must be [E, 2*inter, hidden//group] and [E, hidden, inter//group]")
+    ids, tw, emap = _routing_args("fused_moe_int4_ffn", topk_ids, topk_w, expert_map, dev, M)
+    top_k = ids.shape[1]
+    limit = 0.0 if swiglu_limit is None else float(swiglu_limit)
+    pcode = {"auto": _lib.PATH_AUTO, "simt": _lib.PATH_SIMT, "tc": _lib.PATH_TC}[path]
+    if path != "simt":
+        _check_int4_scales(w13_scale)
+        _check_int4_scales(w2_scale)
+    with torch.cuda.device(dev):
+        out = torch.empty((M, hidden), dtype=A.dtype, device=dev)
+        ws_bytes = int(lib.xkb_fused_moe_int4_ffn_workspace_bytes(M, hidden, inter, E, top_k, _DT[A.dtype]))
+        ws = _caller_workspace(workspace if isinstance(workspace, torch.Tensor) else None, False, ws_bytes, dev, ws_bytes)
+        _lib.check(
+            lib.xkb_fused_moe_int4_ffn(
+                _ptr(A), _DT[A.dtype], _ptr(w13_packed), _ptr(w13_scale), _ptr(w2_packed), _ptr(w2_scale), _ptr(ids),
+                _ptr(tw), _ptr(emap), 0 if emap is None else emap.numel(), _ptr(out), M, hidden, inter, E, top_k,
+                group_size, limit, pcode, _ptr(ws), ws.numel(), _stream(dev)),
+            "xkb_fused_moe_int4_ffn")
+    return out
+
+
 # ---------------------------------------------------------------------------
 # expert-parallel building blocks
 # ---------------------------------------------------------------------------
