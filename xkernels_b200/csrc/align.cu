@@ -127,6 +127,7 @@ align_small_kernel(const int32_t* __restrict__ topk_ids, int64_t numel, int E, i
                    int32_t* __restrict__ sorted_ids, int64_t max_pad,
                    int32_t* __restrict__ expert_ids, int64_t max_blocks,
                    int32_t* __restrict__ num_post, int32_t* __restrict__ expert_off_out) {
+  chain_trigger();   // a kernel chained behind this one may be launched; it waits for completion itself
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int EP = E + 1;
   int* hist = reinterpret_cast<int*>(smem_raw);   // [EP]
@@ -226,6 +227,7 @@ align_scatter_kernel(const int32_t* __restrict__ topk_ids, int64_t numel, int E,
                      const int32_t* __restrict__ expert_map, int num_map,
                      const int32_t* __restrict__ chunk_base /*[C][E+1]*/,
                      const int32_t* __restrict__ expert_off_g, int32_t* __restrict__ sorted_ids) {
+  chain_trigger();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int EP = E + 1;
   int* base = reinterpret_cast<int*>(smem_raw);   // [EP]

@@ -339,10 +339,13 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
   if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
   if (warp == 0 && lane == 0) { prefetch_tensormap(&tm_packed); prefetch_tensormap(&tm_scale); }
   if (warp == kTokWarp && lane == kTokLane) prefetch_tensormap(&tm_tokens);
+  chain_trigger();          // the combine may be launched; it waits for this kernel's completion itself
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_slot, 0);   // (marks it warp-uniform)
+  // everything above needed nothing from the kernels before this one (routing, gathered activations)
+  chain_wait();
 
   // tile index t -> (token block, row tile); the row tile varies fastest so that CTAs that run
   // together share the token block and walk through one expert's weights
@@ -756,6 +759,8 @@ __global__ void __launch_bounds__(256)
 gather_permute_kernel(const __nv_bfloat16* __restrict__ A, const int32_t* __restrict__ sorted_ids,
                       const int32_t* __restrict__ num_post, __nv_bfloat16* __restrict__ Ag, int64_t numel,
                       int K, int top_k) {
+  chain_trigger();
+  chain_wait();             // the routing comes from the align kernel before this one
   const int total = num_post[0];
   for (int64_t pos = blockIdx.x; pos < total; pos += gridDim.x) {
     const int32_t slot = sorted_ids[pos];
@@ -832,7 +837,8 @@ int launch_bt(const CUtensorMap& tmp, const CUtensorMap& tms, const CUtensorMap&
   if (grid < 1) grid = 1;
   {
     GemmTimerScope timed(stream);
-    moe_tc_kernel<BT, MODE><<<(unsigned)grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tmp, tms, tmt, prm);
+    XKB_CHECK_CUDA(launch_chained(moe_tc_kernel<BT, MODE>, dim3((unsigned)grid), dim3(Cfg::kThreads), Cfg::kSmemBytes,
+                                  stream, tmp, tms, tmt, prm));
   }
   XKB_CHECK_LAUNCH("moe_tc_kernel");
   return XKB_OK;
@@ -883,9 +889,9 @@ int launch_int4_tc(const void* A, const int32_t* packed, const void* scale, cons
 
   int64_t gblocks = r.max_pad < 148 * 16 ? r.max_pad : 148 * 16;
   if (gblocks < 1) gblocks = 1;
-  gather_permute_kernel<<<(unsigned)gblocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(A),
+  XKB_CHECK_CUDA(launch_chained(gather_permute_kernel, dim3((unsigned)gblocks), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(A),
                                                                r.sorted_ids, r.num_post, Ag, r.numel, (int)K,
-                                                               top_k);
+                                                               top_k));
   XKB_CHECK_LAUNCH("gather_permute_kernel");
 
   CUtensorMap tm_packed, tm_scale, tm_tokens;
@@ -936,8 +942,8 @@ int launch_int4_ffn_tc(const void* A, const int32_t* w13, const void* s13, const
   __nv_bfloat16* Ag = carve.take<__nv_bfloat16>(r.max_pad * hidden);
   int64_t gblocks = r.max_pad < 148 * 16 ? r.max_pad : 148 * 16;
   if (gblocks < 1) gblocks = 1;
-  gather_permute_kernel<<<(unsigned)gblocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(A), r.sorted_ids,
-                                                               r.num_post, Ag, r.numel, (int)hidden, top_k);
+  XKB_CHECK_CUDA(launch_chained(gather_permute_kernel, dim3((unsigned)gblocks), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(A), r.sorted_ids,
+                                                               r.num_post, Ag, r.numel, (int)hidden, top_k));
   XKB_CHECK_LAUNCH("gather_permute_kernel");
   CUtensorMap tm_w13, tm_s13, tm_w2, tm_s2, tm_tok0, tm_tok1;
   int rc = make_map_2d(&tm_w13, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w13, (uint64_t)E * 2 * inter, (uint64_t)hidden / 2,
@@ -1030,9 +1036,9 @@ int launch_mxfp4_tc(const void* A, const uint8_t* w13, const uint8_t* w13_scale,
   __nv_bfloat16* Ag = carve.take<__nv_bfloat16>(r.max_pad * hidden);
   int64_t gblocks = r.max_pad < 148 * 16 ? r.max_pad : 148 * 16;
   if (gblocks < 1) gblocks = 1;
-  gather_permute_kernel<<<(unsigned)gblocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(A),
+  XKB_CHECK_CUDA(launch_chained(gather_permute_kernel, dim3((unsigned)gblocks), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(A),
                                                                r.sorted_ids, r.num_post, Ag, r.numel,
-                                                               (int)hidden, top_k);
+                                                               (int)hidden, top_k));
   XKB_CHECK_LAUNCH("gather_permute_kernel");
 
   CUtensorMap tm_w13, tm_w2, tm_tok0, tm_tok1, tm_s13, tm_s2;

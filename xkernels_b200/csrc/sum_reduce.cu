@@ -71,6 +71,7 @@ __global__ void __launch_bounds__(256)
 sum_reduce_vec8_kernel(const TY* __restrict__ y, const TW* __restrict__ w, TO* __restrict__ out,
                        int64_t M, int top_k, int64_t H, float rsf, const int32_t* __restrict__ ids,
                        const int32_t* __restrict__ emap, int num_map, int E) {
+  chain_wait();   // as the combine of a fused call: the slot rows come from the GEMM kernel before this one
   const int64_t hv = H >> 3;  // 8-wide columns per row
   const int64_t total = M * hv;
   for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
@@ -132,9 +133,9 @@ int launch_typed(const void* y, const void* w, void* out, int64_t M, int top_k, 
   const int64_t cap = 148 * 8 * 4;
   if (blocks > cap) blocks = cap;
   if (vec_ok) {
-    sum_reduce_vec8_kernel<TY, TW, TO><<<(unsigned)blocks, 256, 0, stream>>>(
-        static_cast<const TY*>(y), static_cast<const TW*>(w), static_cast<TO*>(out), M, top_k, H, rsf,
-        ids, emap, num_map, E);
+    XKB_CHECK_CUDA(launch_chained(sum_reduce_vec8_kernel<TY, TW, TO>, dim3((unsigned)blocks), dim3(256), 0, stream,
+                                  static_cast<const TY*>(y), static_cast<const TW*>(w), static_cast<TO*>(out), M, top_k,
+                                  H, rsf, ids, emap, num_map, E));
     XKB_CHECK_LAUNCH("sum_reduce_vec8_kernel");
   } else {
     sum_reduce_scalar_kernel<TY, TW, TO><<<(unsigned)blocks, 256, 0, stream>>>(
