@@ -174,9 +174,12 @@ template <int BT, int MATS = 1, bool INT4 = true> struct TcCfg {
   static_assert(kIssuers % MATS == 0 && kIssuers / MATS <= kBStages, "token ring arithmetic");
   static constexpr int kNumBars = 2 * kWStages + 2 * kBBars + 2 * kABars + 2 * kDBuf;
   static constexpr size_t kBarBytes = ((size_t)kNumBars * 8 + 64 + 127) / 128 * 128;   // + allocation slot, abort word
+  // MXFP4 with narrow token tiles converts through a table in shared memory (see kLut below)
+  static constexpr bool kLut = !INT4 && BT <= 64;
+  static constexpr size_t kLutBytes = kLut ? 256 * 32 * 4 : 0;
   static constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + (size_t)kWStages * kPackedStageBytes +
                                        (size_t)kBStages * kBStageBytes + (size_t)kWStages * kScaleStageBytes +
-                                       kBarBytes;
+                                       kBarBytes + kLutBytes;
   static_assert(kSmemBytes <= 227 * 1024, "shared memory overcommitted");
 };
 
@@ -285,6 +288,20 @@ __device__ __forceinline__ uint32_t mx_pair(uint32_t mag_shifted, uint32_t sign_
   asm("lop3.b32 %0, %0, %1, 0x80008000, 0xF8;" : "+r"(t) : "r"(sign_shifted));           // a | (b & c)
   return bf2_mul(t, c);
 }
+// The decode-sized MXFP4 tiles are bound by the integer pipe when they convert with shifts and masks
+// (7 shifts + 8 logic operations per packed word on a half-rate pipe).  They convert through a table
+// instead: one 32-bit entry per BYTE value = the two E2M1 codes of the byte as a bf16 pair (even k
+// low), 256 entries, replicated for the 32 lanes so that lane l only ever reads bank l (entry b of
+// lane l at word b * 32 + l: conflict-free whatever the data).  A byte then costs one shift, one
+// logic operation (mask and merge with the lane's base address), one shared-memory load and one bf16
+// multiply by the exact power of two 2^(s-127) -- no scaled accumulators, no scale range limit --
+// and the weights come out in natural K order, so these tiles use no K permutation.
+__device__ __forceinline__ uint32_t e2m1_bf16_bits(uint32_t code) {
+  // magnitudes {0, .5, 1, 1.5, 2, 3, 4, 6} as bf16 bit patterns
+  const uint32_t m = code & 7u;
+  const uint32_t mag = (m == 0u) ? 0u : (m == 1u) ? 0x3F00u : 0x3F80u + ((m - 2u) << 6);
+  return ((code & 8u) << 12) | mag;
+}
 // One packed word (8 codes) -> 4 registers in the nibble order (0,4),(1,5),(2,6),(3,7).
 __device__ __forceinline__ void mx_word(uint32_t x, uint32_t c, uint32_t& r0, uint32_t& r1, uint32_t& r2,
                                         uint32_t& r3) {
@@ -318,6 +335,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
   uint64_t* d_empty = d_full + Cfg::kDBuf;       // [kDBuf]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(d_empty + Cfg::kDBuf);
   int* abort_word = reinterpret_cast<int*>(tmem_slot + 1);
+  uint32_t* lut = reinterpret_cast<uint32_t*>(reinterpret_cast<unsigned char*>(bars) + Cfg::kBarBytes);   // [256][32] if kLut
 
   // broadcast so that the compiler knows the warp index is warp-uniform (tensor-memory addresses and
   // role branches then live in uniform registers)
@@ -336,6 +354,12 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
   // that both poll with back-off slow each other down); otherwise it shares the weight producer's
   constexpr int kCtrlWarps = Cfg::kCtrlWarps;
   constexpr int kTokWarp = kCtrlWarps - 1, kTokLane = 0;   // a warp of its own: two polling threads in one warp slow each other down
+  if (Cfg::kLut) {   // byte -> (bf16 of the low code, bf16 of the high code), one copy per lane/bank
+    for (int i = threadIdx.x; i < 256 * 32; i += Cfg::kThreads) {
+      const uint32_t b = (uint32_t)i >> 5;
+      lut[i] = e2m1_bf16_bits(b & 0xFu) | (e2m1_bf16_bits(b >> 4) << 16);
+    }
+  }
   if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
   if (warp == 0 && lane == 0) { prefetch_tensormap(&tm_packed); prefetch_tensormap(&tm_scale); }
   if (warp == kTokWarp && lane == kTokLane) prefetch_tensormap(&tm_tokens);
@@ -500,6 +524,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
     const int row = quarter * 32 + lane;       // weight row inside the tile
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     const uint32_t s_packed_u32 = smem_u32(s_packed), s_scale_u32 = smem_u32(s_scale);
+    const uint32_t lut_lane = smem_u32(lut) + (uint32_t)lane * 4u;   // this lane's column of the table
     // Epilogue of tile (b, nt) whose accumulators sit in set `dbuf` (use number `duse` of that
     // set).  It runs one weight stage into the NEXT tile (or after the last tile), so that the MMAs
     // it waits for have long finished and the pipeline never drains at a tile boundary.
@@ -558,11 +583,12 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
           // (src/xkernels/ops/moe/mxfp4_reference.py:92-100): gate_up to bf16, (+ bf16 bias, rounded),
           // fp32 clamp and silu(gate) * up, then bf16.  The activation goes out in the K order the
           // down GEMM's dequantiser produces: element j of a group of 8 at ((j & 3) << 1) | (j >> 2).
-          const int64_t col = (n_glob & ~int64_t(7)) | (((n_glob & 3) << 1) | ((n_glob >> 2) & 1));
+          const int64_t col = Cfg::kLut ? n_glob   // the table path of the next GEMM reads natural K order
+                                        : ((n_glob & ~int64_t(7)) | (((n_glob & 3) << 1) | ((n_glob >> 2) & 1)));
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             if (!((live >> j) & 1u)) continue;          // warp-uniform
-            constexpr float kUnscale = (MODE == kModeInt4GateUp) ? kInt4Unscale : kMxUnscale;
+            constexpr float kUnscale = (MODE == kModeInt4GateUp) ? kInt4Unscale : (Cfg::kLut ? 1.f : kMxUnscale);
             float g = round_to_bf16(__uint_as_float(acc[j]) * kUnscale);   // exact: a power of two
             float u = round_to_bf16(__uint_as_float(more[j]) * kUnscale);
             if (p.bias != nullptr) { g = round_to_bf16(g + bias0); u = round_to_bf16(u + bias1); }
@@ -578,7 +604,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
             float v = __uint_as_float(acc[j]);
             if (mode_is_int4(MODE) && kInt4NoSubtract) v *= kInt4Unscale;   // exact: a power of two
             if (MODE == kModeMxDown) {  // reference rounds `down` to bf16, adds the bf16 bias, then x w
-              v = round_to_bf16(v * kMxUnscale);
+              v = round_to_bf16(Cfg::kLut ? v : v * kMxUnscale);
               if (p.bias != nullptr) v = round_to_bf16(v + bias0);
               if (p.mul_w) v = v * p.topk_w[slot];
             } else {
@@ -593,7 +619,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
                 if (p.mul_w) v2 = p.topk_w[slot] * v2;
                 if (p.round_rows) v2 = round_to_bf16(v2);
               } else {
-                v2 = round_to_bf16(v2 * kMxUnscale);
+                v2 = round_to_bf16(Cfg::kLut ? v2 : v2 * kMxUnscale);
                 if (p.bias != nullptr) v2 = round_to_bf16(v2 + bias1);
                 if (p.mul_w) v2 = v2 * p.topk_w[slot];
               }
@@ -697,6 +723,29 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
             }
           } else {
             const uint32_t sb = (sw.x >> (8 * c)) & 0xFFu;
+            if (Cfg::kLut) {
+              // 2^(sb - 127) as a bf16 pair: exponent field sb; byte 0 is the subnormal 2^-127, 0xFF decodes to 0
+              uint32_t f = sb << 7;
+              if (sb == 0u) f = 0x40u;
+              if (sb == 0xFFu) f = 0u;
+              const uint32_t cf = f * 0x00010001u;
+#pragma unroll
+              for (int wp = 0; wp < 2; ++wp) {
+                uint32_t r[8];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                  const uint32_t x = words[2 * wp + h];
+                  // entry of byte k of x for this lane: lut_lane + byte * 128 (bytes): one byte
+                  // permute and one multiply-add each
+                  r[4 * h + 0] = bf2_mul(lds32(__byte_perm(x, 0u, 0x4440u) * 128u + lut_lane), cf);
+                  r[4 * h + 1] = bf2_mul(lds32(__byte_perm(x, 0u, 0x4441u) * 128u + lut_lane), cf);
+                  r[4 * h + 2] = bf2_mul(lds32(__byte_perm(x, 0u, 0x4442u) * 128u + lut_lane), cf);
+                  r[4 * h + 3] = bf2_mul(lds32(__byte_perm(x, 0u, 0x4443u) * 128u + lut_lane), cf);
+                }
+                tmem_st_32x8(dst + c * 16 + wp * 8, r[0], r[1], r[2], r[3], r[4], r[5], r[6], r[7]);
+              }
+              continue;
+            }
             if (sb > kMxMaxScale && sb != 0xFFu) atomicCAS(p.status, 0, kErrMxScaleRange);   // never taken for sane weights
             const uint32_t cf = mx_scale_factor(sb);
 #pragma unroll
@@ -758,7 +807,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
 __global__ void __launch_bounds__(256)
 gather_permute_kernel(const __nv_bfloat16* __restrict__ A, const int32_t* __restrict__ sorted_ids,
                       const int32_t* __restrict__ num_post, __nv_bfloat16* __restrict__ Ag, int64_t numel,
-                      int K, int top_k) {
+                      int K, int top_k, int permute) {
   chain_trigger();
   chain_wait();             // the routing comes from the align kernel before this one
   const int total = num_post[0];
@@ -769,6 +818,7 @@ gather_permute_kernel(const __nv_bfloat16* __restrict__ A, const int32_t* __rest
     uint4* dst = reinterpret_cast<uint4*>(Ag + pos * K);
     for (int i = threadIdx.x; i < K / 8; i += blockDim.x) {
       const uint4 v = __ldg(src + i);  // elements e0..e7 as (e1:e0, e3:e2, e5:e4, e7:e6)
+      if (!permute) { dst[i] = v; continue; }   // consumers that convert in natural K order
       uint4 o;
       o.x = __byte_perm(v.x, v.z, 0x5410);  // (e4 : e0)
       o.y = __byte_perm(v.x, v.z, 0x7632);  // (e5 : e1)
@@ -891,7 +941,7 @@ int launch_int4_tc(const void* A, const int32_t* packed, const void* scale, cons
   if (gblocks < 1) gblocks = 1;
   XKB_CHECK_CUDA(launch_chained(gather_permute_kernel, dim3((unsigned)gblocks), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(A),
                                                                r.sorted_ids, r.num_post, Ag, r.numel, (int)K,
-                                                               top_k));
+                                                               top_k, 1));
   XKB_CHECK_LAUNCH("gather_permute_kernel");
 
   CUtensorMap tm_packed, tm_scale, tm_tokens;
@@ -943,7 +993,7 @@ int launch_int4_ffn_tc(const void* A, const int32_t* w13, const void* s13, const
   int64_t gblocks = r.max_pad < 148 * 16 ? r.max_pad : 148 * 16;
   if (gblocks < 1) gblocks = 1;
   XKB_CHECK_CUDA(launch_chained(gather_permute_kernel, dim3((unsigned)gblocks), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(A), r.sorted_ids,
-                                                               r.num_post, Ag, r.numel, (int)hidden, top_k));
+                                                               r.num_post, Ag, r.numel, (int)hidden, top_k, 1));
   XKB_CHECK_LAUNCH("gather_permute_kernel");
   CUtensorMap tm_w13, tm_s13, tm_w2, tm_s2, tm_tok0, tm_tok1;
   int rc = make_map_2d(&tm_w13, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w13, (uint64_t)E * 2 * inter, (uint64_t)hidden / 2,
@@ -1038,7 +1088,8 @@ int launch_mxfp4_tc(const void* A, const uint8_t* w13, const uint8_t* w13_scale,
   if (gblocks < 1) gblocks = 1;
   XKB_CHECK_CUDA(launch_chained(gather_permute_kernel, dim3((unsigned)gblocks), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(A),
                                                                r.sorted_ids, r.num_post, Ag, r.numel,
-                                                               (int)hidden, top_k));
+                                                               (int)hidden, top_k,
+                                                               r.block == 16 ? 0 : 1));   // 16-token tiles convert through the table: natural K order
   XKB_CHECK_LAUNCH("gather_permute_kernel");
 
   CUtensorMap tm_w13, tm_w2, tm_tok0, tm_tok1, tm_s13, tm_s2;

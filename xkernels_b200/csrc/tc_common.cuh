@@ -74,9 +74,10 @@ struct Guard {
 // role aborted.  `sleep_ns` > 0 backs off between probes: roles that run ahead of the pipeline
 // (the TMA producers) and roles that wait on the slower side (the MMA issuers) would otherwise
 // spend issue slots on probes that the dequantiser warps need.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Guard& g, int where,
-                                          uint32_t sleep_ns = 0, uint64_t budget_ns = kWaitBudgetNs) {
-  if (mbar_try(bar, parity)) return true;   // the common case: already complete
+// The polling loop lives out of line: the callers' fast path (phase already complete) is then one
+// probe and one predicated call, without the loop's divergence bookkeeping in every inlined copy.
+static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, Guard g, int where, uint32_t sleep_ns,
+                                            uint64_t budget_ns) {
   uint64_t t0 = 0;
   for (uint32_t i = 1;; ++i) {
     if (sleep_ns) __nanosleep(sleep_ns);
@@ -90,6 +91,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Guard&
   }
   g.raise(kErrWaitTimeout + (where << 8));
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Guard& g, int where,
+                                          uint32_t sleep_ns = 0, uint64_t budget_ns = kWaitBudgetNs) {
+  if (mbar_try(bar, parity)) return true;   // the common case: already complete
+  return mbar_wait_slow(bar, parity, g, where, sleep_ns, budget_ns);
 }
 
 // Variants for warp-uniform code: every lane of the warp executes the call with the same operands
