@@ -528,7 +528,17 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
     // Epilogue of tile (b, nt) whose accumulators sit in set `dbuf` (use number `duse` of that
     // set).  It runs one weight stage into the NEXT tile (or after the last tile), so that the MMAs
     // it waits for have long finished and the pipeline never drains at a tile boundary.
-    auto run_epilogue = [&](int b, int nt, uint32_t dbuf, uint32_t duse, uint32_t tile_g0, int cg) -> bool {
+    // Slot ids and routing weights of 16 token positions of block b: lane j holds position c0 + j
+    // (padding positions carry the value numel).  Sixteen lanes load them side by side, and the first
+    // group's are requested when the tile joins the read-out queue, two stages before they are used:
+    // a read-out then never waits for global memory.
+    auto load_cols = [&](int b, int c0, int32_t& slot, float& w) {
+      slot = (lane < 16 && c0 < BT) ? __ldg(p.sorted_ids + (int64_t)b * BT + c0 + lane) : -1;
+      const bool live = slot >= 0 && slot < p.numel;
+      w = (!mode_is_gate_up(MODE) && p.mul_w && live) ? __ldg(p.topk_w + slot) : 1.f;
+    };
+    auto run_epilogue = [&](int b, int nt, uint32_t dbuf, uint32_t duse, uint32_t tile_g0, int cg, int32_t my_slot,
+                            float my_w) -> bool {
       const uint32_t d_base = tmem_base + lane_base + dbuf * (uint32_t)(Cfg::kAccs * BT);
       // which accumulators the tile's stages went to: stage vs -> (issuer (g0 + vs) % kIssuers, matrix vs % kMats)
       uint32_t valid = 0;
@@ -541,7 +551,6 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
       if (!mbar_wait(&d_full[dbuf], duse & 1u, guard, 7)) return false;
       tc_fence_after();
       const int64_t n_glob = (int64_t)nt * (mode_is_pair(MODE) ? 2 * kTileRows : kTileRows) + row;
-      const int32_t* slots = p.sorted_ids + (int64_t)b * BT;
       float bias0 = 0.f, bias1 = 0.f;
       if (!mode_is_int4(MODE) && p.bias != nullptr) {
         const int64_t e_row = (int64_t)p.expert_ids[b] * p.rows_per_expert;
@@ -552,11 +561,11 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
       // this warpgroup's 16-column groups: cg, cg + kWGs, ...
 #pragma unroll 1
       for (int c0 = cg * 16; c0 < BT; c0 += 16 * Cfg::kWGs) {
-        // slot ids of the 16 token positions (lane j holds position c0 + j); padding positions carry
-        // the value numel.  Decode-sized blocks hold one or two real tokens, so everything below is
-        // skipped for the others, and a block of padding only costs this one load.
-        const int32_t my_slot = (lane < 16) ? __ldg(slots + c0 + lane) : -1;
-        const uint32_t live = __ballot_sync(0xffffffffu, my_slot >= 0 && my_slot < p.numel) & 0xFFFFu;
+        // Everything below is skipped for padding positions, and a block of padding only costs the load.
+        const int32_t cur_slot = my_slot;
+        const float cur_w = my_w;
+        if (c0 + 16 * Cfg::kWGs < BT) load_cols(b, c0 + 16 * Cfg::kWGs, my_slot, my_w);   // the next group's, in flight meanwhile
+        const uint32_t live = __ballot_sync(0xffffffffu, cur_slot >= 0 && cur_slot < p.numel) & 0xFFFFu;
         if (live == 0u) continue;
         // acc = matrix 0 (INT4 / down: the only one; gate_up: gate; pair: first row tile), more = matrix 1,
         // each the sum of the accumulators that were written in this tile
@@ -600,15 +609,16 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             if (!((live >> j) & 1u)) continue;          // warp-uniform
-            const int32_t slot = __shfl_sync(0xffffffffu, my_slot, j);
+            const int32_t slot = __shfl_sync(0xffffffffu, cur_slot, j);
+            const float w = __shfl_sync(0xffffffffu, cur_w, j);
             float v = __uint_as_float(acc[j]);
             if (mode_is_int4(MODE) && kInt4NoSubtract) v *= kInt4Unscale;   // exact: a power of two
             if (MODE == kModeMxDown) {  // reference rounds `down` to bf16, adds the bf16 bias, then x w
               v = round_to_bf16(Cfg::kLut ? v : v * kMxUnscale);
               if (p.bias != nullptr) v = round_to_bf16(v + bias0);
-              if (p.mul_w) v = v * p.topk_w[slot];
+              if (p.mul_w) v = v * w;
             } else {
-              if (p.mul_w) v = p.topk_w[slot] * v;
+              if (p.mul_w) v = w * v;
               if (p.round_rows) v = round_to_bf16(v);
             }
             p.scratch[(int64_t)slot * p.N + n_glob] = v;
@@ -616,12 +626,12 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
               float v2 = __uint_as_float(more[j]);
               if (MODE == kModeInt4Pair) {
                 if (kInt4NoSubtract) v2 *= kInt4Unscale;
-                if (p.mul_w) v2 = p.topk_w[slot] * v2;
+                if (p.mul_w) v2 = w * v2;
                 if (p.round_rows) v2 = round_to_bf16(v2);
               } else {
                 v2 = round_to_bf16(Cfg::kLut ? v2 : v2 * kMxUnscale);
                 if (p.bias != nullptr) v2 = round_to_bf16(v2 + bias1);
-                if (p.mul_w) v2 = v2 * p.topk_w[slot];
+                if (p.mul_w) v2 = v2 * w;
               }
               p.scratch[(int64_t)slot * p.N + n_glob + kTileRows] = v2;
             }
@@ -635,14 +645,14 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
     };
     // Read-outs that are still due, oldest first (at most two wait at any time: a tile is read out
     // before its accumulator set is needed again, see below).
-    struct Pending { int b, nt; uint32_t it, g0; int wait, cg; };
-    Pending pq0{0, 0, 0, 0, 0, 0}, pq1{0, 0, 0, 0, 0, 0};
+    struct Pending { int b, nt; uint32_t it, g0; int wait, cg; int32_t slot; float w; };
+    Pending pq0{0, 0, 0, 0, 0, 0, -1, 1.f}, pq1{0, 0, 0, 0, 0, 0, -1, 1.f};
     int n_pend = 0;
     auto run_oldest = [&]() -> bool {
       const Pending e = pq0;
       pq0 = pq1;
       --n_pend;
-      return run_epilogue(e.b, e.nt, e.it % Cfg::kDBuf, e.it / Cfg::kDBuf, e.g0, e.cg);
+      return run_epilogue(e.b, e.nt, e.it % Cfg::kDBuf, e.it / Cfg::kDBuf, e.g0, e.cg, e.slot, e.w);
     };
     uint32_t it = 0, g0 = 0;      // g0 = number of the tile's first stage
     // This group's stages are g = grp, grp + kGroups, ... whatever the tile boundaries, so its ring
@@ -780,7 +790,8 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
       const int cg = (Cfg::kEpiWGs == Cfg::kWGs) ? wg
                                                  : (int)(((uint32_t)wg + (uint32_t)Cfg::kWGs - (it * (uint32_t)Cfg::kColGroups) % (uint32_t)Cfg::kWGs) % (uint32_t)Cfg::kWGs);
       if (cg < Cfg::kColGroups || Cfg::kEpiWGs == Cfg::kWGs) {
-        const Pending e{b, nt, it, g0, Cfg::kDBuf >= 2 ? kEpiDelay : 1, cg};   // one set: the next tile's MMAs wait for it
+        Pending e{b, nt, it, g0, Cfg::kDBuf >= 2 ? kEpiDelay : 1, cg, -1, 1.f};   // one set: the next tile's MMAs wait for it
+        load_cols(b, cg * 16, e.slot, e.w);
         if (n_pend == 0) pq0 = e; else pq1 = e;
         ++n_pend;
       }
