@@ -34,13 +34,17 @@ struct GemmTimer {
 };
 static GemmTimer g_timer;
 
+// Scopes nest: only the outermost one records (two GEMMs that overlap are timed as one span, and no
+// event lands between them, which would serialise them).
+static thread_local int g_timer_depth = 0;
 GemmTimerScope::GemmTimerScope(cudaStream_t s) : stream(s), slot(-1) {
-  if (g_timer.enabled && g_timer.used < (int)g_timer.start.size()) {
+  if (g_timer_depth++ == 0 && g_timer.enabled && g_timer.used < (int)g_timer.start.size()) {
     slot = g_timer.used++;
     cudaEventRecord(g_timer.start[slot], stream);
   }
 }
 GemmTimerScope::~GemmTimerScope() {
+  --g_timer_depth;
   if (slot >= 0) cudaEventRecord(g_timer.stop[slot], stream);
 }
 

@@ -57,7 +57,9 @@ constexpr int kSubK = 64;        // K per 128-byte swizzled token sub-tile / per
 constexpr int kSubs = kStageK / kSubK;  // 4
 constexpr int kSlotCols = kStageK / 2;                 // 128 columns of bf16 pairs per A slot
 constexpr int kSubCols = kSubK / 2;                    // 32 of them per warpgroup
-constexpr int kMaxIssuers = 3;
+constexpr int kMaxIssuers = 4;
+constexpr int kMxIssuers = 2;          // MMA issuer warps of the two-matrix modes at token tiles <= 32 (2 or 4)
+constexpr int kInt4TwoMatIssuers = 2;
 constexpr int kWStagesNarrow = 6;      // weight ring depth for token tiles of 16
 constexpr int kBStages16 = 9;          // token ring depth for token tiles of 16
 constexpr uint32_t kProdSleepNs = 400; // back-off of the TMA producers, which run a whole ring ahead
@@ -113,7 +115,8 @@ template <int BT, int MATS = 1, bool INT4 = true> struct TcCfg {
   // Control warps: weight producer, the issuers, token producer.  Narrow INT4 tiles run three
   // issuers (five control warps; 21 warps get 80 registers each, enough for the INT4 dequantiser);
   // the others two issuers (four control warps, 96 registers, which the E2M1 dequantiser needs).
-  static constexpr int kCtrlWarps = (INT4 && MATS == 1 && BT <= 32) ? 5 : 4;
+  static constexpr int kCtrlWarps = (BT > 32) ? 4 : (MATS == 1) ? (INT4 ? 5 : 4)
+                                                : 2 + (INT4 ? kInt4TwoMatIssuers : kMxIssuers);
   static constexpr int kThreads = 32 * (kCtrlWarps + kDequantWarps);
   static constexpr int kGroups = (BT <= 64) ? kWGs / 2 : 1;
   static constexpr int kGroupWarps = kDequantWarps / kGroups;
@@ -143,10 +146,11 @@ template <int BT, int MATS = 1, bool INT4 = true> struct TcCfg {
   // both producers in one warp 238 us, three issuers + five control warps 210 us.)
   static constexpr int kIssuers = kCtrlWarps - 2;
   static_assert(kIssuers <= kMaxIssuers, "not enough issuer warps");
-  // kIssuers == MATS: the stage's parity is its matrix and its issuer at once (a tile has a multiple
-  // of MATS stages), so one accumulator per matrix is enough.
+  // One accumulator per issuer.  A tile has a multiple of MATS stages and kIssuers is a multiple of
+  // MATS, so the matrix of stage g is g % MATS = (g % kIssuers) % MATS: issuer j only ever sees matrix
+  // j % MATS, and accumulator a belongs to matrix a % MATS.  (kIssuers == MATS: one per matrix.)
   static constexpr bool kLocked = (kIssuers == MATS);
-  static constexpr int kAccs = kLocked ? MATS : kIssuers * MATS;   // accumulator (issuer j, matrix m) = j * MATS + m
+  static constexpr int kAccs = kIssuers;
   // Two or three accumulator sets when tensor memory has room beside three stages of A slots: the
   // MMAs of the next tiles start while an earlier tile's accumulators still wait to be read out.
   // (Three sets let the read-out trail two tiles behind, which short tiles need: see kEpiDelay.)
@@ -217,6 +221,12 @@ struct TcParams {
   __nv_bfloat16* act;           // gate_up mode output: [positions, N] bf16 in the K-permuted order
   int rows_per_expert;          // 2*ispp (gate_up) or hidden (down)
   float limit;                  // SwiGLU clamp, <= 0 disables
+  // Two GEMMs of one expert layer that overlap (see "block hand-over" at the kernel): the first
+  // counts the finished read-outs of every token block in done_signal, the second waits until the
+  // count of a block has reached done_target before it loads that block's activations.
+  int32_t* done_signal;         // gate_up modes, or nullptr
+  const int32_t* done_wait;     // the GEMM that consumes `act` as its tokens, or nullptr
+  int done_target;
 };
 
 // (x & 0x000F000F) | 0x43004300  ->  two bf16 values 128 + nibble
@@ -363,13 +373,26 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
   if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
   if (warp == 0 && lane == 0) { prefetch_tensormap(&tm_packed); prefetch_tensormap(&tm_scale); }
   if (warp == kTokWarp && lane == kTokLane) prefetch_tensormap(&tm_tokens);
-  chain_trigger();          // the combine may be launched; it waits for this kernel's completion itself
+  // Block hand-over between the two GEMMs of an expert layer.  The second GEMM is launched as a
+  // programmatic dependent of the first and does NOT wait for the first grid to complete: its CTAs
+  // become resident as CTAs of the first exit (a CTA owns its SM), stream their weights at once and
+  // wait per token block for the first GEMM's read-outs of that block (a counter per block, release
+  // by the writer, acquire + async-proxy fence by the token producer before its TMA loads).  The
+  // tail of the first GEMM, where most SMs have run out of tiles, is filled with tiles of the second.
+  // Every CTA of the first GEMM is resident before any CTA of the second starts and never waits for
+  // the second, so the wait cannot deadlock; it is bounded all the same.  The first GEMM lets its
+  // dependents go only after its own wait for the kernels before it, so that what those wrote (the
+  // routing, the zeroed counters) is visible to the second GEMM although it skips its wait.
+  const bool hand_over_first = mode_is_gate_up(MODE) && p.done_signal != nullptr;
+  const bool hand_over_second = p.done_wait != nullptr;
+  if (!hand_over_first) chain_trigger();   // the next kernel may be launched; it waits for this one's completion itself
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_slot, 0);   // (marks it warp-uniform)
   // everything above needed nothing from the kernels before this one (routing, gathered activations)
-  chain_wait();
+  if (!hand_over_second) chain_wait();
+  if (hand_over_first) chain_trigger();
 
   // tile index t -> (token block, row tile); the row tile varies fastest so that CTAs that run
   // together share the token block and walk through one expert's weights
@@ -416,9 +439,29 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
     // ---------------- token producer (diverged from lane 0; both make progress independently) ----------------
     {
       uint32_t st = 0, tb = 0;   // token stage slot and running number of the token stage
+      int ready_b = -1;          // block hand-over: last block whose activations are known to be complete
       for (int t = (int)blockIdx.x; t < total_tiles && !guard.aborted(); t += (int)gridDim.x) {
         const int b = t / n_tiles;
         const int pos0 = b * BT;
+        if (hand_over_second && b != ready_b) {   // block hand-over: the first GEMM's read-outs of block b
+          uint64_t t0 = 0;
+          bool ready = false;
+          for (uint32_t i = 1; !ready; ++i) {
+            int32_t seen;
+            asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(p.done_wait + b) : "memory");
+            if (seen >= p.done_target) { ready = true; break; }
+            __nanosleep(200);
+            if ((i & 15u) == 0u) {
+              if (guard.aborted()) break;
+              const uint64_t now = globaltimer_ns();
+              if (t0 == 0) t0 = now;
+              else if (now - t0 > kWaitBudgetNs) { guard.raise(kErrWaitTimeout + (9 << 8)); break; }
+            }
+          }
+          if (!ready) break;
+          asm volatile("fence.proxy.async;" ::: "memory");   // the TMA loads below read what generic stores wrote
+          ready_b = b;
+        }
         for (int ks = 0; ks < k_stages; ++ks) {
           // the slot's previous user was token stage tb - kBStages: wait for its readers' commits
           if (tb >= (uint32_t)Cfg::kBStages) {
@@ -466,7 +509,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
         uint32_t started = 0;   // bit m: this issuer has already written its accumulator of matrix m in this tile
         for (int vs = (int)(me >= g0mod ? me - g0mod : me + kIssuers - g0mod); vs < v_stages && ok; vs += kIssuers) {
           const int mat = vs % kMats;                       // which matrix this stage belongs to
-          const int acc = Cfg::kLocked ? mat : (int)me * kMats + mat;
+          const int acc = (int)me;
           const uint32_t d_tmem = tmem_base + (uint32_t)(((int)dbuf * Cfg::kAccs + acc) * BT);
           const uint64_t b_desc = umma_desc_k_sw128(smem_u32(s_tokens + bst * Cfg::kBStageBytes));
           const bool fresh = ((started >> mat) & 1u) == 0;
@@ -540,13 +583,13 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
     auto run_epilogue = [&](int b, int nt, uint32_t dbuf, uint32_t duse, uint32_t tile_g0, int cg, int32_t my_slot,
                             float my_w) -> bool {
       const uint32_t d_base = tmem_base + lane_base + dbuf * (uint32_t)(Cfg::kAccs * BT);
-      // which accumulators the tile's stages went to: stage vs -> (issuer (g0 + vs) % kIssuers, matrix vs % kMats)
+      // which accumulators the tile's stages went to: stage vs -> issuer (g0 + vs) % kIssuers
       uint32_t valid = 0;
       if (Cfg::kLocked) {
         valid = (1u << kMats) - 1u;
       } else {
-        for (int vs = 0; vs < v_stages && vs < Cfg::kIssuers * kMats; ++vs)
-          valid |= 1u << (((tile_g0 + (uint32_t)vs) % Cfg::kIssuers) * kMats + vs % kMats);
+        for (int vs = 0; vs < v_stages && vs < Cfg::kIssuers; ++vs)
+          valid |= 1u << ((tile_g0 + (uint32_t)vs) % Cfg::kIssuers);
       }
       if (!mbar_wait(&d_full[dbuf], duse & 1u, guard, 7)) return false;
       tc_fence_after();
@@ -641,6 +684,14 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
       tc_fence_before();
       __syncwarp();
       mbar_arrive_if(&d_empty[dbuf], (lane == 0) ? 1u : 0u);
+      if (mode_is_gate_up(MODE) && p.done_signal != nullptr) {
+        // this warp's part of block b is written (the __syncwarp above orders the other lanes' stores
+        // before lane 0's release): one count per warp and tile, 4 * kEpiWGs per tile
+        if (lane == 0) {
+          __threadfence();
+          asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(p.done_signal + b) : "memory");
+        }
+      }
       return true;
     };
     // Read-outs that are still due, oldest first (at most two wait at any time: a tile is read out
@@ -818,9 +869,11 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
 __global__ void __launch_bounds__(256)
 gather_permute_kernel(const __nv_bfloat16* __restrict__ A, const int32_t* __restrict__ sorted_ids,
                       const int32_t* __restrict__ num_post, __nv_bfloat16* __restrict__ Ag, int64_t numel,
-                      int K, int top_k, int permute) {
+                      int K, int top_k, int permute, int32_t* __restrict__ zero, int zero_n) {
   chain_trigger();
   chain_wait();             // the routing comes from the align kernel before this one
+  // the per-block counters of the block hand-over between the two GEMMs that follow (if any)
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < zero_n; i += gridDim.x * blockDim.x) zero[i] = 0;
   const int total = num_post[0];
   for (int64_t pos = blockIdx.x; pos < total; pos += gridDim.x) {
     const int32_t slot = sorted_ids[pos];
@@ -920,10 +973,15 @@ int int4_tc_block(int64_t numel, int E) {
   return 128;  // wide: 128 tokens x two 128-row weight tiles per CTA (one tile if N % 256 != 0)
 }
 
+// counters of the block hand-over: one per token block of the smallest token tile
+static int64_t hand_over_bytes(int64_t numel, int E) { return align_up((numel / 16 + E + 2) * 4, 256); }
+// read-out warps that count per tile of the first GEMM: four per warpgroup on duty
+static int hand_over_per_tile(int block) { return 4 * (block / 16 < 4 ? block / 16 : 4); }
+
 int64_t int4_tc_workspace_bytes(int64_t numel, int64_t N, int64_t K, int E) {
   (void)N;
-  // gathered activations for the largest token tile
-  return align_up((numel + (int64_t)(E + 1) * 255) * K * 2, 256);
+  // gathered activations for the largest token tile + one counter per token block (two-GEMM layer)
+  return align_up((numel + (int64_t)(E + 1) * 255) * K * 2, 256) + hand_over_bytes(numel, E);
 }
 
 // one INT4 GEMM (tokens through `tm_tokens`) at the token tile the routing was aligned for
@@ -952,7 +1010,7 @@ int launch_int4_tc(const void* A, const int32_t* packed, const void* scale, cons
   if (gblocks < 1) gblocks = 1;
   XKB_CHECK_CUDA(launch_chained(gather_permute_kernel, dim3((unsigned)gblocks), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(A),
                                                                r.sorted_ids, r.num_post, Ag, r.numel, (int)K,
-                                                               top_k, 1));
+                                                               top_k, 1, static_cast<int32_t*>(nullptr), 0));
   XKB_CHECK_LAUNCH("gather_permute_kernel");
 
   CUtensorMap tm_packed, tm_scale, tm_tokens;
@@ -982,6 +1040,9 @@ int launch_int4_tc(const void* A, const int32_t* packed, const void* scale, cons
   prm.act = nullptr;
   prm.rows_per_expert = (int)N;
   prm.limit = 0.f;
+  prm.done_signal = nullptr;
+  prm.done_wait = nullptr;
+  prm.done_target = 0;
   return launch_int4_by_block(tm_packed, tm_scale, tm_tokens, prm, r, N, stream);
 }
 
@@ -1000,11 +1061,12 @@ int launch_int4_ffn_tc(const void* A, const int32_t* w13, const void* s13, const
                        const Routing& r, const float* topk_w, __nv_bfloat16* act, float* scratch, int64_t hidden,
                        int64_t inter, int E, int top_k, float limit, void* tc_ws, int* status, cudaStream_t stream) {
   Carver carve(tc_ws);
+  int32_t* done = carve.take<int32_t>(r.numel / 16 + E + 2);   // block hand-over counters, zeroed by the gather kernel
   __nv_bfloat16* Ag = carve.take<__nv_bfloat16>(r.max_pad * hidden);
   int64_t gblocks = r.max_pad < 148 * 16 ? r.max_pad : 148 * 16;
   if (gblocks < 1) gblocks = 1;
   XKB_CHECK_CUDA(launch_chained(gather_permute_kernel, dim3((unsigned)gblocks), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(A), r.sorted_ids,
-                                                               r.num_post, Ag, r.numel, (int)hidden, top_k, 1));
+                                                               r.num_post, Ag, r.numel, (int)hidden, top_k, 1, done, (int)r.max_blocks));
   XKB_CHECK_LAUNCH("gather_permute_kernel");
   CUtensorMap tm_w13, tm_s13, tm_w2, tm_s2, tm_tok0, tm_tok1;
   int rc = make_map_2d(&tm_w13, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w13, (uint64_t)E * 2 * inter, (uint64_t)hidden / 2,
@@ -1043,6 +1105,10 @@ int launch_int4_ffn_tc(const void* A, const int32_t* w13, const void* s13, const
   prm.rows_per_expert = (int)(2 * inter);
   prm.mul_w = 0;
   prm.round_rows = 0;
+  prm.done_signal = done;
+  prm.done_wait = nullptr;
+  prm.done_target = (int)(inter / kTileRows) * hand_over_per_tile(r.block);
+  GemmTimerScope timed(stream);   // both GEMMs in one scope: they overlap
   const int64_t tiles0 = r.max_blocks * (inter / kTileRows);
   switch (r.block) {
     case 16: rc = launch_bt<16, kModeInt4GateUp>(tm_w13, tm_s13, tm_tok0, prm, tiles0, stream); break;
@@ -1061,6 +1127,8 @@ int launch_int4_ffn_tc(const void* A, const int32_t* w13, const void* s13, const
   prm.mul_w = 1;
   prm.round_rows = 1;
   prm.limit = 0.f;
+  prm.done_signal = nullptr;
+  prm.done_wait = done;
   return launch_int4_by_block(tm_w2, tm_s2, tm_tok1, prm, r, hidden, stream);
 }
 
@@ -1083,7 +1151,7 @@ int mxfp4_tc_block(int64_t numel, int E) {
 
 int64_t mxfp4_tc_workspace_bytes(int64_t numel, int64_t hidden, int64_t ispp, int E) {
   (void)ispp;
-  return align_up((numel + (int64_t)(E + 1) * 255) * hidden * 2, 256);  // gathered activations
+  return align_up((numel + (int64_t)(E + 1) * 255) * hidden * 2, 256) + hand_over_bytes(numel, E);  // gathered activations, block counters
 }
 
 int launch_mxfp4_tc(const void* A, const uint8_t* w13, const uint8_t* w13_scale, const uint8_t* w2,
@@ -1094,13 +1162,15 @@ int launch_mxfp4_tc(const void* A, const uint8_t* w13, const uint8_t* w13_scale,
   XKB_REQUIRE(reinterpret_cast<uintptr_t>(w13_scale) % 16 == 0 && reinterpret_cast<uintptr_t>(w2_scale) % 16 == 0,
               "mxfp4 tcgen05 path: scale tensors must be 16-byte aligned");
   Carver carve(tc_ws);
+  int32_t* done = carve.take<int32_t>(r.numel / 16 + E + 2);   // block hand-over counters, zeroed by the gather kernel
   __nv_bfloat16* Ag = carve.take<__nv_bfloat16>(r.max_pad * hidden);
   int64_t gblocks = r.max_pad < 148 * 16 ? r.max_pad : 148 * 16;
   if (gblocks < 1) gblocks = 1;
   XKB_CHECK_CUDA(launch_chained(gather_permute_kernel, dim3((unsigned)gblocks), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(A),
                                                                r.sorted_ids, r.num_post, Ag, r.numel,
                                                                (int)hidden, top_k,
-                                                               r.block == 16 ? 0 : 1));   // 16-token tiles convert through the table: natural K order
+                                                               r.block == 16 ? 0 : 1,   // 16-token tiles convert through the table: natural K order
+                                                               done, (int)r.max_blocks));
   XKB_CHECK_LAUNCH("gather_permute_kernel");
 
   CUtensorMap tm_w13, tm_w2, tm_tok0, tm_tok1, tm_s13, tm_s2;
@@ -1140,6 +1210,10 @@ int launch_mxfp4_tc(const void* A, const uint8_t* w13, const uint8_t* w13_scale,
   prm.K = (int)hidden;
   prm.rows_per_expert = (int)(2 * ispp);
   prm.bias = static_cast<const __nv_bfloat16*>(b13);
+  prm.done_signal = done;
+  prm.done_wait = nullptr;
+  prm.done_target = (int)(ispp / kTileRows) * hand_over_per_tile(r.block);
+  GemmTimerScope timed(stream);   // both GEMMs in one scope: they overlap
   int64_t max_tiles = r.max_blocks * (ispp / kTileRows);
   rc = r.block == 16 ? launch_bt<16, kModeMxGateUp>(tm_w13, tm_s13, tm_tok0, prm, max_tiles, stream)
                      : launch_bt<128, kModeMxGateUp>(tm_w13, tm_s13, tm_tok0, prm, max_tiles, stream);
@@ -1151,6 +1225,8 @@ int launch_mxfp4_tc(const void* A, const uint8_t* w13, const uint8_t* w13_scale,
   prm.K = (int)ispp;
   prm.rows_per_expert = (int)hidden;
   prm.bias = static_cast<const __nv_bfloat16*>(b2);
+  prm.done_signal = nullptr;
+  prm.done_wait = done;
   max_tiles = r.max_blocks * (hidden / kTileRows);
   // (hidden is a multiple of 512 here, so the row tiles pair up)
   return r.block == 16 ? launch_bt<16, kModeMxDown>(tm_w2, tm_s2, tm_tok1, prm, max_tiles / 2, stream)
