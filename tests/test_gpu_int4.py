@@ -149,6 +149,30 @@ def test_down_projection_shape_against_oracle(M, cuda_device):
     assert_within(out, want, *TOL[torch.bfloat16], what=f"down projection shape, M={M}")
 
 
+def test_alternating_shapes_share_the_workspace(cuda_device):
+    """Calls of different shapes take turns on the per-device workspace, so the routing of one call
+    lies where the other call keeps slot rows or activations.  The kernels of a call overlap
+    (programmatic dependent launch): one that read the routing before the align stage of ITS call
+    had written it would see the other call's bytes there.  Every call must reproduce its first
+    result bit for bit and leave the status word clear."""
+    from xkernels_b200 import ops
+
+    cfgs = [synth.Int4Config("a", M=64, K=2048, N=7168, E=48, top_k=8),
+            synth.Int4Config("b", M=1, K=2048, N=7168, E=48, top_k=8),
+            synth.Int4Config("c", M=40, K=1024, N=512, E=16, top_k=4)]
+    data = [synth.make_int4(c, seed=70 + i, device=cuda_device) for i, c in enumerate(cfgs)]
+    call = lambda d: xkb.fused_moe_int4_w4a16(d["A"], d["packed"], d["scale"], d["topk_ids"], d["topk_w"])  # noqa: E731
+    first = []
+    for d in data:
+        first.append(call(d))
+        ops.check_status(cuda_device)
+    for _round in range(8):
+        for d, want in zip(data, first):
+            got = call(d)
+            ops.check_status(cuda_device)
+            assert torch.equal(got, want)
+
+
 def prefill_token_sample(topk_ids: torch.Tensor, E: int, block: int, n_tokens: int, seed: int) -> torch.Tensor:
     """Token rows to check at the prefill configuration: for every expert the tokens whose slots sit
     at the first and the last position of the expert's sorted run (so the first and the last,

@@ -403,6 +403,9 @@ extern "C" int xkb_workspace_status(const void* workspace, void* stream_) {
   if (host == 2)
     return fail(XKB_ERR_DEVICE, "an MXFP4 scale byte in 191..254 (weights of 2^64 and more) is outside the range "
                                 "the tcgen05 dequantiser converts: status 0x2");
+  if ((host & 0xFF) == 3)
+    return fail(XKB_ERR_DEVICE, "a kernel read a routing value outside what the routing buffers hold and skipped the "
+                                "work: status 0x%x (site %d)", host, host >> 8);
   if (host != 0)
     return fail(XKB_ERR_DEVICE, "a kernel gave up a bounded wait: status 0x%x (wait site %d)", host, host >> 8);
   return XKB_OK;

@@ -224,6 +224,10 @@ struct TcParams {
   // Two GEMMs of one expert layer that overlap (see "block hand-over" at the kernel): the first
   // counts the finished read-outs of every token block in done_signal, the second waits until the
   // count of a block has reached done_target before it loads that block's activations.
+  // what the routing may hold at most: a kernel that reads a value outside records status 3 and
+  // skips the work instead of using it as an index
+  int max_blocks;               // token blocks the routing buffers were sized for
+  int num_experts;
   int32_t* done_signal;         // gate_up modes, or nullptr
   const int32_t* done_wait;     // the GEMM that consumes `act` as its tokens, or nullptr
   int done_target;
@@ -287,6 +291,7 @@ constexpr int kMxShift = 62;
 constexpr float kMxUnscale = 4611686018427387904.f;   // 2^62
 constexpr uint32_t kMxMaxScale = 190;
 constexpr int kErrMxScaleRange = 2;                  // status code: an e8m0 scale byte in 191..254
+constexpr int kErrBadRouting = 3;    // status code: a routing value read by a kernel was outside what the buffers can hold
 __device__ __forceinline__ uint32_t mx_scale_factor(uint32_t s) {
   // exponent field of 2^(s - 1 - kMxShift), twice; 0 for the NaN code
   const uint32_t f = (s + (uint32_t)(126 - kMxShift)) * 0x00800080u;
@@ -397,7 +402,10 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
   // tile index t -> (token block, row tile); the row tile varies fastest so that CTAs that run
   // together share the token block and walk through one expert's weights
   const int n_tiles = p.N / (mode_is_pair(MODE) ? 2 * kTileRows : kTileRows);
-  const int n_blocks = p.num_post[0] / BT;
+  const int n_post = __ldcg(p.num_post);   // the routing was written by kernels this one may overlap: L2 loads, after the wait
+  const bool routing_ok = n_post >= 0 && n_post <= p.max_blocks * BT;
+  if (!routing_ok && threadIdx.x == 0) atomicCAS(p.status, 0, kErrBadRouting + (1 << 8));
+  const int n_blocks = routing_ok ? n_post / BT : 0;
   const int total_tiles = n_blocks * n_tiles;   // the host checks that the worst case fits 31 bits
   const int k_stages = p.K / kStageK;   // 256-K stages per tile
   // "virtual" weight stages of a tile: two-matrix modes alternate the matrices stage by stage
@@ -405,7 +413,8 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
   const int v_stages = kMats * k_stages;
   // first weight row (in the [E * rows_per_expert] row space) of virtual stage vs of tile (b, nt)
   auto tile_row = [&](int b, int nt, int vs) -> int {
-    const int e = p.expert_ids[b];
+    int e = __ldcg(p.expert_ids + b);
+    if ((unsigned)e >= (unsigned)p.num_experts) { atomicCAS(p.status, 0, kErrBadRouting + (2 << 8)); e = 0; }
     if (MODE == kModeInt4) return e * p.N + nt * kTileRows;
     if (MODE == kModeInt4Pair) return e * p.N + (2 * nt + (vs & 1)) * kTileRows;
     if (MODE == kModeMxDown) return e * p.rows_per_expert + (2 * nt + (vs & 1)) * kTileRows;
@@ -576,7 +585,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
     // group's are requested when the tile joins the read-out queue, two stages before they are used:
     // a read-out then never waits for global memory.
     auto load_cols = [&](int b, int c0, int32_t& slot, float& w) {
-      slot = (lane < 16 && c0 < BT) ? __ldg(p.sorted_ids + (int64_t)b * BT + c0 + lane) : -1;
+      slot = (lane < 16 && c0 < BT) ? __ldcg(p.sorted_ids + (int64_t)b * BT + c0 + lane) : -1;   // written by a kernel this one overlaps: no .nc load
       const bool live = slot >= 0 && slot < p.numel;
       w = (!mode_is_gate_up(MODE) && p.mul_w && live) ? __ldg(p.topk_w + slot) : 1.f;
     };
@@ -596,7 +605,9 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
       const int64_t n_glob = (int64_t)nt * (mode_is_pair(MODE) ? 2 * kTileRows : kTileRows) + row;
       float bias0 = 0.f, bias1 = 0.f;
       if (!mode_is_int4(MODE) && p.bias != nullptr) {
-        const int64_t e_row = (int64_t)p.expert_ids[b] * p.rows_per_expert;
+        int e_bias = __ldcg(p.expert_ids + b);
+        if ((unsigned)e_bias >= (unsigned)p.num_experts) e_bias = 0;   // recorded by the weight producer
+        const int64_t e_row = (int64_t)e_bias * p.rows_per_expert;
         bias0 = __bfloat162float(p.bias[e_row + n_glob]);
         if (MODE == kModeMxGateUp) bias1 = __bfloat162float(p.bias[e_row + p.N + n_glob]);
         if (MODE == kModeMxDown) bias1 = __bfloat162float(p.bias[e_row + n_glob + kTileRows]);
@@ -867,16 +878,26 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
 // Padding positions are left untouched: their accumulator columns are never read.
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
-gather_permute_kernel(const __nv_bfloat16* __restrict__ A, const int32_t* __restrict__ sorted_ids,
-                      const int32_t* __restrict__ num_post, __nv_bfloat16* __restrict__ Ag, int64_t numel,
-                      int K, int top_k, int permute, int32_t* __restrict__ zero, int zero_n) {
+gather_permute_kernel(const __nv_bfloat16* __restrict__ A, const int32_t* sorted_ids,
+                      const int32_t* num_post, __nv_bfloat16* __restrict__ Ag, int64_t numel,
+                      int K, int top_k, int permute, int32_t* __restrict__ zero, int zero_n, int64_t max_pad,
+                      int* __restrict__ status) {
+  // The routing comes from the align kernel before this one, which may still be running when this
+  // kernel starts.  It is read with L2 loads after the wait and through pointers that are NOT
+  // `const __restrict__`: loads the compiler may treat as invariant (ld.global.nc) were seen to
+  // deliver the value from before the align kernel's write (hoisted above the wait, or served from
+  // the non-coherent cache).
+  chain_wait();
   chain_trigger();
-  chain_wait();             // the routing comes from the align kernel before this one
   // the per-block counters of the block hand-over between the two GEMMs that follow (if any)
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < zero_n; i += gridDim.x * blockDim.x) zero[i] = 0;
-  const int total = num_post[0];
+  int total = __ldcg(num_post);
+  if (total < 0 || total > max_pad) {   // never with a routing the align stage wrote: recorded, nothing gathered
+    if (threadIdx.x == 0 && blockIdx.x == 0) atomicCAS(status, 0, kErrBadRouting + (3 << 8));
+    total = 0;
+  }
   for (int64_t pos = blockIdx.x; pos < total; pos += gridDim.x) {
-    const int32_t slot = sorted_ids[pos];
+    const int32_t slot = __ldcg(sorted_ids + pos);
     if (slot < 0 || slot >= numel) continue;
     const uint4* src = reinterpret_cast<const uint4*>(A + (int64_t)(slot / top_k) * K);
     uint4* dst = reinterpret_cast<uint4*>(Ag + pos * K);
@@ -1010,7 +1031,7 @@ int launch_int4_tc(const void* A, const int32_t* packed, const void* scale, cons
   if (gblocks < 1) gblocks = 1;
   XKB_CHECK_CUDA(launch_chained(gather_permute_kernel, dim3((unsigned)gblocks), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(A),
                                                                r.sorted_ids, r.num_post, Ag, r.numel, (int)K,
-                                                               top_k, 1, static_cast<int32_t*>(nullptr), 0));
+                                                               top_k, 1, static_cast<int32_t*>(nullptr), 0, r.max_pad, status));
   XKB_CHECK_LAUNCH("gather_permute_kernel");
 
   CUtensorMap tm_packed, tm_scale, tm_tokens;
@@ -1032,6 +1053,8 @@ int launch_int4_tc(const void* A, const int32_t* packed, const void* scale, cons
   prm.scratch = scratch;
   prm.status = status;
   prm.numel = r.numel;
+  prm.max_blocks = (int)r.max_blocks;
+  prm.num_experts = E;
   prm.N = (int)N;
   prm.K = (int)K;
   prm.mul_w = mul_w;
@@ -1066,7 +1089,7 @@ int launch_int4_ffn_tc(const void* A, const int32_t* w13, const void* s13, const
   int64_t gblocks = r.max_pad < 148 * 16 ? r.max_pad : 148 * 16;
   if (gblocks < 1) gblocks = 1;
   XKB_CHECK_CUDA(launch_chained(gather_permute_kernel, dim3((unsigned)gblocks), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(A), r.sorted_ids,
-                                                               r.num_post, Ag, r.numel, (int)hidden, top_k, 1, done, (int)r.max_blocks));
+                                                               r.num_post, Ag, r.numel, (int)hidden, top_k, 1, done, (int)r.max_blocks, r.max_pad, status));
   XKB_CHECK_LAUNCH("gather_permute_kernel");
   CUtensorMap tm_w13, tm_s13, tm_w2, tm_s2, tm_tok0, tm_tok1;
   int rc = make_map_2d(&tm_w13, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w13, (uint64_t)E * 2 * inter, (uint64_t)hidden / 2,
@@ -1095,6 +1118,8 @@ int launch_int4_ffn_tc(const void* A, const int32_t* w13, const void* s13, const
   prm.topk_w = topk_w;
   prm.status = status;
   prm.numel = r.numel;
+  prm.max_blocks = (int)r.max_blocks;
+  prm.num_experts = E;
   prm.bias = nullptr;
   prm.limit = limit;
   // gate_up + SwiGLU -> act
@@ -1170,7 +1195,7 @@ int launch_mxfp4_tc(const void* A, const uint8_t* w13, const uint8_t* w13_scale,
                                                                r.sorted_ids, r.num_post, Ag, r.numel,
                                                                (int)hidden, top_k,
                                                                r.block == 16 ? 0 : 1,   // 16-token tiles convert through the table: natural K order
-                                                               done, (int)r.max_blocks));
+                                                               done, (int)r.max_blocks, r.max_pad, status));
   XKB_CHECK_LAUNCH("gather_permute_kernel");
 
   CUtensorMap tm_w13, tm_w2, tm_tok0, tm_tok1, tm_s13, tm_s2;
@@ -1200,6 +1225,8 @@ int launch_mxfp4_tc(const void* A, const uint8_t* w13, const uint8_t* w13_scale,
   prm.topk_w = topk_w;
   prm.status = status;
   prm.numel = r.numel;
+  prm.max_blocks = (int)r.max_blocks;
+  prm.num_experts = E;
   prm.mul_w = mul_w;
   prm.round_rows = 0;
   prm.limit = limit;

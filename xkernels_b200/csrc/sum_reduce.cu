@@ -15,7 +15,7 @@ namespace {
 template <typename T> struct Vec8;
 template <> struct Vec8<__nv_bfloat16> {
   static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
-    const uint4 r = __ldg(reinterpret_cast<const uint4*>(p));
+    const uint4 r = *reinterpret_cast<const uint4*>(p);   // plain loads: the rows may come from a kernel this one overlaps
     const uint32_t u[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -35,8 +35,8 @@ template <> struct Vec8<__nv_bfloat16> {
 };
 template <> struct Vec8<float> {
   static __device__ __forceinline__ void load(const float* p, float (&v)[8]) {
-    const float4 a = __ldg(reinterpret_cast<const float4*>(p));
-    const float4 b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    const float4 b = *(reinterpret_cast<const float4*>(p) + 1);
     v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
     v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
   }
@@ -68,10 +68,13 @@ __device__ __forceinline__ bool slot_valid(const int32_t* ids, const int32_t* em
 
 template <typename TY, typename TW, typename TO>
 __global__ void __launch_bounds__(256)
-sum_reduce_vec8_kernel(const TY* __restrict__ y, const TW* __restrict__ w, TO* __restrict__ out,
+sum_reduce_vec8_kernel(const TY* y, const TW* __restrict__ w, TO* __restrict__ out,
                        int64_t M, int top_k, int64_t H, float rsf, const int32_t* __restrict__ ids,
                        const int32_t* __restrict__ emap, int num_map, int E) {
-  chain_wait();   // as the combine of a fused call: the slot rows come from the GEMM kernel before this one
+  // As the combine of a fused call the slot rows come from the GEMM kernel before this one, which is
+  // still running when this kernel starts: `y` is therefore not `const __restrict__` (no invariant /
+  // non-coherent loads, which may deliver what was there before the wait).
+  chain_wait();
   const int64_t hv = H >> 3;  // 8-wide columns per row
   const int64_t total = M * hv;
   for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
