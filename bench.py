@@ -482,28 +482,83 @@ def extras(dev, peaks):
     from xkernels_b200 import _lib, ops, synth
 
     out = {}
+    def settle():
+        # a long tensor-bound run leaves the SM clock under the power cap for a while; the short
+        # configurations are timed first and every block starts from an idle, synchronised device
+        torch.cuda.synchronize()
+        time.sleep(0.5)
+
     try:
-        cfg = synth.CONFIGS["int4_prefill"]
-        d = synth.make_int4(cfg, seed=1729, device=dev)
-        fn = lambda: xkb.fused_moe_int4_w4a16(d["A"], d["packed"], d["scale"], d["topk_ids"], d["topk_w"])  # noqa: E731
-        for _ in range(2):
+        cfg = synth.CONFIGS["mxfp4_decode"]
+        d = synth.make_mxfp4(cfg, seed=1729, device=dev)
+        n_active = int(torch.unique(d["topk_ids"]).numel())
+        fn = lambda: xkb.fused_moe_mxfp4(d["A"], d["w13"], d["w13_scale"], d["w2"], d["w2_scale"],  # noqa: E731
+                                         d["topk_ids"], d["topk_w"])
+        for _ in range(3):
             fn()
         torch.cuda.synchronize()
-        _lib.gemm_timer_enable(5)           # armed after the warm-up: five timed launches, five pairs
-        ms = time_call(fn, 0, 5)
+        _lib.gemm_timer_enable(64)          # two GEMM kernels (gate_up, down) per call
+        ms = time_call(fn, 0, 20)
         g = _lib.gemm_timer_read()
         _lib.gemm_timer_enable(0)
         ops.check_status(dev)
-        gm = sum(g) / len(g)
-        tf = synth.int4_flops(cfg) / (gm * 1e-3) / 1e12
-        al = time_call(lambda: xkb.moe_align_block_size(d["topk_ids"], 16, cfg.E, truncate=False), 3, 20)
-        out["int4_prefill"] = {"ms_per_call": ms, "tokens_per_s": cfg.M / (ms * 1e-3), "gemm_kernel_ms": gm,
-                               "gemm_tflops": tf, "frac_of_bf16_peak": tf / peaks["bf16_tflops"],
-                               "align_block16_us": al * 1e3}
+        gm = sum(g) / 20
+        b = synth.mxfp4_algorithmic_bytes(cfg, n_active)
+        out["mxfp4_decode"] = {"us_per_call": ms * 1e3, "gemm_kernels_us": gm * 1e3, "active_experts": n_active,
+                               "algorithmic_bytes": b, "gemm_gbs": b / (gm * 1e-3) / 1e9,
+                               "frac_of_hbm_peak": b / (gm * 1e-3) / 1e9 / peaks["hbm_gbs"]}
         del d
     except Exception as exc:  # noqa: BLE001
-        out["int4_prefill"] = {"error": repr(exc)[:300]}
+        out["mxfp4_decode"] = {"error": repr(exc)[:300]}
     torch.cuda.empty_cache()
+    settle()
+    try:
+        # the decode call captured in a CUDA graph (the call is stream-ordered end to end): launch
+        # overhead of its four kernels collapses into one graph launch
+        cfg = synth.CONFIGS["int4_decode"]
+        d = synth.make_int4(cfg, seed=1729, device=dev)
+        fn = lambda: xkb.fused_moe_int4_w4a16(d["A"], d["packed"], d["scale"], d["topk_ids"], d["topk_w"],  # noqa: E731
+                                              group_size=cfg.group_size)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                fn()
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            fn()
+        ms = time_call(graph.replay, 3, 50)
+        out["int4_decode_cuda_graph"] = {"us_per_call": ms * 1e3, "tokens_per_s": cfg.M / (ms * 1e-3)}
+        del d, graph
+    except Exception as exc:  # noqa: BLE001
+        out["int4_decode_cuda_graph"] = {"error": repr(exc)[:300]}
+    torch.cuda.empty_cache()
+    settle()
+    try:
+        M, E, top_k = 16384, 256, 8          # the router in front of the prefill configuration
+        logits = torch.randn(M, E, device=dev).to(torch.bfloat16)
+        ms = time_call(lambda: xkb.topk_softmax(logits, top_k, True), 3, 20)
+        b = M * E * 2 + M * top_k * 8
+        out["topk_softmax_16384x256_top8_bf16"] = {"us_per_call": ms * 1e3, "gbs": b / (ms * 1e-3) / 1e9,
+                                                   "frac_of_hbm_peak": b / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                                                   "note": "8.9 MB per call: fits in L2, launch-latency sized"}
+    except Exception as exc:  # noqa: BLE001
+        out["topk_softmax_16384x256_top8_bf16"] = {"error": repr(exc)[:300]}
+    torch.cuda.empty_cache()
+    settle()
+    try:
+        M, top_k, H = 8192, 8, 7168
+        y = torch.randn(M, top_k, H, device=dev, dtype=torch.bfloat16)
+        w = torch.rand(M, top_k, device=dev)
+        ms = time_call(lambda: xkb.moe_sum_reduce(y, w), 3, 20)
+        b = M * top_k * H * 2 + M * top_k * 4 + M * H * 2
+        out["moe_sum_reduce_8192x8x7168_bf16"] = {"us_per_call": ms * 1e3, "gbs": b / (ms * 1e-3) / 1e9,
+                                                  "frac_of_hbm_peak": b / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+    except Exception as exc:  # noqa: BLE001
+        out["moe_sum_reduce_8192x8x7168_bf16"] = {"error": repr(exc)[:300]}
+    torch.cuda.empty_cache()
+    settle()
     try:
         # The two expert-GEMM shapes of the reference's own INT4 benchmark (E=48, top_k=8, group 32;
         # meta/benchmarks/bench_moe_int4_w4a16.py:3-12,88-91): gate_up N=4096 K=7168 and the
@@ -513,6 +568,7 @@ def extras(dev, peaks):
         for name, (N, K) in {"gate_up_N4096_K7168": (4096, 7168), "down_N7168_K2048": (7168, 2048)}.items():
             packed, scale = synth.int4_weights(48, N, K, 32, seed=11, device=dev)
             rows = {}
+            settle()
             for M in (1, 16, 64, 512, 4096):
                 cfg = synth.Int4Config(name, M=M, K=K, N=N, E=48, top_k=8)
                 A = synth.activations(M, K, seed=M, device=dev)
@@ -539,72 +595,28 @@ def extras(dev, peaks):
     except Exception as exc:  # noqa: BLE001
         out["int4_kimi_shapes"] = {"error": repr(exc)[:300]}
     torch.cuda.empty_cache()
+    settle()
     try:
-        cfg = synth.CONFIGS["mxfp4_decode"]
-        d = synth.make_mxfp4(cfg, seed=1729, device=dev)
-        n_active = int(torch.unique(d["topk_ids"]).numel())
-        fn = lambda: xkb.fused_moe_mxfp4(d["A"], d["w13"], d["w13_scale"], d["w2"], d["w2_scale"],  # noqa: E731
-                                         d["topk_ids"], d["topk_w"])
-        for _ in range(3):
+        cfg = synth.CONFIGS["int4_prefill"]
+        d = synth.make_int4(cfg, seed=1729, device=dev)
+        fn = lambda: xkb.fused_moe_int4_w4a16(d["A"], d["packed"], d["scale"], d["topk_ids"], d["topk_w"])  # noqa: E731
+        for _ in range(2):
             fn()
         torch.cuda.synchronize()
-        _lib.gemm_timer_enable(64)          # two GEMM kernels (gate_up, down) per call
-        ms = time_call(fn, 0, 20)
+        _lib.gemm_timer_enable(5)           # armed after the warm-up: five timed launches, five pairs
+        ms = time_call(fn, 0, 5)
         g = _lib.gemm_timer_read()
         _lib.gemm_timer_enable(0)
         ops.check_status(dev)
-        gm = sum(g) / 20
-        b = synth.mxfp4_algorithmic_bytes(cfg, n_active)
-        out["mxfp4_decode"] = {"us_per_call": ms * 1e3, "gemm_kernels_us": gm * 1e3, "active_experts": n_active,
-                               "algorithmic_bytes": b, "gemm_gbs": b / (gm * 1e-3) / 1e9,
-                               "frac_of_hbm_peak": b / (gm * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+        gm = sum(g) / len(g)
+        tf = synth.int4_flops(cfg) / (gm * 1e-3) / 1e12
+        al = time_call(lambda: xkb.moe_align_block_size(d["topk_ids"], 16, cfg.E, truncate=False), 3, 20)
+        out["int4_prefill"] = {"ms_per_call": ms, "tokens_per_s": cfg.M / (ms * 1e-3), "gemm_kernel_ms": gm,
+                               "gemm_tflops": tf, "frac_of_bf16_peak": tf / peaks["bf16_tflops"],
+                               "align_block16_us": al * 1e3}
         del d
     except Exception as exc:  # noqa: BLE001
-        out["mxfp4_decode"] = {"error": repr(exc)[:300]}
-    torch.cuda.empty_cache()
-    try:
-        # the decode call captured in a CUDA graph (the call is stream-ordered end to end): launch
-        # overhead of its four kernels collapses into one graph launch
-        cfg = synth.CONFIGS["int4_decode"]
-        d = synth.make_int4(cfg, seed=1729, device=dev)
-        fn = lambda: xkb.fused_moe_int4_w4a16(d["A"], d["packed"], d["scale"], d["topk_ids"], d["topk_w"],  # noqa: E731
-                                              group_size=cfg.group_size)
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            for _ in range(3):
-                fn()
-        torch.cuda.current_stream().wait_stream(side)
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            fn()
-        ms = time_call(graph.replay, 3, 50)
-        out["int4_decode_cuda_graph"] = {"us_per_call": ms * 1e3, "tokens_per_s": cfg.M / (ms * 1e-3)}
-        del d, graph
-    except Exception as exc:  # noqa: BLE001
-        out["int4_decode_cuda_graph"] = {"error": repr(exc)[:300]}
-    torch.cuda.empty_cache()
-    try:
-        M, E, top_k = 16384, 256, 8          # the router in front of the prefill configuration
-        logits = torch.randn(M, E, device=dev).to(torch.bfloat16)
-        ms = time_call(lambda: xkb.topk_softmax(logits, top_k, True), 3, 20)
-        b = M * E * 2 + M * top_k * 8
-        out["topk_softmax_16384x256_top8_bf16"] = {"us_per_call": ms * 1e3, "gbs": b / (ms * 1e-3) / 1e9,
-                                                   "frac_of_hbm_peak": b / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
-                                                   "note": "8.9 MB per call: fits in L2, launch-latency sized"}
-    except Exception as exc:  # noqa: BLE001
-        out["topk_softmax_16384x256_top8_bf16"] = {"error": repr(exc)[:300]}
-    torch.cuda.empty_cache()
-    try:
-        M, top_k, H = 8192, 8, 7168
-        y = torch.randn(M, top_k, H, device=dev, dtype=torch.bfloat16)
-        w = torch.rand(M, top_k, device=dev)
-        ms = time_call(lambda: xkb.moe_sum_reduce(y, w), 3, 20)
-        b = M * top_k * H * 2 + M * top_k * 4 + M * H * 2
-        out["moe_sum_reduce_8192x8x7168_bf16"] = {"us_per_call": ms * 1e3, "gbs": b / (ms * 1e-3) / 1e9,
-                                                  "frac_of_hbm_peak": b / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
-    except Exception as exc:  # noqa: BLE001
-        out["moe_sum_reduce_8192x8x7168_bf16"] = {"error": repr(exc)[:300]}
+        out["int4_prefill"] = {"error": repr(exc)[:300]}
     torch.cuda.empty_cache()
     return out
 
