@@ -639,7 +639,7 @@ def run_multi_gpu(args, world: int, rank: int, local_rank: int):
     packed, scale = synth.int4_weights(e_local, cfg.N, cfg.K, cfg.group_size, seed=1730 + 7 * rank, device=dev)
     layer = ep.ExpertParallelInt4(packed, scale, num_global_experts=cfg.E, group=dist.group.WORLD,
                                   group_size=cfg.group_size, placement=args.ep_placement, chunks=args.ep_chunks,
-                                  sm_margin=args.ep_sm_margin)
+                                  sm_margin=args.ep_sm_margin, local_first=bool(args.ep_local_first))
     # model set-up, outside the timed region: the most popular experts (measured on this batch's
     # routing) are copied to every rank; their slots are then served where the token lives
     hot = layer.rebalance(ids, args.ep_replicas) if args.ep_replicas > 0 else []
@@ -753,7 +753,7 @@ def run_multi_gpu(args, world: int, rank: int, local_rank: int):
                          "peak_source": peaks["source"] + " (sustained)"},
             "slots_received_per_rank": slots,
             "rows_received_per_rank": rows_in,   # one activation row per (token, rank) pair crosses the wire
-            "ep": {"placement": args.ep_placement, "chunks": args.ep_chunks, "sm_margin": args.ep_sm_margin,
+            "ep": {"placement": args.ep_placement, "chunks": args.ep_chunks, "sm_margin": args.ep_sm_margin, "local_first": layer.local_first,
                    "replicated_experts": hot,
                    "same_config_on_one_gpu": single,
                    # weak scaling against the SAME configuration on one GPU (the N=1 line of this
@@ -815,6 +815,8 @@ def main():
     ap.add_argument("--ep-chunks", type=int, default=1, help="token chunks pipelined through the exchanges")
     ap.add_argument("--ep-replicas", type=int, default=4,
                     help="most popular experts copied to every rank (their slots stay on the token's rank)")
+    ap.add_argument("--ep-local-first", type=int, default=1, choices=[0, 1],
+                    help="compute the slots of a rank's own experts beside the exchange instead of sending them to itself")
     ap.add_argument("--ep-sm-margin", type=int, default=16,
                     help="SMs the GEMM kernels leave to the exchange kernels when chunks > 1")
     ap.add_argument("--case", default=None, choices=sorted(PROFILE_CASES),

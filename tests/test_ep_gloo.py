@@ -48,7 +48,7 @@ def _cpu_reduce(rows, row_index, M, dtype):
 
 
 def _worker(rank: int, world: int, port: int, fail_rank: int, placement: str = "contiguous", chunks: int = 1,
-            n_replicas: int = 0):
+            n_replicas: int = 0, local_first: bool = True):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
@@ -59,8 +59,9 @@ def _worker(rank: int, world: int, port: int, fail_rank: int, placement: str = "
         ids, w = synth.routing(CFG.M, CFG.E, CFG.top_k, seed=200 + rank, zipf_scale=CFG.zipf_scale)
         layer = ep.ExpertParallelInt4(packed[sl], scale[sl], num_global_experts=CFG.E, group_size=32,
                                       partial_fn=_oracle_partial(packed[sl], scale[sl]), reduce_fn=_cpu_reduce,
-                                      placement=placement, chunks=chunks,
+                                      placement=placement, chunks=chunks, local_first=local_first,
                                       max_recv_rows=0 if rank == fail_rank else None)
+        assert layer.local_first == (local_first and chunks == 1)
         if fail_rank >= 0:
             # capacity check: EVERY rank raises the same refusal before any payload moves, so none
             # is left waiting in the dispatch all-to-all
@@ -98,24 +99,29 @@ def _worker(rank: int, world: int, port: int, fail_rank: int, placement: str = "
         plan = ep.plan_dispatch(ids, e_local, world, placement, chunks)
         owners = ep.owner_and_local(ids.long(), e_local, world, placement)[0]
         n_pairs = sum(len(set(row.tolist())) for row in owners)
-        assert sum(layer.last_send_counts) == n_pairs == plan.pair_token.numel() <= CFG.M * CFG.top_k
+        assert n_pairs == plan.pair_token.numel() <= CFG.M * CFG.top_k
+        # local-first: a token's slots on this rank's own experts never enter the exchange
+        n_home = sum(1 for row in owners if rank in row.tolist()) if layer.local_first else 0
+        assert sum(layer.last_send_counts) == n_pairs - n_home
+        assert not layer.local_first or layer.last_send_counts[rank] == 0
         total = torch.tensor([layer.last_recv_rows, layer.count_recv_slots()])
         dist.all_reduce(total)
-        pairs_all = torch.tensor([n_pairs])
+        pairs_all = torch.tensor([n_pairs - n_home])
         dist.all_reduce(pairs_all)
         assert int(total[0]) == int(pairs_all) and int(total[1]) == world * CFG.M * CFG.top_k
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,placement,chunks", [(2, "contiguous", 1), (4, "contiguous", 1),
-                                                     (2, "round_robin", 3), (4, "round_robin", 2),
-                                                     (4, "snake", 1)])
-def test_all_to_all_matches_dense_oracle(world, placement, chunks):
-    mp.spawn(_worker, args=(world, _free_port(), -1, placement, chunks), nprocs=world, join=True)
+@pytest.mark.parametrize("world,placement,chunks,local_first", [
+    (2, "contiguous", 1, True), (4, "contiguous", 1, True), (2, "contiguous", 1, False),
+    (2, "round_robin", 3, True), (4, "round_robin", 2, True), (4, "snake", 1, True), (4, "snake", 1, False)])
+def test_all_to_all_matches_dense_oracle(world, placement, chunks, local_first):
+    mp.spawn(_worker, args=(world, _free_port(), -1, placement, chunks, 0, local_first), nprocs=world, join=True)
 
 
-@pytest.mark.parametrize("world,placement,chunks,n_replicas", [(2, "contiguous", 1, 2), (4, "round_robin", 2, 3)])
+@pytest.mark.parametrize("world,placement,chunks,n_replicas", [(2, "contiguous", 1, 2), (4, "round_robin", 2, 3),
+                                                               (4, "snake", 1, 3)])
 def test_replicated_popular_experts_keep_the_result_and_cut_the_traffic(world, placement, chunks, n_replicas):
     mp.spawn(_worker, args=(world, _free_port(), -1, placement, chunks, n_replicas), nprocs=world, join=True)
 

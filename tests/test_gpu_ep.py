@@ -114,6 +114,25 @@ def test_device_plan_with_replicas_equals_host_plan(cuda_device):
     assert int(want.pair_ids.max()) >= E // world          # replica slots use the indices behind the own experts
 
 
+def test_device_plan_leaves_home_experts_out(cuda_device):
+    """Local-first mode: experts the rank serves itself carry destination -1 in the table and open no
+    pair, in xkb_ep_plan as in ep.plan_dispatch."""
+    from xkernels_b200 import ep
+
+    M, E, top_k, world, rank = 257, 32, 6, 4, 1
+    ids, w = synth.routing(M, E, top_k, seed=11, zipf_scale=2.0)
+    table = ep.expert_table(E // world, world, "snake", rank=rank, replicas=[3, 9], home_is_not_dispatched=True)
+    assert int((table[:, 0] < 0).sum()) == E // world + 2
+    want = ep.plan_dispatch(ids, E // world, world, "snake", 1, table=table)
+    pt, pd, routing, pair_of, counts, info = ops.ep_plan(ids.to(cuda_device), w.to(cuda_device), E // world, world,
+                                                          "snake", 1, table=table.to(cuda_device))
+    P = want.pair_token.numel()
+    assert info.tolist() == [P, 0] and counts.cpu().tolist() == want.send_counts.tolist()
+    assert counts.cpu()[0, rank] == 0 and bool((pair_of.cpu()[:, rank] == -1).all())
+    assert torch.equal(pt[:P].cpu().long(), want.pair_token) and torch.equal(pd[:P].cpu().long(), want.pair_dest)
+    assert torch.equal(routing[:P, :top_k].cpu(), want.pair_ids) and torch.equal(pair_of.cpu(), want.pair_of)
+
+
 def test_gather_rows_with_the_count_on_the_device(cuda_device):
     g = torch.Generator().manual_seed(2)
     src = torch.randn(50, 64, generator=g).to(torch.bfloat16).to(cuda_device)
@@ -152,8 +171,10 @@ def _ep_worker(rank: int, world: int, port: int, placement: str, chunks: int, n_
         if n_replicas:
             hot = layer.rebalance(ids.to(dev), n_replicas)
             assert len(hot) == n_replicas and layer.packed.shape[0] == e_local + n_replicas
+        assert layer.local_first == (chunks == 1)
         out = layer(A.to(dev), ids.to(dev), w.to(dev))
         ops.check_status(dev)
+        ops.check_status(dev, tag=2)          # the workspace of the local pass
         want = oracle.moe_w4a16(A, packed, scale, ids, w, 32)
         bad = oracle.count_violations(out.cpu(), want, 2e-2, 1e-2)
         assert bad == 0, f"rank {rank}: {bad} elements differ from the dense oracle"

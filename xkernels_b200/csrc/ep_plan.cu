@@ -1,6 +1,8 @@
 // Dispatch plan of the all-to-all expert-parallel mode, on the device and without a host read.
 //
-// A token goes once to every rank that owns at least one of its top-k experts.  The plan lists those
+// A token goes once to every rank that owns at least one of its top-k experts (an expert whose table
+// entry has a negative rank is served without dispatch - the caller computes it where the token is -
+// and opens no pair).  The plan lists those
 // (token, rank) pairs grouped by (token chunk, rank), ascending token inside a group, and for every
 // pair the routing that travels with it.  Three launches: a key per slot (the rank of a slot that
 // opens a pair, "none" otherwise), the counting sort of the align stage with one position per
@@ -46,7 +48,7 @@ ep_key_kernel(const int32_t* __restrict__ topk_ids, int64_t M, int top_k, int ex
     d[j] = o;
     bool first = true;
     for (int i = 0; i < j; ++i) first = first && (d[i] != o);
-    key[m * top_k + j] = first ? chunk * world + o : -1;
+    key[m * top_k + j] = (first && o >= 0) ? chunk * world + o : -1;   // o < 0 (table only): not dispatched
     dest[m * top_k + j] = o;
     local[m * top_k + j] = l;
   }

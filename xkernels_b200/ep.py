@@ -98,10 +98,12 @@ class DispatchPlan:
 
 
 def expert_table(experts_per_rank: int, world: int, placement: str, rank: int | None = None,
-                 replicas: list[int] | tuple[int, ...] = ()) -> torch.Tensor:
+                 replicas: list[int] | tuple[int, ...] = (), home_is_not_dispatched: bool = False) -> torch.Tensor:
     """``[E, 2]`` int32: (destination rank, expert index there) of every global expert as rank ``rank``
     sees it.  Experts in ``replicas`` (global ids, in replica order) are held by every rank behind its
-    own ``experts_per_rank`` experts, so their destination is ``rank`` itself."""
+    own ``experts_per_rank`` experts, so their destination is ``rank`` itself.  With
+    ``home_is_not_dispatched`` the experts served by ``rank`` itself get destination -1: the plan then
+    opens no pair for them (the layer computes them where the token is, beside the exchange)."""
     E = experts_per_rank * world
     owner, local = owner_and_local(torch.arange(E, dtype=torch.int64), experts_per_rank, world, placement)
     table = torch.stack([owner, local], dim=1).to(torch.int32)
@@ -111,6 +113,10 @@ def expert_table(experts_per_rank: int, world: int, placement: str, rank: int | 
         for i, g in enumerate(replicas):
             table[int(g), 0] = rank
             table[int(g), 1] = experts_per_rank + i
+    if home_is_not_dispatched:
+        if rank is None:
+            raise ValueError("expert_table: home_is_not_dispatched needs the rank")
+        table[table[:, 0] == rank, 0] = -1
     return table
 
 
@@ -137,7 +143,7 @@ def plan_dispatch(topk_ids: torch.Tensor, experts_per_rank: int, world: int, pla
     # a slot opens a pair if no earlier slot of its token goes to the same rank
     same = dest.unsqueeze(2) == dest.unsqueeze(1)                                   # [M, j, i]
     earlier = torch.ones(top_k, top_k, dtype=torch.bool, device=dev).tril(-1)       # i < j
-    first = ~(same & earlier).any(dim=2)
+    first = ~(same & earlier).any(dim=2) & (dest >= 0)      # a negative destination (table) is not dispatched
     tokens_per_chunk = -(-M // chunks) if M else 1
     chunk = torch.div(torch.arange(M, device=dev), tokens_per_chunk, rounding_mode="floor").unsqueeze(1)
     sentinel = chunks * world                                                        # sorts behind every pair
@@ -145,7 +151,7 @@ def plan_dispatch(topk_ids: torch.Tensor, experts_per_rank: int, world: int, pla
     slot = torch.argsort(key, stable=True)             # pairs first, grouped by key, ascending token inside a key
     counts = torch.bincount(key, minlength=sentinel + 1)[:sentinel].view(chunks, world)
     pair_token = torch.div(slot, top_k, rounding_mode="floor")
-    pair_dest = dest.reshape(-1)[slot]
+    pair_dest = dest.reshape(-1)[slot].clamp(min=0)
     is_pair = key[slot] < sentinel
     mine = dest[pair_token] == pair_dest.unsqueeze(1)                               # [numel, top_k]
     pair_ids = torch.where(mine, local[pair_token], torch.full_like(local[pair_token], -1)).to(torch.int32)
@@ -253,7 +259,7 @@ class ExpertParallelInt4:
 
     def __init__(self, packed, scale, *, num_global_experts: int, group=None, group_size: int = 32,
                  placement: str = "contiguous", chunks: int = 1, partial_fn=None, reduce_fn=None,
-                 max_recv_rows: int | None = None, sm_margin: int = 16):
+                 max_recv_rows: int | None = None, sm_margin: int = 16, local_first: bool = True):
         self.group = group if group is not None else dist.group.WORLD
         self.world = dist.get_world_size(self.group)
         self.rank = dist.get_rank(self.group)
@@ -280,6 +286,13 @@ class ExpertParallelInt4:
         self.own_packed, self.own_scale = packed, scale
         self.replicas: list[int] = []    # global ids of the experts every rank holds a copy of
         self.table = None                # [E, 2] int32 on the weights' device when replicas exist
+        # Local-first: the slots whose expert this rank serves itself (its own experts and the
+        # replicas) never enter the exchange.  They are computed from the rank's own tokens on a
+        # second stream while the count exchange and the dispatch all-to-all are in flight, and
+        # their partial rows join the final sum at this rank's position.  Needs one chunk.
+        self.local_first = bool(local_first) and self.world > 1 and self.chunks == 1
+        self._home_tables = None         # (table as seen from this rank, the same with home experts marked -1)
+        self._side = None                # CUDA stream of the local pass
 
     # ---- replicas of popular experts -------------------------------------------------
     def set_replicas(self, global_ids, packed_rep=None, scale_rep=None) -> None:
@@ -289,6 +302,7 @@ class ExpertParallelInt4:
         E = self.e_local * self.world
         if len(set(global_ids)) != len(global_ids) or any(g < 0 or g >= E for g in global_ids):
             raise ValueError("set_replicas: ids must be distinct global expert ids")
+        self._home_tables = None
         if not global_ids:
             self.packed, self.scale, self.replicas, self.table = self.own_packed, self.own_scale, [], None
             return
@@ -349,9 +363,55 @@ class ExpertParallelInt4:
 
     # ---- one step ----------------------------------------------------------------------
     def __call__(self, A: torch.Tensor, topk_ids: torch.Tensor, topk_w: torch.Tensor) -> torch.Tensor:
+        try:
+            return self._step(A, topk_ids, topk_w)
+        finally:
+            # the SM margin is a process-wide setting of the library: never leave it behind, also not
+            # when the exchange was refused half-way
+            if A.is_cuda and self.sm_margin > 0 and (self.local_first or self.chunks > 1):
+                from . import _lib
+
+                _lib.set_sm_margin(0)
+
+    def _step(self, A: torch.Tensor, topk_ids: torch.Tensor, topk_w: torch.Tensor) -> torch.Tensor:
         M, K = A.shape
         top_k = topk_ids.shape[1]
         chunks = max(1, min(self.chunks, M))
+        local_first = self.local_first and M > 0
+        plan_table, home, rows_all, local_done = self.table, None, None, None
+        if local_first:
+            if self._home_tables is None:
+                full = expert_table(self.e_local, self.world, self.placement, self.rank, self.replicas)
+                away = expert_table(self.e_local, self.world, self.placement, self.rank, self.replicas,
+                                    home_is_not_dispatched=True)
+                self._home_tables = (full.to(A.device), away.to(A.device))
+            full, plan_table = self._home_tables
+            E = self.e_local * self.world
+            t = full[topk_ids.to(torch.int64).clamp(0, E - 1)]                       # [M, top_k, 2]; invalid ids are refused below
+            home_ids = torch.where(t[..., 0] == self.rank, t[..., 1], torch.full_like(t[..., 1], -1)).to(torch.int32)
+            home = (home_ids, topk_w.to(torch.float32))
+            # rows of the final sum: [0, M) this rank's own partial per token, then one row per pair
+            cap = M * min(top_k, self.world - 1)
+            rows_all = torch.empty((M + cap, self.N), dtype=torch.float32, device=A.device)
+            if A.is_cuda and self.partial_fn == self._partial_cuda:
+                from . import _lib, ops
+
+                if self._side is None:
+                    self._side = torch.cuda.Stream(device=A.device)
+                routing_home = torch.cat([home_ids, home[1].view(torch.int32)], dim=1).contiguous()
+                self._side.wait_stream(torch.cuda.current_stream(A.device))
+                if self.sm_margin > 0:
+                    _lib.set_sm_margin(self.sm_margin)   # the exchange kernels need SMs beside the persistent GEMMs
+                with torch.cuda.stream(self._side):
+                    ops.moe_int4_w4a16_partial(A, self.packed, self.scale, routing_home, group_size=self.group_size,
+                                               out=rows_all[:M], workspace_tag=2)
+                    local_done = torch.cuda.Event()
+                    local_done.record(self._side)
+                A.record_stream(self._side)
+                rows_all.record_stream(self._side)
+                routing_home.record_stream(self._side)
+            else:
+                rows_all[:M] = self.partial_fn(A, home_ids, home[1])
         if A.is_cuda:
             # the plan on the device (three launches, no host read); the one read of the count exchange
             # also brings the pair count and the invalid-id count.  The send buffer is filled by a
@@ -360,7 +420,7 @@ class ExpertParallelInt4:
             from . import ops
 
             pair_token, _dest, routing, pair_of, counts, info = ops.ep_plan(
-                topk_ids, topk_w, self.e_local, self.world, self.placement, chunks, table=self.table)
+                topk_ids, topk_w, self.e_local, self.world, self.placement, chunks, table=plan_table)
             pending = exchange_counts_begin(counts, self.group, n_bad=info[1], capacity=self.max_recv_rows,
                                             n_slots=M * top_k)
             send_all = ops.gather_rows(A, pair_token, info[0:1])          # [M * top_k, K]; the first P rows are set
@@ -369,7 +429,7 @@ class ExpertParallelInt4:
             pair_token, send_R, send_A = pair_token[:P], routing[:P], send_all[:P]
         else:
             plan = plan_dispatch(topk_ids, self.e_local, self.world, self.placement, chunks, host_checks=False,
-                                 table=self.table)
+                                 table=plan_table)
             send_l, recv_l = exchange_counts(plan.send_counts, self.group, n_bad=plan.n_bad,
                                              capacity=self.max_recv_rows, n_slots=M * top_k)
             P = sum(sum(r) for r in send_l)
@@ -384,7 +444,14 @@ class ExpertParallelInt4:
         self.last_recv_rows = n_recv
         self.last_send_counts = [sum(send_l[c][p] for c in range(chunks)) for p in range(self.world)]
 
-        back = torch.empty((P, self.N), dtype=torch.float32, device=A.device)
+        if local_first:
+            back = rows_all[M:M + P]
+            # this rank's own partial sits at its position in every token's row of the index, so the
+            # sum runs over the ranks in the same order as without the local pass
+            pair_of = torch.where(pair_of >= 0, pair_of + M, pair_of)
+            pair_of[:, self.rank] = torch.arange(M, dtype=pair_of.dtype, device=pair_of.device)
+        else:
+            back = torch.empty((P, self.N), dtype=torch.float32, device=A.device)
         use_async = A.is_cuda and chunks > 1
 
         # dispatch every chunk (in flight back to back on the communication stream) ...
@@ -403,7 +470,7 @@ class ExpertParallelInt4:
         # ... then per chunk: wait for its rows, expert GEMM + per-row sum, send the fp32 partials home
         back_works = []
         fused_partial = A.is_cuda and self.partial_fn == self._partial_cuda
-        margin = use_async and fused_partial and self.sm_margin > 0
+        margin = (use_async or local_done is not None) and fused_partial and self.sm_margin > 0
         if margin:
             from . import _lib
 
@@ -431,6 +498,11 @@ class ExpertParallelInt4:
             for wb, _p, _i in back_works:
                 wb.wait()
         self._last_routing = [r for _wb, _p, r in back_works]
+        if local_first:
+            if local_done is not None:
+                torch.cuda.current_stream(A.device).wait_event(local_done)
+            self._last_routing.append(torch.cat([home[0], home[1].view(torch.int32)], dim=1))
+            return self.reduce_fn(rows_all[:M + P], pair_of, M, A.dtype)
         return self.reduce_fn(back, pair_of, M, A.dtype)
 
     def count_recv_slots(self) -> int:

@@ -501,10 +501,12 @@ def moe_int4_w4a16_rows(A, packed, scale, topk_ids, topk_w=None, group_size=32, 
     return rows
 
 
-def moe_int4_w4a16_partial(A, packed, scale, routing, group_size=32, *, out=None, path="auto"):
+def moe_int4_w4a16_partial(A, packed, scale, routing, group_size=32, *, out=None, path="auto", workspace_tag=0):
     """Expert side of the all-to-all mode in one C call: ``A [R, K]`` received rows, ``routing
     [R, 2*top_k]`` int32 (local expert ids, -1 = elsewhere, then the routing weights' bit patterns)
-    -> ``[R, N]`` fp32, per row the weighted sum over its local experts in ascending slot order."""
+    -> ``[R, N]`` fp32, per row the weighted sum over its local experts in ascending slot order (a
+    row without a local expert comes out as zeros).  Two calls that overlap on different streams must
+    use different ``workspace_tag`` values (see :func:`get_workspace`)."""
     lib = _lib.load()
     dev = _require_cuda("moe_int4_w4a16_partial", A, packed, scale, routing, out)
     if A.dtype not in _DT:
@@ -530,7 +532,7 @@ def moe_int4_w4a16_partial(A, packed, scale, routing, group_size=32, *, out=None
         if R == 0:
             return out
         ws_bytes = int(lib.xkb_moe_int4_w4a16_partial_workspace_bytes(R, N, K, E, top_k, _DT[A.dtype]))
-        ws = get_workspace(dev, ws_bytes)
+        ws = get_workspace(dev, ws_bytes, tag=int(workspace_tag))
         _lib.check(
             lib.xkb_moe_int4_w4a16_partial(_ptr(A), _DT[A.dtype], _ptr(packed), _ptr(scale), _ptr(routing), _ptr(out),
                                            R, N, K, E, top_k, int(group_size), pcode, _ptr(ws), ws.numel(),
