@@ -675,11 +675,11 @@ def run_multi_gpu(args, world: int, rank: int, local_rank: int):
     if sampler:
         sampler.__exit__()
     launches = _lib.launch_count() - launches0
-    _lib.gemm_timer_enable(args.steps)          # kernel durations in a second pass (see run_single_gpu)
-    timed_loop(step, args.steps, sync, dist.barrier)
+    _lib.gemm_timer_enable(4 * args.steps)      # kernel durations in a second pass (see run_single_gpu);
+    timed_loop(step, args.steps, sync, dist.barrier)   # a step may launch more than one GEMM (local pass, chunks)
     gemm_ms = _lib.gemm_timer_read()
     _lib.gemm_timer_enable(0)
-    t = torch.tensor([ms, sum(gemm_ms) / max(len(gemm_ms), 1), float(layer.count_recv_slots()),
+    t = torch.tensor([ms, sum(gemm_ms) / args.steps, float(layer.count_recv_slots()),
                       float(layer.last_recv_rows)], device=dev, dtype=torch.float64)
     gathered = [torch.zeros_like(t) for _ in range(world)]
     dist.all_gather(gathered, t)
@@ -815,7 +815,7 @@ def main():
     ap.add_argument("--ep-chunks", type=int, default=1, help="token chunks pipelined through the exchanges")
     ap.add_argument("--ep-replicas", type=int, default=4,
                     help="most popular experts copied to every rank (their slots stay on the token's rank)")
-    ap.add_argument("--ep-local-first", type=int, default=1, choices=[0, 1],
+    ap.add_argument("--ep-local-first", type=int, default=0, choices=[0, 1],
                     help="compute the slots of a rank's own experts beside the exchange instead of sending them to itself")
     ap.add_argument("--ep-sm-margin", type=int, default=16,
                     help="SMs the GEMM kernels leave to the exchange kernels when chunks > 1")

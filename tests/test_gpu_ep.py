@@ -121,7 +121,7 @@ def test_device_plan_leaves_home_experts_out(cuda_device):
 
     M, E, top_k, world, rank = 257, 32, 6, 4, 1
     ids, w = synth.routing(M, E, top_k, seed=11, zipf_scale=2.0)
-    table = ep.expert_table(E // world, world, "snake", rank=rank, replicas=[3, 9], home_is_not_dispatched=True)
+    table = ep.expert_table(E // world, world, "snake", rank=rank, replicas=[3, 8], home_is_not_dispatched=True)
     assert int((table[:, 0] < 0).sum()) == E // world + 2
     want = ep.plan_dispatch(ids, E // world, world, "snake", 1, table=table)
     pt, pd, routing, pair_of, counts, info = ops.ep_plan(ids.to(cuda_device), w.to(cuda_device), E // world, world,
@@ -150,7 +150,8 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _ep_worker(rank: int, world: int, port: int, placement: str, chunks: int, n_replicas: int = 0):
+def _ep_worker(rank: int, world: int, port: int, placement: str, chunks: int, n_replicas: int = 0,
+               local_first: bool = False):
     import torch.distributed as dist
 
     from xkernels_b200 import ep
@@ -167,11 +168,11 @@ def _ep_worker(rank: int, world: int, port: int, placement: str, chunks: int, n_
         A = synth.activations(cfg.M, cfg.K, seed=100 + rank)
         ids, w = synth.routing(cfg.M, cfg.E, cfg.top_k, seed=200 + rank, zipf_scale=cfg.zipf_scale)
         layer = ep.ExpertParallelInt4(packed[sl].to(dev), scale[sl].to(dev), num_global_experts=cfg.E,
-                                      placement=placement, chunks=chunks)
+                                      placement=placement, chunks=chunks, local_first=local_first)
         if n_replicas:
             hot = layer.rebalance(ids.to(dev), n_replicas)
             assert len(hot) == n_replicas and layer.packed.shape[0] == e_local + n_replicas
-        assert layer.local_first == (chunks == 1)
+        assert layer.local_first == (local_first and chunks == 1)
         out = layer(A.to(dev), ids.to(dev), w.to(dev))
         ops.check_status(dev)
         ops.check_status(dev, tag=2)          # the workspace of the local pass
@@ -185,13 +186,14 @@ def _ep_worker(rank: int, world: int, port: int, placement: str, chunks: int, n_
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("placement,chunks,n_replicas", [("contiguous", 1, 0), ("round_robin", 3, 0), ("snake", 1, 0),
-                                                         ("round_robin", 1, 3)])
-def test_all_to_all_on_gpus(placement, chunks, n_replicas):
+@pytest.mark.parametrize("placement,chunks,n_replicas,local_first", [
+    ("contiguous", 1, 0, False), ("round_robin", 3, 0, False), ("snake", 1, 0, True), ("round_robin", 1, 3, False),
+    ("round_robin", 1, 3, True)])
+def test_all_to_all_on_gpus(placement, chunks, n_replicas, local_first):
     n = torch.cuda.device_count()
     if n < 2:
         pytest.skip("needs at least 2 GPUs")
     import torch.multiprocessing as mp
 
     world = 4 if n >= 4 else 2
-    mp.spawn(_ep_worker, args=(world, _free_port(), placement, chunks, n_replicas), nprocs=world, join=True)
+    mp.spawn(_ep_worker, args=(world, _free_port(), placement, chunks, n_replicas, local_first), nprocs=world, join=True)

@@ -259,7 +259,7 @@ class ExpertParallelInt4:
 
     def __init__(self, packed, scale, *, num_global_experts: int, group=None, group_size: int = 32,
                  placement: str = "contiguous", chunks: int = 1, partial_fn=None, reduce_fn=None,
-                 max_recv_rows: int | None = None, sm_margin: int = 16, local_first: bool = True):
+                 max_recv_rows: int | None = None, sm_margin: int = 16, local_first: bool = False):
         self.group = group if group is not None else dist.group.WORLD
         self.world = dist.get_world_size(self.group)
         self.rank = dist.get_rank(self.group)
@@ -368,7 +368,7 @@ class ExpertParallelInt4:
         finally:
             # the SM margin is a process-wide setting of the library: never leave it behind, also not
             # when the exchange was refused half-way
-            if A.is_cuda and self.sm_margin > 0 and (self.local_first or self.chunks > 1):
+            if A.is_cuda and self.sm_margin > 0 and self.chunks > 1:
                 from . import _lib
 
                 _lib.set_sm_margin(0)
@@ -393,23 +393,9 @@ class ExpertParallelInt4:
             # rows of the final sum: [0, M) this rank's own partial per token, then one row per pair
             cap = M * min(top_k, self.world - 1)
             rows_all = torch.empty((M + cap, self.N), dtype=torch.float32, device=A.device)
-            if A.is_cuda and self.partial_fn == self._partial_cuda:
-                from . import _lib, ops
-
-                if self._side is None:
-                    self._side = torch.cuda.Stream(device=A.device)
+            fused_home = A.is_cuda and self.partial_fn == self._partial_cuda
+            if fused_home:
                 routing_home = torch.cat([home_ids, home[1].view(torch.int32)], dim=1).contiguous()
-                self._side.wait_stream(torch.cuda.current_stream(A.device))
-                if self.sm_margin > 0:
-                    _lib.set_sm_margin(self.sm_margin)   # the exchange kernels need SMs beside the persistent GEMMs
-                with torch.cuda.stream(self._side):
-                    ops.moe_int4_w4a16_partial(A, self.packed, self.scale, routing_home, group_size=self.group_size,
-                                               out=rows_all[:M], workspace_tag=2)
-                    local_done = torch.cuda.Event()
-                    local_done.record(self._side)
-                A.record_stream(self._side)
-                rows_all.record_stream(self._side)
-                routing_home.record_stream(self._side)
             else:
                 rows_all[:M] = self.partial_fn(A, home_ids, home[1])
         if A.is_cuda:
@@ -424,6 +410,30 @@ class ExpertParallelInt4:
             pending = exchange_counts_begin(counts, self.group, n_bad=info[1], capacity=self.max_recv_rows,
                                             n_slots=M * top_k)
             send_all = ops.gather_rows(A, pair_token, info[0:1])          # [M * top_k, K]; the first P rows are set
+            if local_first and fused_home:
+                # The local pass goes to a second stream AFTER everything the exchange waits for has been
+                # queued (plan, counts, send-buffer gather), so that those kernels get their SMs first;
+                # it then runs beside the host's wait for the counts and the dispatch all-to-all, with
+                # sm_margin SMs left to NCCL's kernels.  The remote pass afterwards takes every SM.
+                from . import _lib
+
+                if self._side is None:
+                    self._side = torch.cuda.Stream(device=A.device)
+                self._side.wait_stream(torch.cuda.current_stream(A.device))
+                if self.sm_margin > 0:
+                    _lib.set_sm_margin(self.sm_margin)
+                try:
+                    with torch.cuda.stream(self._side):
+                        ops.moe_int4_w4a16_partial(A, self.packed, self.scale, routing_home, group_size=self.group_size,
+                                                   out=rows_all[:M], workspace_tag=2)
+                        local_done = torch.cuda.Event()
+                        local_done.record(self._side)
+                finally:
+                    if self.sm_margin > 0:
+                        _lib.set_sm_margin(0)
+                A.record_stream(self._side)
+                rows_all.record_stream(self._side)
+                routing_home.record_stream(self._side)
             send_l, recv_l = pending.finish()
             P = sum(sum(r) for r in send_l)
             pair_token, send_R, send_A = pair_token[:P], routing[:P], send_all[:P]
@@ -470,7 +480,7 @@ class ExpertParallelInt4:
         # ... then per chunk: wait for its rows, expert GEMM + per-row sum, send the fp32 partials home
         back_works = []
         fused_partial = A.is_cuda and self.partial_fn == self._partial_cuda
-        margin = (use_async or local_done is not None) and fused_partial and self.sm_margin > 0
+        margin = use_async and fused_partial and self.sm_margin > 0
         if margin:
             from . import _lib
 
