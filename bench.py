@@ -84,7 +84,9 @@ class ClockSampler:
                 self.proc.kill()
 
     def summary(self):
-        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0,
+               "window": "the timed steps plus an untimed continuation of the same loop (about 0.45 s; "
+                         "the timed steps alone are shorter than one sampling period)"}
         if not self.path or not os.path.exists(self.path):
             return out
         sm, mx, reasons = [], [], set()
@@ -252,6 +254,19 @@ def workload_config(cfg, world: int):
 # --------------------------------------------------------------------------------------
 # helpers
 # --------------------------------------------------------------------------------------
+def keep_loaded(fn, sync, total_ms: float, steps: int, seconds: float = 0.45, cap: int = 4000):
+    """Untimed continuation of the timed loop, run while the clock sampler is still on: the K timed
+    steps of a decode-sized call last a few milliseconds, less than one nvidia-smi sampling period, so
+    the clocks and throttle reasons are read while the SAME loop goes on for about `seconds` more.
+    The number of extra steps depends only on the arguments (every rank passes the same ones)."""
+    per_step = max(total_ms / max(steps, 1), 1e-3)
+    n = int(min(cap, max(1, seconds * 1e3 / per_step)))
+    for i in range(n):
+        fn(i)
+    sync()
+    return n
+
+
 def timed_loop(fn, steps: int, sync, barrier):
     """barrier + synchronize, K steps between two CUDA events on the current stream, barrier +
     synchronize.  Returns milliseconds for all K steps."""
@@ -343,7 +358,8 @@ def run_single_gpu(args):
     launches0 = _lib.launch_count()
     with ClockSampler(0) as clocks:
         ms = timed_loop(step, args.steps, sync, lambda: None)
-    launches = _lib.launch_count() - launches0
+        launches = _lib.launch_count() - launches0
+        keep_loaded(step, sync, ms, args.steps)
     ops.check_status(dev)
     # ---- the GEMM kernel's own duration, live, in a second pass of K steps: the event pairs the
     # library records around that launch sit between the kernels of a call and would keep them from
@@ -672,9 +688,14 @@ def run_multi_gpu(args, world: int, rank: int, local_rank: int):
     if sampler:
         sampler.__enter__()
     ms = timed_loop(step, args.steps, sync, dist.barrier)
+    launches = _lib.launch_count() - launches0
+    # same number of extra steps on every rank (the steps are collective): from the slowest rank's time
+    t_all = torch.tensor([ms], device=dev, dtype=torch.float64)
+    dist.all_reduce(t_all, op=dist.ReduceOp.MAX)
+    keep_loaded(step, sync, float(t_all), args.steps, cap=400)
+    dist.barrier()
     if sampler:
         sampler.__exit__()
-    launches = _lib.launch_count() - launches0
     _lib.gemm_timer_enable(4 * args.steps)      # kernel durations in a second pass (see run_single_gpu);
     timed_loop(step, args.steps, sync, dist.barrier)   # a step may launch more than one GEMM (local pass, chunks)
     gemm_ms = _lib.gemm_timer_read()

@@ -287,7 +287,12 @@ int xkb_fused_moe_mxfp4(const void* A, int a_dtype, const uint8_t* w13,
 /* ------------------------------------------------------------------------
  * Device status of the last fused call that used `workspace`: synchronises
  * `stream`, reads the status word in the workspace header and returns
- * XKB_ERR_DEVICE if a tcgen05 kernel gave up one of its bounded waits.
+ * XKB_ERR_DEVICE if the word is not zero.  Low byte of the word: 1 = a
+ * tcgen05 kernel gave up one of its bounded waits (the wait site in the upper
+ * bits), 2 = an MXFP4 scale byte outside the range the 128-token instance of
+ * the tcgen05 path converts, 3 = a kernel read a routing value (token-block
+ * count, expert id) outside what the routing buffers can hold and skipped the
+ * work instead of using it as an index.
  * The reference reports kernel failures as Python exceptions raised by the
  * launch (src/xkernels/_dispatch.py:204-240); this is the explicit query.
  * ---------------------------------------------------------------------- */

@@ -42,6 +42,7 @@
 // a status code, all roles leave their loops, and tensor memory is released.
 
 #include <atomic>
+#include <mutex>
 #include "moe_kernels.h"
 #include "tc_common.cuh"
 
@@ -936,8 +937,34 @@ EncodeTiledFn get_encode_fn() {
 }
 
 // 2-D row-major tensor [rows, cols] of `elem_bytes` elements, box [box_rows, box_cols].
+// Encoded maps are kept per (base, shape, box, type, swizzle): a serving loop calls with the same
+// weights and workspace addresses every step, and an encode costs about as much host time as a launch.
+// A map holds no device state, so a stale entry (memory freed and reused with another layout) is
+// harmless: the key is everything the encoding depends on.
+struct MapKey {
+  const void* base; uint64_t rows, cols; uint32_t box_rows, box_cols; int dt, elem_bytes, swz;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && rows == o.rows && cols == o.cols && box_rows == o.box_rows && box_cols == o.box_cols &&
+           dt == o.dt && elem_bytes == o.elem_bytes && swz == o.swz;
+  }
+};
+constexpr int kMapCacheSize = 64;
+struct MapCache {
+  std::mutex mu;
+  MapKey keys[kMapCacheSize];
+  CUtensorMap maps[kMapCacheSize];
+  int used = 0, next = 0;
+};
+MapCache g_map_cache;
+
 int make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const void* base, uint64_t rows,
                 uint64_t cols, uint32_t box_rows, uint32_t box_cols, CUtensorMapSwizzle swz, const char* what) {
+  const MapKey key{base, rows, cols, box_rows, box_cols, (int)dt, elem_bytes, (int)swz};
+  {
+    std::lock_guard<std::mutex> lock(g_map_cache.mu);
+    for (int i = 0; i < g_map_cache.used; ++i)
+      if (g_map_cache.keys[i] == key) { *map = g_map_cache.maps[i]; return XKB_OK; }
+  }
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) return fail(XKB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   XKB_REQUIRE(reinterpret_cast<uintptr_t>(base) % 16 == 0, "%s: base pointer must be 16-byte aligned", what);
@@ -951,6 +978,12 @@ int make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const 
   CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(XKB_ERR_CUDA, "cuTensorMapEncodeTiled(%s) failed with CUresult %d", what, (int)r);
+  {
+    std::lock_guard<std::mutex> lock(g_map_cache.mu);
+    const int slot = g_map_cache.used < kMapCacheSize ? g_map_cache.used++ : (g_map_cache.next++ % kMapCacheSize);
+    g_map_cache.keys[slot] = key;
+    g_map_cache.maps[slot] = *map;
+  }
   return XKB_OK;
 }
 
@@ -958,11 +991,25 @@ template <int BT, int MODE>
 int launch_bt(const CUtensorMap& tmp, const CUtensorMap& tms, const CUtensorMap& tmt, const TcParams& prm,
               int64_t max_tiles, cudaStream_t stream) {
   using Cfg = TcCfg<BT, mode_mats(MODE), mode_is_int4(MODE)>;
-  XKB_CHECK_CUDA(cudaFuncSetAttribute(moe_tc_kernel<BT, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      (int)Cfg::kSmemBytes));
-  int dev = 0, sms = 148;
+  int dev = 0;
   XKB_CHECK_CUDA(cudaGetDevice(&dev));
-  XKB_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  // once per (kernel instance, device): the shared-memory opt-in and the SM count
+  static std::atomic<uint64_t> smem_set{0};
+  static std::atomic<int> sm_count[64];
+  const uint64_t bit = dev < 64 ? (1ull << dev) : 0ull;
+  if (bit == 0 || (smem_set.load(std::memory_order_acquire) & bit) == 0) {
+    XKB_CHECK_CUDA(cudaFuncSetAttribute(moe_tc_kernel<BT, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)Cfg::kSmemBytes));
+    int n = 148;
+    XKB_CHECK_CUDA(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
+    if (bit != 0) {
+      sm_count[dev].store(n, std::memory_order_relaxed);
+      smem_set.fetch_or(bit, std::memory_order_release);
+    }
+  }
+  int sms = 148;
+  if (bit != 0) sms = sm_count[dev].load(std::memory_order_relaxed);
+  else XKB_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   // one persistent CTA per SM (it owns all 512 tensor-memory columns), minus the SMs the caller
   // asked to keep free for kernels that should run beside this one (xkb_set_sm_margin)
   XKB_REQUIRE(max_tiles < (1ll << 31), "moe_tc_kernel: %lld tiles do not fit the kernel's 31-bit tile index", (long long)max_tiles);
