@@ -108,7 +108,8 @@ class ClockSampler:
         except OSError:
             pass
         if sm:
-            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm),
+                       sm_mhz_first_sample=sm[0])
         return out
 
 
@@ -261,10 +262,13 @@ def keep_loaded(fn, sync, total_ms: float, steps: int, seconds: float = 0.45, ca
     The number of extra steps depends only on the arguments (every rank passes the same ones)."""
     per_step = max(total_ms / max(steps, 1), 1e-3)
     n = int(min(cap, max(1, seconds * 1e3 / per_step)))
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
     for i in range(n):
         fn(i)
+    stop.record()
     sync()
-    return n
+    return n, start.elapsed_time(stop)
 
 
 def timed_loop(fn, steps: int, sync, barrier):
@@ -359,7 +363,7 @@ def run_single_gpu(args):
     with ClockSampler(0) as clocks:
         ms = timed_loop(step, args.steps, sync, lambda: None)
         launches = _lib.launch_count() - launches0
-        keep_loaded(step, sync, ms, args.steps)
+        n_more, ms_more = keep_loaded(step, sync, ms, args.steps)
     ops.check_status(dev)
     # ---- the GEMM kernel's own duration, live, in a second pass of K steps: the event pairs the
     # library records around that launch sit between the kernels of a call and would keep them from
@@ -420,6 +424,9 @@ def run_single_gpu(args):
         "us_per_call": ms_per_step * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": workload_config(cfg, 1), "clocks": clocks.summary(), "e2e": e2e,
+        "sustained": {"tokens_per_s": cfg.M * n_more / (ms_more * 1e-3), "ms_per_step": ms_more / n_more, "steps": n_more,
+                      "note": "the untimed continuation of the timed loop during which the clocks were sampled "
+                              "(long enough for the power cap to act)"},
         "gpu_launches": int(launches), "roofline": roofline, "parity": parity,
     }
     if not args.no_extras:
@@ -692,7 +699,7 @@ def run_multi_gpu(args, world: int, rank: int, local_rank: int):
     # same number of extra steps on every rank (the steps are collective): from the slowest rank's time
     t_all = torch.tensor([ms], device=dev, dtype=torch.float64)
     dist.all_reduce(t_all, op=dist.ReduceOp.MAX)
-    keep_loaded(step, sync, float(t_all), args.steps, cap=400)
+    n_more, ms_more = keep_loaded(step, sync, float(t_all), args.steps, cap=400)
     dist.barrier()
     if sampler:
         sampler.__exit__()
@@ -764,6 +771,9 @@ def run_multi_gpu(args, world: int, rank: int, local_rank: int):
             "config": workload_config(synth.Int4Config(cfg.name, M=tokens, K=cfg.K, N=cfg.N, E=cfg.E,
                                                        top_k=cfg.top_k), world),
             "clocks": sampler.summary() if sampler else None,
+            "sustained": {"tokens_per_s": world * cfg.M * n_more / (ms_more * 1e-3), "ms_per_step": ms_more / n_more,
+                          "steps": n_more, "note": "rank 0's untimed continuation of the timed loop during which "
+                                                   "the clocks were sampled"},
             "e2e": {"value": tokens / (e2e_ms / args.steps * 1e-3), "unit": "tokens/s",
                     "h2d_bytes_per_step": world * stage.nbytes,
                     "d2h_bytes_per_step": world * hO.numel() * 2},
