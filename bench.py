@@ -620,6 +620,36 @@ def extras(dev, peaks):
     torch.cuda.empty_cache()
     settle()
     try:
+        # the two GEMMs above as ONE expert layer: gate_up (2*inter = 4096 rows) -> SwiGLU -> down, one call
+        hidden, inter, E, top_k = 7168, 2048, 48, 8
+        w13, s13 = synth.int4_weights(E, 2 * inter, hidden, 32, seed=21, device=dev)
+        w2, s2 = synth.int4_weights(E, hidden, inter, 32, seed=22, device=dev)
+        rows = {}
+        for M in (16, 64):
+            A = synth.activations(M, hidden, seed=M + 1, device=dev)
+            ids, w = synth.routing(M, E, top_k, seed=M + 4, device=dev)
+            fn = lambda: xkb.fused_moe_int4_ffn(A, w13, s13, w2, s2, ids, w)  # noqa: E731
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            ms = time_call(fn, 0, 20)           # the call, kernels overlapping as in use
+            _lib.gemm_timer_enable(20)
+            time_call(fn, 0, 20)
+            g = _lib.gemm_timer_read()
+            _lib.gemm_timer_enable(0)
+            gm = sum(g) / 20
+            n_act = int(torch.unique(ids).numel())
+            b = n_act * (2 * inter * hidden + hidden * inter) * (0.5 + 2.0 / 32)      # packed nibbles + bf16 group scales
+            rows[f"M={M}"] = {"us_per_call": ms * 1e3, "gemm_kernels_us": gm * 1e3, "active_experts": n_act,
+                              "weight_bytes": b, "kernels_frac_of_hbm_peak": b / (gm * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+        ops.check_status(dev)
+        out["int4_ffn_hidden7168_inter2048"] = rows
+        del w13, s13, w2, s2
+    except Exception as exc:  # noqa: BLE001
+        out["int4_ffn_hidden7168_inter2048"] = {"error": repr(exc)[:300]}
+    torch.cuda.empty_cache()
+    settle()
+    try:
         cfg = synth.CONFIGS["int4_prefill"]
         d = synth.make_int4(cfg, seed=1729, device=dev)
         fn = lambda: xkb.fused_moe_int4_w4a16(d["A"], d["packed"], d["scale"], d["topk_ids"], d["topk_w"])  # noqa: E731
