@@ -71,6 +71,11 @@ struct Routing {
   int64_t max_pad;   // length of sorted_ids
   int64_t max_blocks;
   int block;
+  // two arrays of `counters_each` ints, zeroed with the status word at the start of a fused call:
+  // [0] rows the gather kernel has delivered per token block, [1] finished read-outs of the first
+  // GEMM of a two-GEMM layer per token block (nullptr: the kernels do not overlap that way)
+  int32_t* block_counters;
+  int64_t counters_each;
 };
 
 // Internal launchers shared between translation units --------------------------

@@ -52,6 +52,8 @@ namespace {
 
 struct RoutingBuffers {
   int* status;
+  int32_t* counters;        // directly behind the status header: one memset clears both
+  int64_t counters_each;
   int32_t* sorted_ids;
   int32_t* expert_ids;
   int32_t* num_post;
@@ -73,6 +75,8 @@ int64_t routing_max_pad(int64_t numel, int E, int block) {
 RoutingBuffers carve_routing(Carver& c, int64_t numel, int E) {
   RoutingBuffers r;
   r.status = c.take<int>(64);  // workspace header: word 0 = device status of the last call
+  r.counters_each = numel / kMinBlock + E + 2;     // >= token blocks at the smallest token tile
+  r.counters = c.take<int32_t>(2 * r.counters_each);
   r.sorted_ids = c.take<int32_t>(routing_max_pad(numel, E, kMaxBlock));
   r.expert_ids = c.take<int32_t>(ceil_div(routing_max_pad(numel, E, kMinBlock), kMinBlock) + 1);
   r.num_post = c.take<int32_t>(1);
@@ -80,6 +84,11 @@ RoutingBuffers carve_routing(Carver& c, int64_t numel, int E) {
   r.align_ws_bytes = align_workspace_bytes(numel, E);
   r.align_ws = c.take<char>(r.align_ws_bytes);
   return r;
+}
+
+// status header and the block counters behind it, as one span
+size_t header_bytes(const RoutingBuffers& r) {
+  return (size_t)(reinterpret_cast<const char*>(r.counters + 2 * r.counters_each) - reinterpret_cast<const char*>(r.status));
 }
 
 int64_t routing_bytes(int64_t numel, int E) {
@@ -98,6 +107,8 @@ Routing make_routing(const RoutingBuffers& b, int64_t numel, int E, int block) {
   r.block = block;
   r.max_pad = routing_max_pad(numel, E, block);
   r.max_blocks = ceil_div(r.max_pad, block);
+  r.block_counters = b.counters;
+  r.counters_each = b.counters_each;
   return r;
 }
 
@@ -165,7 +176,7 @@ static int int4_impl(const void* A, int a_dtype, const int32_t* packed, const vo
   const int block = use_tc ? int4_tc_block(numel, E) : kSimtBlock;
 
   Routing r = make_routing(rb, numel, E, block);
-  XKB_CHECK_CUDA(cudaMemsetAsync(rb.status, 0, sizeof(int), stream));
+  XKB_CHECK_CUDA(cudaMemsetAsync(rb.status, 0, header_bytes(rb), stream));   // status word + block counters
   int rc = launch_align(topk_ids, numel, E, block, expert_map, num_map, rb.sorted_ids, rb.expert_ids,
                         rb.num_post, rb.expert_off, rb.align_ws, rb.align_ws_bytes, stream);
   if (rc != XKB_OK) return rc;
@@ -309,7 +320,7 @@ extern "C" int xkb_fused_moe_int4_ffn(const void* A, int a_dtype, const int32_t*
   const bool use_tc = (path == XKB_PATH_TC) || (path == XKB_PATH_AUTO && tc_fit);
   const int block = use_tc ? int4_tc_block(numel, E) : kSimtBlock;
   Routing r = make_routing(rb, numel, E, block);
-  XKB_CHECK_CUDA(cudaMemsetAsync(rb.status, 0, sizeof(int), stream));
+  XKB_CHECK_CUDA(cudaMemsetAsync(rb.status, 0, header_bytes(rb), stream));   // status word + block counters
   int rc = launch_align(topk_ids, numel, E, block, expert_map, num_map, rb.sorted_ids, rb.expert_ids, rb.num_post,
                         rb.expert_off, rb.align_ws, rb.align_ws_bytes, stream);
   if (rc != XKB_OK) return rc;
@@ -379,7 +390,7 @@ extern "C" int xkb_fused_moe_mxfp4(const void* A, int a_dtype, const uint8_t* w1
   const int block = use_tc ? mxfp4_tc_block(numel, E) : kSimtBlock;
 
   Routing r = make_routing(rb, numel, E, block);
-  XKB_CHECK_CUDA(cudaMemsetAsync(rb.status, 0, sizeof(int), stream));
+  XKB_CHECK_CUDA(cudaMemsetAsync(rb.status, 0, header_bytes(rb), stream));   // status word + block counters
   int rc = launch_align(topk_ids, numel, E, block, expert_map, num_map, rb.sorted_ids, rb.expert_ids,
                         rb.num_post, rb.expert_off, rb.align_ws, rb.align_ws_bytes, stream);
   if (rc != XKB_OK) return rc;

@@ -388,7 +388,8 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
   // Every CTA of the first GEMM is resident before any CTA of the second starts and never waits for
   // the second, so the wait cannot deadlock; it is bounded all the same.  The first GEMM lets its
   // dependents go only after its own wait for the kernels before it, so that what those wrote (the
-  // routing, the zeroed counters) is visible to the second GEMM although it skips its wait.
+  // routing) is visible to the second GEMM although it skips its wait; the counters are cleared
+  // together with the status word by the memset that opens the fused call.
   const bool hand_over_first = mode_is_gate_up(MODE) && p.done_signal != nullptr;
   const bool hand_over_second = p.done_wait != nullptr;
   if (!hand_over_first) chain_trigger();   // the next kernel may be launched; it waits for this one's completion itself
@@ -881,8 +882,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_consta
 __global__ void __launch_bounds__(256)
 gather_permute_kernel(const __nv_bfloat16* __restrict__ A, const int32_t* sorted_ids,
                       const int32_t* num_post, __nv_bfloat16* __restrict__ Ag, int64_t numel,
-                      int K, int top_k, int permute, int32_t* __restrict__ zero, int zero_n, int64_t max_pad,
-                      int* __restrict__ status) {
+                      int K, int top_k, int permute, int64_t max_pad, int* __restrict__ status) {
   // The routing comes from the align kernel before this one, which may still be running when this
   // kernel starts.  It is read with L2 loads after the wait and through pointers that are NOT
   // `const __restrict__`: loads the compiler may treat as invariant (ld.global.nc) were seen to
@@ -890,8 +890,6 @@ gather_permute_kernel(const __nv_bfloat16* __restrict__ A, const int32_t* sorted
   // the non-coherent cache).
   chain_wait();
   chain_trigger();
-  // the per-block counters of the block hand-over between the two GEMMs that follow (if any)
-  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < zero_n; i += gridDim.x * blockDim.x) zero[i] = 0;
   int total = __ldcg(num_post);
   if (total < 0 || total > max_pad) {   // never with a routing the align stage wrote: recorded, nothing gathered
     if (threadIdx.x == 0 && blockIdx.x == 0) atomicCAS(status, 0, kErrBadRouting + (3 << 8));
@@ -1041,15 +1039,13 @@ int int4_tc_block(int64_t numel, int E) {
   return 128;  // wide: 128 tokens x two 128-row weight tiles per CTA (one tile if N % 256 != 0)
 }
 
-// counters of the block hand-over: one per token block of the smallest token tile
-static int64_t hand_over_bytes(int64_t numel, int E) { return align_up((numel / 16 + E + 2) * 4, 256); }
 // read-out warps that count per tile of the first GEMM: four per warpgroup on duty
 static int hand_over_per_tile(int block) { return 4 * (block / 16 < 4 ? block / 16 : 4); }
 
 int64_t int4_tc_workspace_bytes(int64_t numel, int64_t N, int64_t K, int E) {
   (void)N;
-  // gathered activations for the largest token tile + one counter per token block (two-GEMM layer)
-  return align_up((numel + (int64_t)(E + 1) * 255) * K * 2, 256) + hand_over_bytes(numel, E);
+  // gathered activations for the largest token tile
+  return align_up((numel + (int64_t)(E + 1) * 255) * K * 2, 256);
 }
 
 // one INT4 GEMM (tokens through `tm_tokens`) at the token tile the routing was aligned for
@@ -1078,7 +1074,7 @@ int launch_int4_tc(const void* A, const int32_t* packed, const void* scale, cons
   if (gblocks < 1) gblocks = 1;
   XKB_CHECK_CUDA(launch_chained(gather_permute_kernel, dim3((unsigned)gblocks), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(A),
                                                                r.sorted_ids, r.num_post, Ag, r.numel, (int)K,
-                                                               top_k, 1, static_cast<int32_t*>(nullptr), 0, r.max_pad, status));
+                                                               top_k, 1, r.max_pad, status));
   XKB_CHECK_LAUNCH("gather_permute_kernel");
 
   CUtensorMap tm_packed, tm_scale, tm_tokens;
@@ -1131,12 +1127,12 @@ int launch_int4_ffn_tc(const void* A, const int32_t* w13, const void* s13, const
                        const Routing& r, const float* topk_w, __nv_bfloat16* act, float* scratch, int64_t hidden,
                        int64_t inter, int E, int top_k, float limit, void* tc_ws, int* status, cudaStream_t stream) {
   Carver carve(tc_ws);
-  int32_t* done = carve.take<int32_t>(r.numel / 16 + E + 2);   // block hand-over counters, zeroed by the gather kernel
+  int32_t* done = r.block_counters != nullptr ? r.block_counters + r.counters_each : nullptr;   // block hand-over counters
   __nv_bfloat16* Ag = carve.take<__nv_bfloat16>(r.max_pad * hidden);
   int64_t gblocks = r.max_pad < 148 * 16 ? r.max_pad : 148 * 16;
   if (gblocks < 1) gblocks = 1;
   XKB_CHECK_CUDA(launch_chained(gather_permute_kernel, dim3((unsigned)gblocks), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(A), r.sorted_ids,
-                                                               r.num_post, Ag, r.numel, (int)hidden, top_k, 1, done, (int)r.max_blocks, r.max_pad, status));
+                                                               r.num_post, Ag, r.numel, (int)hidden, top_k, 1, r.max_pad, status));
   XKB_CHECK_LAUNCH("gather_permute_kernel");
   CUtensorMap tm_w13, tm_s13, tm_w2, tm_s2, tm_tok0, tm_tok1;
   int rc = make_map_2d(&tm_w13, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w13, (uint64_t)E * 2 * inter, (uint64_t)hidden / 2,
@@ -1223,7 +1219,7 @@ int mxfp4_tc_block(int64_t numel, int E) {
 
 int64_t mxfp4_tc_workspace_bytes(int64_t numel, int64_t hidden, int64_t ispp, int E) {
   (void)ispp;
-  return align_up((numel + (int64_t)(E + 1) * 255) * hidden * 2, 256) + hand_over_bytes(numel, E);  // gathered activations, block counters
+  return align_up((numel + (int64_t)(E + 1) * 255) * hidden * 2, 256);  // gathered activations
 }
 
 int launch_mxfp4_tc(const void* A, const uint8_t* w13, const uint8_t* w13_scale, const uint8_t* w2,
@@ -1234,7 +1230,7 @@ int launch_mxfp4_tc(const void* A, const uint8_t* w13, const uint8_t* w13_scale,
   XKB_REQUIRE(reinterpret_cast<uintptr_t>(w13_scale) % 16 == 0 && reinterpret_cast<uintptr_t>(w2_scale) % 16 == 0,
               "mxfp4 tcgen05 path: scale tensors must be 16-byte aligned");
   Carver carve(tc_ws);
-  int32_t* done = carve.take<int32_t>(r.numel / 16 + E + 2);   // block hand-over counters, zeroed by the gather kernel
+  int32_t* done = r.block_counters != nullptr ? r.block_counters + r.counters_each : nullptr;   // block hand-over counters
   __nv_bfloat16* Ag = carve.take<__nv_bfloat16>(r.max_pad * hidden);
   int64_t gblocks = r.max_pad < 148 * 16 ? r.max_pad : 148 * 16;
   if (gblocks < 1) gblocks = 1;
@@ -1242,7 +1238,7 @@ int launch_mxfp4_tc(const void* A, const uint8_t* w13, const uint8_t* w13_scale,
                                                                r.sorted_ids, r.num_post, Ag, r.numel,
                                                                (int)hidden, top_k,
                                                                r.block == 16 ? 0 : 1,   // 16-token tiles convert through the table: natural K order
-                                                               done, (int)r.max_blocks, r.max_pad, status));
+                                                               r.max_pad, status));
   XKB_CHECK_LAUNCH("gather_permute_kernel");
 
   CUtensorMap tm_w13, tm_w2, tm_tok0, tm_tok1, tm_s13, tm_s2;
