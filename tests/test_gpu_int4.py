@@ -173,6 +173,23 @@ def test_alternating_shapes_share_the_workspace(cuda_device):
             assert torch.equal(got, want)
 
 
+def test_prefill_sized_batch_whole_output(cuda_device):
+    """16 384 slots at 128-token tiles (two row tiles per token tile), skewed routing: the whole
+    output against the oracle, repeated calls bit-identical, status clear."""
+    from xkernels_b200 import ops
+
+    cfg = synth.Int4Config("prefill_sized", M=2048, K=1024, N=512, E=16, top_k=8, expert_bias_std=0.5)
+    d = synth.make_int4(cfg, seed=5, device=cuda_device)
+    out = xkb.fused_moe_int4_w4a16(d["A"], d["packed"], d["scale"], d["topk_ids"], d["topk_w"], path="tc")
+    ops.check_status(cuda_device)
+    want = oracle.moe_w4a16(d["A"].cpu(), d["packed"].cpu(), d["scale"].cpu(), d["topk_ids"].cpu(), d["topk_w"].cpu(), 32)
+    assert_within(out, want, *TOL[torch.bfloat16], what="prefill-sized batch")
+    for _ in range(5):
+        again = xkb.fused_moe_int4_w4a16(d["A"], d["packed"], d["scale"], d["topk_ids"], d["topk_w"], path="tc")
+        ops.check_status(cuda_device)
+        assert torch.equal(out, again)
+
+
 def prefill_token_sample(topk_ids: torch.Tensor, E: int, block: int, n_tokens: int, seed: int) -> torch.Tensor:
     """Token rows to check at the prefill configuration: for every expert the tokens whose slots sit
     at the first and the last position of the expert's sorted run (so the first and the last,
