@@ -366,6 +366,10 @@ def fused_moe_mxfp4(A, w13, w13_scale, w2, w2_scale, topk_ids, topk_w, b13=None,
     ``w13`` ``[E, 2*ispp, hidden//2]`` and ``w2`` ``[E, hidden, ispp//2]`` are uint8
     E2M1 pairs, the scales uint8 e8m0 per 32 elements.  The three bf16 rounding
     points of the reference (gate_up, activation, down) are reproduced.
+    ``workspace`` as in :func:`fused_moe_int4_w4a16` (None, a CUDA uint8 tensor or the reference's
+    ``MoeMxfp4Workspace``).  After a call :func:`check_status` (or :func:`check_workspace_status`)
+    reports a kernel that gave up a bounded wait, a scale byte the prefill-sized tcgen05 instance
+    does not convert (191..254), or a routing value out of range.
     """
     lib = _lib.load()
     dev = _require_cuda("fused_moe_mxfp4", A, w13, w13_scale, w2, w2_scale, topk_ids, topk_w, b13, b2,
@@ -428,6 +432,7 @@ def fused_moe_int4_ffn(A, w13_packed, w13_scale, w2_packed, w2_scale, topk_ids, 
     ``w13``, the second GEMM with the routing weights (bf16 result per slot), ``moe_sum_reduce`` over
     the slots.  ``w13_packed [E, 2*inter, hidden//8]``, ``w13_scale [E, 2*inter, hidden//group]``,
     ``w2_packed [E, hidden, inter//8]``, ``w2_scale [E, hidden, inter//group]``.
+    ``workspace`` and :func:`check_status` as in :func:`fused_moe_int4_w4a16`.
     """
     lib = _lib.load()
     dev = _require_cuda("fused_moe_int4_ffn", A, w13_packed, w13_scale, w2_packed, w2_scale, topk_ids, topk_w, expert_map)
